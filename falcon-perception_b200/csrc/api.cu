@@ -1,0 +1,169 @@
+// extern "C" boundary of libfpkv.so: argument validation, then the launchers.
+// Declarations and the reference code each entry point replaces: include/fpkv.h.
+
+#include "common.cuh"
+
+using namespace fpkv;
+
+namespace {
+
+inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
+
+int esize_of(int dtype) {
+    switch (dtype) {
+        case FPKV_F32: return 4;
+        case FPKV_BF16: case FPKV_F16: return 2;
+    }
+    return 0;
+}
+
+// Validate the pool descriptor and build the internal view.
+int make_view(const fpkv_pool* pool, int layer, PoolView* pv) {
+    if (pool == nullptr || pool->data == nullptr || pool->page_table == nullptr ||
+        pool->physical_to_logical == nullptr)
+        return FPKV_EINVAL;
+    const int es = esize_of(pool->dtype);
+    if (es == 0) return FPKV_EDTYPE;
+    if (pool->num_layers <= 0 || pool->n_heads <= 0 || pool->n_pages <= 0 || pool->max_batch_size <= 0)
+        return FPKV_EINVAL;
+    if (layer < 0 || layer >= pool->num_layers) return FPKV_EINVAL;
+    if (pool->head_dim != 64 && pool->head_dim != 128) return FPKV_ESHAPE;
+    if (pool->page_size <= 0 || pool->page_size % 16 != 0) return FPKV_ESHAPE;
+    if (!aligned16(pool->data)) return FPKV_EALIGN;
+    pv->base = static_cast<char*>(pool->data);
+    pv->page_table = pool->page_table;
+    pv->p2l = pool->physical_to_logical;
+    pv->num_layers = pool->num_layers; pv->H = pool->n_heads; pv->n_pages = pool->n_pages;
+    pv->P = pool->page_size; pv->D = pool->head_dim; pv->max_batch = pool->max_batch_size;
+    pv->dtype = pool->dtype; pv->esize = es;
+    return FPKV_OK;
+}
+
+int check_rows(const void* p, long long s0, long long s1, int esize) {
+    if (p == nullptr) return FPKV_EINVAL;
+    if (!aligned16(p) || (s0 * esize) % 16 != 0 || (s1 * esize) % 16 != 0) return FPKV_EALIGN;
+    return FPKV_OK;
+}
+
+int check_arch() {
+    int dev = 0, major = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess) return FPKV_EARCH;
+    if (cudaDeviceGetAttribute(&major, cudaDevAttrComputeCapabilityMajor, dev) != cudaSuccess) return FPKV_EARCH;
+    return major == 10 ? FPKV_OK : FPKV_EARCH;
+}
+
+}  // namespace
+
+extern "C" {
+
+int fpkv_version(void) { return 100; }
+
+const char* fpkv_strerror(int code) {
+    switch (code) {
+        case FPKV_OK: return "ok";
+        case FPKV_EINVAL: return "invalid argument (null pointer, negative size or bad enum)";
+        case FPKV_ESHAPE: return "unsupported shape (head_dim, page_size or head ratio)";
+        case FPKV_EALIGN: return "pointer or stride is not 16-byte aligned";
+        case FPKV_EARCH: return "device is not sm_100";
+        case FPKV_ELAUNCH: return "CUDA error at kernel launch";
+        case FPKV_EWORKSPACE: return "workspace too small";
+        case FPKV_EDTYPE: return "dtype not supported by this entry point";
+    }
+    return "unknown fpkv error code";
+}
+
+int fpkv_append_decode(const fpkv_pool* pool, int32_t layer, const int64_t* batch_idx, const void* input_pos,
+                       int32_t pos_type, const void* k, int64_t k_stride_b, int64_t k_stride_h,
+                       const void* v, int64_t v_stride_b, int64_t v_stride_h, int32_t B, int32_t* status,
+                       void* stream)
+{
+    PoolView pv;
+    int rc = make_view(pool, layer, &pv);
+    if (rc) return rc;
+    if (B < 0 || (pos_type != FPKV_I32 && pos_type != FPKV_I64)) return FPKV_EINVAL;
+    if (B == 0) return FPKV_OK;
+    if (batch_idx == nullptr || input_pos == nullptr) return FPKV_EINVAL;
+    if ((rc = check_rows(k, k_stride_b, k_stride_h, pv.esize))) return rc;
+    if ((rc = check_rows(v, v_stride_b, v_stride_h, pv.esize))) return rc;
+    if ((rc = check_arch())) return rc;
+    return launch_append(pv, layer, batch_idx, input_pos, pos_type, k, k_stride_b, k_stride_h, v, v_stride_b,
+                         v_stride_h, B, /*decode_mode=*/true, status, static_cast<cudaStream_t>(stream));
+}
+
+int fpkv_append_packed(const fpkv_pool* pool, int32_t layer, const int64_t* batch_idx, const void* input_pos,
+                       int32_t pos_type, const void* k, int64_t k_stride_h, int64_t k_stride_t,
+                       const void* v, int64_t v_stride_h, int64_t v_stride_t, int32_t L, int32_t* status,
+                       void* stream)
+{
+    PoolView pv;
+    int rc = make_view(pool, layer, &pv);
+    if (rc) return rc;
+    if (L < 0 || (pos_type != FPKV_I32 && pos_type != FPKV_I64)) return FPKV_EINVAL;
+    if (L == 0) return FPKV_OK;
+    if (batch_idx == nullptr || input_pos == nullptr) return FPKV_EINVAL;
+    if ((rc = check_rows(k, k_stride_h, k_stride_t, pv.esize))) return rc;
+    if ((rc = check_rows(v, v_stride_h, v_stride_t, pv.esize))) return rc;
+    if ((rc = check_arch())) return rc;
+    return launch_append(pv, layer, batch_idx, input_pos, pos_type, k, k_stride_t, k_stride_h, v, v_stride_t,
+                         v_stride_h, L, /*decode_mode=*/false, status, static_cast<cudaStream_t>(stream));
+}
+
+int fpkv_gather(const fpkv_pool* pool, int32_t layer, int32_t slot, int32_t n_tokens, void* k_out, void* v_out,
+                int32_t* status, void* stream)
+{
+    PoolView pv;
+    int rc = make_view(pool, layer, &pv);
+    if (rc) return rc;
+    if (n_tokens < 0 || slot < 0 || slot >= pv.max_batch) return FPKV_EINVAL;
+    if ((long long)n_tokens > (long long)pv.n_pages * pv.P) return FPKV_EINVAL;
+    if (n_tokens == 0) return FPKV_OK;
+    if (k_out == nullptr || v_out == nullptr) return FPKV_EINVAL;
+    if (!aligned16(k_out) || !aligned16(v_out)) return FPKV_EALIGN;
+    if ((rc = check_arch())) return rc;
+    return launch_gather(pv, layer, slot, n_tokens, k_out, v_out, status, static_cast<cudaStream_t>(stream));
+}
+
+int fpkv_decode_workspace_bytes(const fpkv_pool* pool, int32_t B, int32_t n_q_heads, size_t* bytes)
+{
+    PoolView pv;
+    int rc = make_view(pool, 0, &pv);
+    if (rc) return rc;
+    if (bytes == nullptr || B < 0 || n_q_heads <= 0) return FPKV_EINVAL;
+    if (n_q_heads % pv.H) return FPKV_ESHAPE;
+    size_t a = decode_portable_workspace_bytes(B, n_q_heads, pv.D);
+    size_t b = decode_tma_workspace_bytes(n_q_heads, pv.H, pv.D);
+    *bytes = (a > b ? a : b) + 256;
+    return FPKV_OK;
+}
+
+int fpkv_decode_attn(const fpkv_pool* pool, int32_t layer, void* out, float* lse, const void* q,
+                     int64_t q_stride_b, int64_t q_stride_h, const int64_t* batch_idx, const void* input_pos,
+                     int32_t pos_type, int32_t B, int32_t n_q_heads, float sm_scale, void* workspace,
+                     size_t workspace_bytes, int32_t flags, int32_t* status, void* stream)
+{
+    PoolView pv;
+    int rc = make_view(pool, layer, &pv);
+    if (rc) return rc;
+    if (B < 0 || n_q_heads <= 0 || (pos_type != FPKV_I32 && pos_type != FPKV_I64)) return FPKV_EINVAL;
+    if (n_q_heads % pv.H) return FPKV_ESHAPE;
+    if (B == 0) return FPKV_OK;
+    if (out == nullptr || lse == nullptr || batch_idx == nullptr || input_pos == nullptr || workspace == nullptr)
+        return FPKV_EINVAL;
+    if ((rc = check_rows(q, q_stride_b, q_stride_h, pv.esize))) return rc;
+    if (!aligned16(out) || !aligned16(workspace)) return FPKV_EALIGN;
+    const int which = flags & 3;
+    const bool tma_ok = decode_tma_supported(pv, n_q_heads);
+    if (which == FPKV_DECODE_TMA && !tma_ok) return FPKV_ESHAPE;
+    const bool use_tma = which == FPKV_DECODE_TMA || (which == FPKV_DECODE_AUTO && tma_ok);
+    const size_t need = use_tma ? decode_tma_workspace_bytes(n_q_heads, pv.H, pv.D)
+                                : decode_portable_workspace_bytes(B, n_q_heads, pv.D);
+    if (workspace_bytes < need) return FPKV_EWORKSPACE;
+    if ((rc = check_arch())) return rc;
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    return use_tma ? launch_decode_tma(pv, layer, out, lse, q, q_stride_b, q_stride_h, batch_idx, input_pos,
+                                       pos_type, B, n_q_heads, sm_scale, workspace, status, s)
+                   : launch_decode_portable(pv, layer, out, lse, q, q_stride_b, q_stride_h, batch_idx,
+                                            input_pos, pos_type, B, n_q_heads, sm_scale, workspace, status, s);
+}
+
+}  // extern "C"

@@ -1,0 +1,74 @@
+// Shared device/host helpers for the fpkv kernels (sm_100a only).
+#pragma once
+
+#include <cuda_runtime.h>
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+#include <stdint.h>
+
+#include "../../include/fpkv.h"
+
+namespace fpkv {
+
+constexpr float kLog2e = 1.4426950408889634f;
+constexpr float kLn2 = 0.6931471805599453f;
+
+// Host-side view of one call's pool arguments after validation.
+struct PoolView {
+    char* base;                       // start of the pool
+    const int64_t* page_table;
+    const int64_t* p2l;
+    int num_layers, H, n_pages, P, D, max_batch, dtype, esize;
+    // bytes between consecutive (layer, k|v, head) planes and helpers
+    __host__ __device__ size_t plane_bytes() const { return (size_t)n_pages * P * D * esize; }
+    __host__ __device__ char* plane(int layer, int kv, int h) const {
+        return base + ((size_t)(layer * 2 + kv) * H + h) * plane_bytes();
+    }
+};
+
+__device__ __forceinline__ void raise_status(int32_t* status, uint32_t bits) {
+    if (status != nullptr) atomicOr(reinterpret_cast<unsigned int*>(status), bits);
+}
+
+template <typename PosT>
+__device__ __forceinline__ long long load_pos(const void* p, int i) {
+    return (long long)reinterpret_cast<const PosT*>(p)[i];
+}
+
+template <typename T> struct ElemTraits;
+template <> struct ElemTraits<float> {
+    static __device__ __forceinline__ float to_float(float x) { return x; }
+    static __device__ __forceinline__ float from_float(float x) { return x; }
+};
+template <> struct ElemTraits<__nv_bfloat16> {
+    static __device__ __forceinline__ float to_float(__nv_bfloat16 x) { return __bfloat162float(x); }
+    static __device__ __forceinline__ __nv_bfloat16 from_float(float x) { return __float2bfloat16_rn(x); }
+};
+template <> struct ElemTraits<__half> {
+    static __device__ __forceinline__ float to_float(__half x) { return __half2float(x); }
+    static __device__ __forceinline__ __half from_float(float x) { return __float2half_rn(x); }
+};
+
+// ---- launchers implemented in the .cu files (host side, internal) ----------
+int launch_append(const PoolView& pv, int layer, const int64_t* batch_idx, const void* pos, int pos_type,
+                  const void* k, long long k_stride_tok, long long k_stride_h,
+                  const void* v, long long v_stride_tok, long long v_stride_h,
+                  int n_tok, bool decode_mode, int32_t* status, cudaStream_t stream);
+
+int launch_gather(const PoolView& pv, int layer, int slot, int n_tokens, void* k_out, void* v_out,
+                  int32_t* status, cudaStream_t stream);
+
+size_t decode_portable_workspace_bytes(int B, int Hq, int D);
+int launch_decode_portable(const PoolView& pv, int layer, void* out, float* lse, const void* q,
+                           long long q_stride_b, long long q_stride_h, const int64_t* batch_idx,
+                           const void* pos, int pos_type, int B, int Hq, float sm_scale,
+                           void* workspace, int32_t* status, cudaStream_t stream);
+
+bool decode_tma_supported(const PoolView& pv, int Hq);
+size_t decode_tma_workspace_bytes(int Hq, int Hkv, int D);
+int launch_decode_tma(const PoolView& pv, int layer, void* out, float* lse, const void* q,
+                      long long q_stride_b, long long q_stride_h, const int64_t* batch_idx,
+                      const void* pos, int pos_type, int B, int Hq, float sm_scale,
+                      void* workspace, int32_t* status, cudaStream_t stream);
+
+}  // namespace fpkv

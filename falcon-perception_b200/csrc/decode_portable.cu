@@ -1,0 +1,198 @@
+// Portable paged decode attention (CUDA cores): any pool dtype (fp32, bf16,
+// fp16), head_dim 64 or 128, any page size.  It is the path for shapes the
+// TMA + tensor-core kernel does not take (fp32 pools, small pages, wide GQA
+// groups) and the on-device cross-check for that kernel; it is not tuned.
+//
+// Grid (B * Hq, S): CTA (row, split) walks the split's share of the row's
+// pages.  Each warp keeps an online-softmax state over the tokens it visits;
+// a lane owns head_dim/32 consecutive elements of q, of the K row and of the
+// output accumulator, so a token costs one coalesced K row read, a 5-step
+// shuffle reduction and one coalesced V row read.  Warps merge through shared
+// memory and the CTA writes one partial (m, l, acc[head_dim]) per split; a
+// second kernel merges the splits.
+//
+// Visible key set of row b (slot s = batch_idx[b], p = input_pos[b]): logical
+// positions 0..p whose page id PT[s, j / P] is mapped and maps back
+// (P2L[s, page] >= 0) -- the reference's decode mask after conversion to
+// physical pages (falcon_perception/paged_inference.py:797-826,
+// falcon_perception/paged_attention.py:267-333).
+
+#include "common.cuh"
+
+namespace fpkv {
+
+constexpr int kPortableWarps = 4;
+constexpr int kPortableMaxSplits = 32;
+
+__host__ __device__ inline int portable_splits(int B, int Hq) {
+    int s = (4 * 148) / (B * Hq > 0 ? B * Hq : 1);
+    if (s < 1) s = 1;
+    if (s > kPortableMaxSplits) s = kPortableMaxSplits;
+    return s;
+}
+
+template <typename T, int D, typename PosT>
+__global__ void __launch_bounds__(kPortableWarps * 32)
+decode_portable_kernel(const char* __restrict__ pool_layer, size_t plane_bytes, int H,
+                       const int64_t* __restrict__ page_table, const int64_t* __restrict__ p2l,
+                       int n_pages, int max_batch, int P,
+                       const T* __restrict__ q, long long q_stride_b, long long q_stride_h,
+                       const int64_t* __restrict__ batch_idx, const PosT* __restrict__ pos,
+                       int Hq, float scale_log2, float* __restrict__ ws, int32_t* status)
+{
+    constexpr int E = D / 32;                     // elements per lane
+    const int row = blockIdx.x;                   // b * Hq + hq
+    const int b = row / Hq, hq = row % Hq;
+    const int S = gridDim.y, split = blockIdx.y;
+    const int warp = threadIdx.x / 32, lane = threadIdx.x % 32;
+    const int n_rep = Hq / H;
+    const int h = hq / n_rep;
+
+    __shared__ float sm_m[kPortableWarps], sm_l[kPortableWarps];
+    __shared__ float sm_acc[kPortableWarps][D];
+
+    const long long slot = batch_idx[b];
+    const long long p = (long long)pos[b];
+    int n_pg = 0;
+    long long n_keys = 0;
+    if (slot < 0 || slot >= max_batch) {
+        if (threadIdx.x == 0 && split == 0) raise_status(status, FPKV_STATUS_BAD_SLOT);
+    } else if (p < 0 || p / P >= n_pages) {
+        if (threadIdx.x == 0 && split == 0) raise_status(status, FPKV_STATUS_BAD_POS);
+    } else {
+        n_keys = p + 1;
+        n_pg = (int)((n_keys + P - 1) / P);
+    }
+    const int pg0 = (int)((long long)n_pg * split / S);
+    const int pg1 = (int)((long long)n_pg * (split + 1) / S);
+
+    float qv[E];
+    {
+        const T* qp = q + b * q_stride_b + hq * q_stride_h + lane * E;
+#pragma unroll
+        for (int e = 0; e < E; ++e) qv[e] = ElemTraits<T>::to_float(qp[e]) * scale_log2;
+    }
+    float m = -INFINITY, l = 0.f, acc[E];
+#pragma unroll
+    for (int e = 0; e < E; ++e) acc[e] = 0.f;
+
+    const T* Kp = reinterpret_cast<const T*>(pool_layer + (size_t)h * plane_bytes);
+    const T* Vp = reinterpret_cast<const T*>(pool_layer + ((size_t)H + h) * plane_bytes);
+
+    for (int pg = pg0; pg < pg1; ++pg) {
+        const long long page = page_table[slot * n_pages + pg];
+        if (page < 0) continue;
+        if (page >= n_pages) { if (threadIdx.x == 0) raise_status(status, FPKV_STATUS_BAD_PAGE); continue; }
+        if (p2l[slot * n_pages + page] < 0) continue;
+        long long n_here = n_keys - (long long)pg * P;
+        if (n_here > P) n_here = P;
+        for (int t = warp; t < n_here; t += kPortableWarps) {
+            const size_t off = ((size_t)page * P + t) * D + lane * E;
+            float s = 0.f;
+#pragma unroll
+            for (int e = 0; e < E; ++e) s += qv[e] * ElemTraits<T>::to_float(Kp[off + e]);
+#pragma unroll
+            for (int o = 16; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
+            const float m_new = fmaxf(m, s);
+            const float alpha = exp2f(m - m_new);          // m = -inf -> 0
+            const float pr = exp2f(s - m_new);
+            l = l * alpha + pr;
+#pragma unroll
+            for (int e = 0; e < E; ++e) acc[e] = acc[e] * alpha + pr * ElemTraits<T>::to_float(Vp[off + e]);
+            m = m_new;
+        }
+    }
+    if (lane == 0) { sm_m[warp] = m; sm_l[warp] = l; }
+#pragma unroll
+    for (int e = 0; e < E; ++e) sm_acc[warp][lane * E + e] = acc[e];
+    __syncthreads();
+    float M = -INFINITY;
+#pragma unroll
+    for (int w = 0; w < kPortableWarps; ++w) M = fmaxf(M, sm_m[w]);
+    float* dst = ws + ((size_t)row * S + split) * (D + 2);
+    for (int d = threadIdx.x; d < D; d += blockDim.x) {
+        float o = 0.f;
+#pragma unroll
+        for (int w = 0; w < kPortableWarps; ++w)
+            if (sm_m[w] != -INFINITY) o += sm_acc[w][d] * exp2f(sm_m[w] - M);
+        dst[2 + d] = o;
+    }
+    if (threadIdx.x == 0) {
+        float L = 0.f;
+#pragma unroll
+        for (int w = 0; w < kPortableWarps; ++w)
+            if (sm_m[w] != -INFINITY) L += sm_l[w] * exp2f(sm_m[w] - M);
+        dst[0] = M; dst[1] = L;
+    }
+}
+
+// Merge S partials of each (b, hq) row: out = sum_s acc_s 2^(m_s - M) / L.
+template <typename T, int D>
+__global__ void __launch_bounds__(D)
+decode_portable_merge_kernel(const float* __restrict__ ws, int S, T* __restrict__ out, float* __restrict__ lse)
+{
+    const int row = blockIdx.x, d = threadIdx.x;
+    const float* src = ws + (size_t)row * S * (D + 2);
+    float M = -INFINITY;
+    for (int s = 0; s < S; ++s) M = fmaxf(M, src[s * (D + 2)]);
+    float L = 0.f, o = 0.f;
+    for (int s = 0; s < S; ++s) {
+        const float ms = src[s * (D + 2)];
+        if (ms == -INFINITY) continue;
+        const float w = exp2f(ms - M);
+        L += src[s * (D + 2) + 1] * w;
+        o += src[s * (D + 2) + 2 + d] * w;
+    }
+    out[(size_t)row * D + d] = ElemTraits<T>::from_float(L > 0.f ? o / L : 0.f);
+    if (d == 0) lse[row] = L > 0.f ? (M + log2f(L)) * kLn2 : -INFINITY;
+}
+
+size_t decode_portable_workspace_bytes(int B, int Hq, int D) {
+    return (size_t)B * Hq * kPortableMaxSplits * (D + 2) * sizeof(float);
+}
+
+template <typename T, int D, typename PosT>
+static int launch_typed(const PoolView& pv, int layer, void* out, float* lse, const void* q,
+                        long long q_stride_b, long long q_stride_h, const int64_t* batch_idx,
+                        const void* pos, int B, int Hq, float sm_scale, void* workspace,
+                        int32_t* status, cudaStream_t stream)
+{
+    const int S = portable_splits(B, Hq);
+    dim3 grid(B * Hq, S);
+    decode_portable_kernel<T, D, PosT><<<grid, kPortableWarps * 32, 0, stream>>>(
+        pv.plane(layer, 0, 0), pv.plane_bytes(), pv.H, pv.page_table, pv.p2l, pv.n_pages, pv.max_batch, pv.P,
+        (const T*)q, q_stride_b, q_stride_h, batch_idx, (const PosT*)pos, Hq, sm_scale * kLog2e,
+        (float*)workspace, status);
+    if (cudaGetLastError() != cudaSuccess) return FPKV_ELAUNCH;
+    decode_portable_merge_kernel<T, D><<<B * Hq, D, 0, stream>>>((const float*)workspace, S, (T*)out, lse);
+    return cudaGetLastError() == cudaSuccess ? FPKV_OK : FPKV_ELAUNCH;
+}
+
+template <typename T, int D>
+static int launch_pos(const PoolView& pv, int layer, void* out, float* lse, const void* q, long long qsb,
+                      long long qsh, const int64_t* bi, const void* pos, int pos_type, int B, int Hq,
+                      float sc, void* ws, int32_t* st, cudaStream_t s)
+{
+    return pos_type == FPKV_I32
+        ? launch_typed<T, D, int32_t>(pv, layer, out, lse, q, qsb, qsh, bi, pos, B, Hq, sc, ws, st, s)
+        : launch_typed<T, D, int64_t>(pv, layer, out, lse, q, qsb, qsh, bi, pos, B, Hq, sc, ws, st, s);
+}
+
+int launch_decode_portable(const PoolView& pv, int layer, void* out, float* lse, const void* q,
+                           long long qsb, long long qsh, const int64_t* bi, const void* pos, int pos_type,
+                           int B, int Hq, float sc, void* ws, int32_t* st, cudaStream_t s)
+{
+    if (B == 0) return FPKV_OK;
+#define FPKV_DISPATCH(T)                                                                              \
+    return pv.D == 64 ? launch_pos<T, 64>(pv, layer, out, lse, q, qsb, qsh, bi, pos, pos_type, B, Hq, sc, ws, st, s) \
+                      : launch_pos<T, 128>(pv, layer, out, lse, q, qsb, qsh, bi, pos, pos_type, B, Hq, sc, ws, st, s)
+    switch (pv.dtype) {
+        case FPKV_F32:  FPKV_DISPATCH(float);
+        case FPKV_BF16: FPKV_DISPATCH(__nv_bfloat16);
+        case FPKV_F16:  FPKV_DISPATCH(__half);
+    }
+#undef FPKV_DISPATCH
+    return FPKV_EDTYPE;
+}
+
+}  // namespace fpkv

@@ -1,0 +1,75 @@
+"""ctypes binding of libfpkv.so (the C ABI declared in include/fpkv.h).
+
+There is no fallback: if the shared library has not been built the import
+fails with instructions, and every compute entry point needs CUDA tensors.
+"""
+
+from __future__ import annotations
+
+import ctypes
+import os
+
+_HERE = os.path.dirname(os.path.abspath(__file__))
+LIB_PATH = os.path.join(_HERE, "libfpkv.so")
+
+FPKV_F32, FPKV_BF16, FPKV_F16 = 0, 1, 2
+FPKV_I32, FPKV_I64 = 0, 1
+DECODE_AUTO, DECODE_PORTABLE, DECODE_TMA = 0, 1, 2
+STATUS_BAD_SLOT, STATUS_BAD_POS, STATUS_BAD_PAGE, STATUS_TIMEOUT = 1, 2, 4, 8
+
+# every symbol include/fpkv.h declares
+EXPORTS = ("fpkv_version", "fpkv_strerror", "fpkv_append_decode", "fpkv_append_packed", "fpkv_gather",
+           "fpkv_decode_workspace_bytes", "fpkv_decode_attn")
+
+
+class FpkvPool(ctypes.Structure):
+    """struct fpkv_pool"""
+    _fields_ = [("data", ctypes.c_void_p), ("page_table", ctypes.c_void_p),
+                ("physical_to_logical", ctypes.c_void_p),
+                ("num_layers", ctypes.c_int32), ("n_heads", ctypes.c_int32), ("n_pages", ctypes.c_int32),
+                ("page_size", ctypes.c_int32), ("head_dim", ctypes.c_int32), ("max_batch_size", ctypes.c_int32),
+                ("dtype", ctypes.c_int32), ("reserved_", ctypes.c_int32)]
+
+
+class FpkvError(RuntimeError):
+    def __init__(self, code, where):
+        self.code = code
+        super().__init__(f"{where}: {strerror(code)} (fpkv code {code})")
+
+
+def _load():
+    if not os.path.exists(LIB_PATH):
+        raise ImportError(
+            f"{LIB_PATH} is missing: build it with `python falcon-perception_b200/build.py` "
+            "(nvcc, sm_100a). fpkv has no CPU or PyTorch fallback.")
+    lib = ctypes.CDLL(LIB_PATH)
+    vp, i32, i64, f32 = ctypes.c_void_p, ctypes.c_int32, ctypes.c_int64, ctypes.c_float
+    pool = ctypes.POINTER(FpkvPool)
+    lib.fpkv_version.restype = ctypes.c_int
+    lib.fpkv_version.argtypes = []
+    lib.fpkv_strerror.restype = ctypes.c_char_p
+    lib.fpkv_strerror.argtypes = [ctypes.c_int]
+    lib.fpkv_append_decode.restype = ctypes.c_int
+    lib.fpkv_append_decode.argtypes = [pool, i32, vp, vp, i32, vp, i64, i64, vp, i64, i64, i32, vp, vp]
+    lib.fpkv_append_packed.restype = ctypes.c_int
+    lib.fpkv_append_packed.argtypes = [pool, i32, vp, vp, i32, vp, i64, i64, vp, i64, i64, i32, vp, vp]
+    lib.fpkv_gather.restype = ctypes.c_int
+    lib.fpkv_gather.argtypes = [pool, i32, i32, i32, vp, vp, vp, vp]
+    lib.fpkv_decode_workspace_bytes.restype = ctypes.c_int
+    lib.fpkv_decode_workspace_bytes.argtypes = [pool, i32, i32, ctypes.POINTER(ctypes.c_size_t)]
+    lib.fpkv_decode_attn.restype = ctypes.c_int
+    lib.fpkv_decode_attn.argtypes = [pool, i32, vp, vp, vp, i64, i64, vp, vp, i32, i32, i32, f32, vp,
+                                     ctypes.c_size_t, i32, vp, vp]
+    return lib
+
+
+lib = _load()
+
+
+def strerror(code: int) -> str:
+    return lib.fpkv_strerror(int(code)).decode()
+
+
+def check(code: int, where: str) -> None:
+    if code != 0:
+        raise FpkvError(code, where)

@@ -1,0 +1,74 @@
+"""Mask descriptors for the paged attention kernels.
+
+The reference builds FlexAttention ``BlockMask`` objects (sparsity metadata
+plus a ``mask_mod`` closure, ``falcon_perception/attention.py:22-102``) and
+converts them to physical page ids every decode step
+(``falcon_perception/paged_attention.py:234-301``).  The kernels here derive
+the same visibility rule from the index tensors themselves, so a mask is just
+a small record of those tensors.
+"""
+
+from __future__ import annotations
+
+from dataclasses import dataclass
+
+import torch
+from torch import Tensor
+
+
+@dataclass
+class CausalDecodeMask:
+    """Logical causal mask over ``B`` slots and ``L`` positions with
+    ``page_size`` blocks: what ``create_causal_blockmask`` returns.  Row b at
+    position p sees keys 0..p of its own slot."""
+    B: int
+    L: int
+    page_size: int
+
+    @property
+    def BLOCK_SIZE(self):
+        return (self.page_size, self.page_size)
+
+    @property
+    def seq_lengths(self):
+        return (self.L, self.L)
+
+    def for_step(self, batch_idx: Tensor, input_pos: Tensor) -> "DecodeStepMask":
+        """The slice the reference engine takes each decode step
+        (``paged_inference.py:783-826``)."""
+        return DecodeStepMask(batch_idx, input_pos, self.page_size)
+
+
+@dataclass
+class DecodeStepMask:
+    """Decode-step mask: slot and position of every row of the batch."""
+    batch_idx: Tensor
+    input_pos: Tensor
+    page_size: int
+
+
+@dataclass
+class PrefillMask:
+    """Packed-row prefill mask (``paged_attention.py:343-362``): query t sees
+    key u iff both lie in the same image span (``img_id`` equal and non-zero)
+    or u <= t within the same document (``doc_id`` equal)."""
+    doc_id: Tensor      # (L,) int32 slot of each token, 0 for pads
+    img_id: Tensor      # (L,) int32 running image number, 0 outside image spans
+    BLOCK_SIZE: int = 128
+
+    @property
+    def L(self):
+        return int(self.doc_id.shape[0])
+
+
+def image_span_ids(input_ids: Tensor, soi_id: int, eoi_id: int) -> Tensor:
+    """Per-token image number of a (1,L) or (L,) id row: tokens from an
+    image-start token (inclusive) to the next end-of-image token (exclusive)
+    carry the running count of image starts, all others 0
+    (``falcon_perception/attention.py:79-88``).  Integer prefix sums on the
+    tensor's own device."""
+    ids = input_ids.reshape(-1)
+    n_soi = torch.cumsum(ids == soi_id, dim=0)
+    n_eoi = torch.cumsum(ids == eoi_id, dim=0)
+    inside = (n_soi - n_eoi) > 0
+    return (n_soi * inside).to(torch.int32)

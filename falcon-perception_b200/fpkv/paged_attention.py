@@ -1,0 +1,353 @@
+"""Paged KV cache and paged attention on B200, behind the reference's API.
+
+``PagedKVCache`` keeps the constructor, attributes and methods of the
+reference class (``falcon_perception/paged_attention.py:27-393``): page pool,
+per-slot page table and its inverse, host mirrors, LIFO free lists,
+``allocate / reserve / can_reserve / erase``, ``insert_kv`` with its decode
+and packed-prefill forms, and the mask builders.  The bookkeeping is host
+Python exactly as there; every byte of K/V moves through the CUDA kernels in
+libfpkv.so (append, gather, paged attention).  There is no PyTorch or CPU
+fallback for those: a CPU cache can be built (to exercise the allocator), but
+its data-path methods raise.
+
+Differences a caller has to know about:
+  * ``n_heads`` is the number of heads STORED.  Pass the model's KV heads and
+    skip the reference's ``repeat_kv`` expansion (``model.py:114-115``);
+    attention maps query head hq to stored head hq // (Hq // n_heads).
+  * the mask builders return light records (``fpkv.attention``) instead of
+    FlexAttention ``BlockMask`` objects;
+  * attention is ``paged_attention(...)`` below instead of a ``flex_attention``
+    call on the whole pool.
+"""
+
+from __future__ import annotations
+
+import ctypes
+import math
+
+import torch
+from torch import Tensor
+
+from . import _lib
+from .attention import CausalDecodeMask, DecodeStepMask, PrefillMask, image_span_ids
+from .kv_cache import KVCacheBase
+
+_DTYPES = {torch.float32: _lib.FPKV_F32, torch.bfloat16: _lib.FPKV_BF16, torch.float16: _lib.FPKV_F16}
+
+
+def _cdiv(a: int, b: int) -> int:
+    return int((a + b - 1) // b)
+
+
+def _pos_type(t: Tensor) -> int:
+    if t.dtype == torch.int32:
+        return _lib.FPKV_I32
+    if t.dtype == torch.int64:
+        return _lib.FPKV_I64
+    raise AssertionError("input_pos must be int32 or int64")
+
+
+def _stream(device) -> int:
+    return torch.cuda.current_stream(device).cuda_stream
+
+
+class PagedKVCache(KVCacheBase):
+    """Page pool + page table + free lists; see the module docstring."""
+
+    def __init__(self, n_pages: int, page_size: int, max_batch_size: int, n_heads: int, head_dim: int,
+                 num_layers: int, dtype: torch.dtype, device: str | torch.device = "cuda"):
+        assert dtype in _DTYPES, "dtype must be float32, bfloat16 or float16"
+        self.n_pages = n_pages
+        self.page_size = page_size
+        self.max_batch_size = max_batch_size
+        self.n_heads = n_heads
+        self.head_dim = head_dim
+        self.num_layers = num_layers
+        self.dtype = dtype
+        self.device = device
+        self._dev = torch.device(device)
+
+        # [slot, logical page] -> physical page; page 0 and slot 0 are reserved (no-op targets)
+        self.page_table = torch.full((max_batch_size, n_pages), -1, dtype=torch.int64, device=device)
+        self.page_table[0, :] = 0
+        self.page_table_cpu = [[] for _ in range(max_batch_size)]
+        self.capacity = [0 for _ in range(max_batch_size)]
+        self.free_pages = list(reversed(range(1, n_pages)))
+        self.free_batch_idx = list(reversed(range(1, max_batch_size)))
+        # [slot, physical page] -> logical page
+        self.physical_to_logical = torch.full((max_batch_size, n_pages), -1, dtype=torch.int64, device=device)
+
+        self.kv_shape = (num_layers, 2, 1, n_heads, n_pages * page_size, head_dim)
+        self.kv_cache = torch.zeros(self.kv_shape, dtype=dtype, device=device)
+
+        self._pool = _lib.FpkvPool(self.kv_cache.data_ptr(), self.page_table.data_ptr(),
+                                   self.physical_to_logical.data_ptr(), num_layers, n_heads, n_pages,
+                                   page_size, head_dim, max_batch_size, _DTYPES[dtype], 0)
+        self._status = torch.zeros(1, dtype=torch.int32, device=device)
+        self._workspace = None
+        self.decode_kernel = _lib.DECODE_AUTO       # DECODE_PORTABLE / DECODE_TMA force one kernel
+
+    # ------------------------------------------------------------------ helpers
+    def _require_cuda(self, *tensors):
+        if self._dev.type != "cuda":
+            raise RuntimeError("fpkv moves K/V only with its CUDA kernels; this cache lives on "
+                               f"{self._dev} and has no CPU path")
+        for t in tensors:
+            assert t.is_cuda, "tensor must be on the cache's CUDA device"
+
+    def _status_ptr(self):
+        return self._status.data_ptr()
+
+    def check_status(self) -> int:
+        """Read and clear the device status word (one synchronising copy).
+        Raises if a kernel met an out-of-range index or a bounded wait ran out."""
+        bits = int(self._status.item())
+        if bits:
+            self._status.zero_()
+            names = [n for b, n in ((1, "bad slot"), (2, "bad position"), (4, "bad page id"),
+                                    (8, "on-chip wait timed out")) if bits & b]
+            raise RuntimeError("fpkv kernel status: " + ", ".join(names))
+        return bits
+
+    # ---------------------------------------------------------------- insert_kv
+    def insert_kv(self, layer_id: int, k: Tensor, v: Tensor, input_pos: Tensor | None = None,
+                  batch_idx: Tensor | None = None, **kwargs):
+        del kwargs
+        assert input_pos is not None, "input_pos is required for paged kv cache"
+        assert batch_idx is not None, "batch_idx is required for paged kv cache"
+        assert batch_idx.ndim in [1, 2], "batch_idx must be 1D (decode) or 2D (prefill 1xL)"
+        if batch_idx.ndim == 1:
+            return self.assign(layer_id, batch_idx, input_pos, k, v)
+        return self.assign_prefill_no_paging(layer_id, k, v, input_pos, batch_idx)
+
+    # ---------------------------------------------------------------- allocator
+    def can_reserve(self, size: int, batch_idx_int: int | None = None) -> bool:
+        """Host-only check: room for a new request, or for growing an existing one."""
+        if batch_idx_int is None:
+            return self.num_free_pages * self.page_size >= size and len(self.free_batch_idx) > 0
+        return self.reserve(batch_idx_int, None, size, dry_run=True)
+
+    def allocate(self) -> int:
+        slot = self.free_batch_idx.pop()
+        self.capacity[slot] = 0
+        self.physical_to_logical[slot, :] = -1
+        self.page_table[slot, :] = -1
+        return slot
+
+    @property
+    def num_free_pages(self) -> int:
+        return len(self.free_pages)
+
+    def reserve(self, batch_idx_int: int, batch_idx: Tensor | None, seq_len: int, dry_run: bool = False) -> bool:
+        """Grow slot ``batch_idx_int`` to hold at least ``seq_len`` tokens.
+        ``batch_idx`` (the slot as a one-element tensor) is accepted for
+        signature compatibility and not needed."""
+        if seq_len <= self.capacity[batch_idx_int]:
+            return True
+        n_new = _cdiv(seq_len - self.capacity[batch_idx_int], self.page_size)
+        can = bool(n_new <= self.num_free_pages)
+        if dry_run:
+            return can
+        if not can:
+            raise RuntimeError(
+                f"Cannot reserve {n_new} pages for a sequence of length {seq_len} "
+                f"in batch {batch_idx_int}. Only {self.num_free_pages} pages available. "
+                f"Current capacity is {self.capacity[batch_idx_int]} tokens.")
+        start = self.capacity[batch_idx_int] // self.page_size
+        end = start + n_new
+        pages = self.free_pages[-n_new:]
+        pages_t = torch.tensor(pages, dtype=torch.int64)
+        if self._dev.type == "cuda":
+            pages_t = pages_t.pin_memory().to(self._dev, non_blocking=True)
+        self.page_table[batch_idx_int, start:end] = pages_t
+        self.physical_to_logical[batch_idx_int, pages_t] = torch.arange(start, end, device=self.device)
+        self.page_table_cpu[batch_idx_int] += pages
+        self.free_pages = self.free_pages[:-n_new]
+        self.capacity[batch_idx_int] += n_new * self.page_size
+        return True
+
+    def erase(self, batch_idx: int) -> None:
+        self.free_batch_idx.append(batch_idx)
+        self.free_pages.extend(reversed(self.page_table_cpu[batch_idx]))
+        self.page_table_cpu[batch_idx] = []
+        # cleared on the device too, so padding rows and stale slots read "unmapped"
+        self.page_table[batch_idx, :] = -1
+        self.physical_to_logical[batch_idx, :] = -1
+        self.capacity[batch_idx] = 0
+
+    # ------------------------------------------------------------------- append
+    def assign(self, layer_id: int, batch_idx: Tensor, input_pos: Tensor, k_val: Tensor, v_val: Tensor):
+        """Decode append of (B,H,1,D) rows; returns this layer's K and V pool views."""
+        B, H, S, K_D = k_val.shape
+        _, _, _, H_cache, MAX_S, D_cache = self.kv_cache.shape
+        assert H_cache == H, "number of heads must match"
+        assert MAX_S >= S, "cache must have enough space"
+        assert D_cache == K_D, "hidden dim must match"
+        assert v_val.shape == k_val.shape, "k and v must have the same shape"
+        assert S == 1, "decode append takes one token per row"
+        assert input_pos.shape == (B, S), "input_pos must have the same shape as val"
+        assert batch_idx.shape == (B,), "batch_idx must have one dimension only"
+        assert k_val.dtype == self.dtype and v_val.dtype == self.dtype, "dtype must match the pool"
+        self._require_cuda(k_val, v_val, batch_idx, input_pos)
+        if batch_idx.dtype != torch.int64:
+            batch_idx = batch_idx.to(torch.int64)
+        k_val, v_val = self._rows16(k_val), self._rows16(v_val)
+        input_pos = input_pos.reshape(-1)
+        if not input_pos.is_contiguous():
+            input_pos = input_pos.contiguous()
+        _lib.check(_lib.lib.fpkv_append_decode(
+            ctypes.byref(self._pool), layer_id, batch_idx.data_ptr(), input_pos.data_ptr(), _pos_type(input_pos),
+            k_val.data_ptr(), k_val.stride(0), k_val.stride(1), v_val.data_ptr(), v_val.stride(0), v_val.stride(1),
+            B, self._status_ptr(), _stream(self._dev)), "fpkv_append_decode")
+        return self.kv_cache[layer_id, 0], self.kv_cache[layer_id, 1]
+
+    def assign_prefill_no_paging(self, layer_id: int, k_val: Tensor, v_val: Tensor, input_pos: Tensor,
+                                 batch_idx: Tensor):
+        """Packed prefill append of (1,H,L,D) rows with per-token (1,L) slot and
+        position; returns the fresh k, v (prefill attends over them)."""
+        assert batch_idx.ndim == 2, "batch_idx must be a 2D tensor"
+        assert batch_idx.shape[0] == 1, "batch_idx must have batch size 1"
+        assert input_pos.ndim == 2, "input_pos must be a 2D tensor"
+        assert k_val.ndim == 4, "k_val must be a 4D tensor"
+        assert v_val.ndim == 4, "v_val must be a 4D tensor"
+        assert k_val.shape[0] == 1 and k_val.shape[1] == self.n_heads and k_val.shape[3] == self.head_dim
+        assert v_val.shape == k_val.shape and k_val.shape[2] == batch_idx.shape[1] == input_pos.shape[1]
+        assert k_val.dtype == self.dtype and v_val.dtype == self.dtype, "dtype must match the pool"
+        self._require_cuda(k_val, v_val, batch_idx, input_pos)
+        if batch_idx.dtype != torch.int64:
+            batch_idx = batch_idx.to(torch.int64)
+        kk, vv = self._rows16(k_val), self._rows16(v_val)
+        bi, ip = batch_idx.reshape(-1), input_pos.reshape(-1)
+        bi = bi if bi.is_contiguous() else bi.contiguous()
+        ip = ip if ip.is_contiguous() else ip.contiguous()
+        _lib.check(_lib.lib.fpkv_append_packed(
+            ctypes.byref(self._pool), layer_id, bi.data_ptr(), ip.data_ptr(), _pos_type(ip),
+            kk.data_ptr(), kk.stride(1), kk.stride(2), vv.data_ptr(), vv.stride(1), vv.stride(2),
+            kk.shape[2], self._status_ptr(), _stream(self._dev)), "fpkv_append_packed")
+        return k_val, v_val
+
+    def _rows16(self, t: Tensor) -> Tensor:
+        """The kernels read whole head_dim rows with 16-byte accesses through
+        arbitrary outer strides (so the model's permuted views need no copy);
+        only a row that is not contiguous or not 16-byte aligned is repacked."""
+        es = t.element_size()
+        ok = t.stride(-1) == 1 and t.data_ptr() % 16 == 0 and all((s * es) % 16 == 0 for s in t.stride()[:-1])
+        return t if ok else t.contiguous()
+
+    # ------------------------------------------------------------------- gather
+    def gather(self, layer_id: int, slot: int, n_tokens: int):
+        """K and V of logical positions [0, n_tokens) of a slot as two
+        (n_heads, n_tokens, head_dim) tensors read through the page table."""
+        self._require_cuda()
+        k = torch.empty((self.n_heads, n_tokens, self.head_dim), dtype=self.dtype, device=self._dev)
+        v = torch.empty_like(k)
+        _lib.check(_lib.lib.fpkv_gather(ctypes.byref(self._pool), layer_id, slot, n_tokens, k.data_ptr(),
+                                        v.data_ptr(), self._status_ptr(), _stream(self._dev)), "fpkv_gather")
+        return k, v
+
+    # --------------------------------------------------------- decode attention
+    def _get_workspace(self, B: int, Hq: int) -> Tensor:
+        need = ctypes.c_size_t(0)
+        _lib.check(_lib.lib.fpkv_decode_workspace_bytes(ctypes.byref(self._pool), B, Hq, ctypes.byref(need)),
+                   "fpkv_decode_workspace_bytes")
+        if self._workspace is None or self._workspace.numel() < need.value:
+            self._workspace = torch.empty(need.value, dtype=torch.uint8, device=self._dev)
+        return self._workspace
+
+    def decode_attention(self, layer_id: int, q: Tensor, batch_idx: Tensor, input_pos: Tensor,
+                         sm_scale: float | None = None, out: Tensor | None = None, lse: Tensor | None = None):
+        """One query token per row against keys 0..input_pos[b] of slot
+        batch_idx[b].  q (B,Hq,1,D) -> out (B,Hq,1,D) in q's dtype, lse (B,Hq,1)
+        fp32.  Call after ``insert_kv`` of the same step, as the model does."""
+        B, Hq, S, D = q.shape
+        assert S == 1, "decode attention takes one query token per row"
+        assert D == self.head_dim and Hq % self.n_heads == 0, "head layout must match the pool"
+        assert q.dtype == self.dtype, "q dtype must match the pool"
+        assert batch_idx.shape == (B,), "batch_idx must have one dimension only"
+        input_pos = input_pos.reshape(-1)
+        assert input_pos.shape == (B,), "input_pos must have one entry per row"
+        self._require_cuda(q, batch_idx, input_pos)
+        if batch_idx.dtype != torch.int64:
+            batch_idx = batch_idx.to(torch.int64)
+        if not input_pos.is_contiguous():
+            input_pos = input_pos.contiguous()
+        q = self._rows16(q)
+        if out is None:
+            out = torch.empty((B, Hq, 1, D), dtype=q.dtype, device=q.device)
+        if lse is None:
+            lse = torch.empty((B, Hq, 1), dtype=torch.float32, device=q.device)
+        ws = self._get_workspace(B, Hq)
+        scale = (1.0 / math.sqrt(D)) if sm_scale is None else float(sm_scale)
+        _lib.check(_lib.lib.fpkv_decode_attn(
+            ctypes.byref(self._pool), layer_id, out.data_ptr(), lse.data_ptr(), q.data_ptr(), q.stride(0),
+            q.stride(1), batch_idx.data_ptr(), input_pos.data_ptr(), _pos_type(input_pos), B, Hq, scale,
+            ws.data_ptr(), ws.numel(), int(self.decode_kernel), self._status_ptr(), _stream(self._dev)),
+            "fpkv_decode_attn")
+        return out, lse
+
+    # ------------------------------------------------------------ mask builders
+    def create_causal_blockmask(self, B: int, L: int) -> CausalDecodeMask:
+        """Logical causal mask for decode steps with page_size blocks."""
+        return CausalDecodeMask(B, L, self.page_size)
+
+    def convert_logical_block_mask(self, block_mask, batch_idx: Tensor | None = None):
+        """Logical -> physical conversion.  The kernels walk the page table
+        themselves, so the step mask only has to carry slot and position; a
+        mask whose column block differs from page_size is rejected as in the
+        reference."""
+        if isinstance(block_mask, CausalDecodeMask):
+            raise RuntimeError("slice the causal mask for this step first: mask.for_step(batch_idx, input_pos)")
+        if block_mask.page_size != self.page_size:
+            raise RuntimeError(
+                f"Expect block_mask has the same column block size as page_size"
+                f"but got size={block_mask.page_size} and size={self.page_size}")
+        if batch_idx is not None:
+            assert batch_idx.ndim == 1, "batch_idx must be a 1D tensor"
+            assert batch_idx.shape[0] == block_mask.batch_idx.shape[0], \
+                "batch_idx must have the same shape as block_mask"
+            assert batch_idx.shape[0] <= self.max_batch_size, \
+                "batch_idx must be less than or equal to max_batch_size"
+            return DecodeStepMask(batch_idx, block_mask.input_pos, self.page_size)
+        return block_mask
+
+    def get_logical_kv_idx(self, physical_batch_idx: Tensor, physical_kv_idx: Tensor, batch_idx: Tensor):
+        """Physical token address -> (is_valid, logical position) for the slot
+        of each row; index arithmetic only, on the tables' device."""
+        slot = batch_idx[physical_batch_idx]
+        page = physical_kv_idx // self.page_size
+        logical_page = self.physical_to_logical[slot, page]
+        logical = logical_page * self.page_size + physical_kv_idx % self.page_size
+        return logical_page >= 0, logical.clamp(min=0)
+
+    def get_mask_mod(self, mask_mod, batch_idx: Tensor):
+        """Wrap a logical ``mask_mod(b, h, q_idx, kv_idx)`` so that it takes
+        physical key addresses."""
+        def new_mask_mod(b, h, q_idx, physical_kv_idx):
+            ok, logical = self.get_logical_kv_idx(b, physical_kv_idx, batch_idx)
+            inner = True if mask_mod is None else mask_mod(b, h, q_idx, logical)
+            return ok & inner
+        return new_mask_mod
+
+    def create_prefill_blockmask(self, batch_idx: Tensor, input_ids: Tensor, soi_id: int, eoi_id: int,
+                                 BLOCK_SIZE: int = 128) -> PrefillMask:
+        """Document-causal OR same-image mask of a packed prefill row."""
+        assert batch_idx.ndim == 2 and batch_idx.shape[0] == 1
+        doc = batch_idx.reshape(-1).to(torch.int32)
+        return PrefillMask(doc, image_span_ids(input_ids, soi_id, eoi_id), BLOCK_SIZE)
+
+
+def paged_attention(q: Tensor, kv_cache: PagedKVCache, layer_id: int, batch_idx: Tensor, input_pos: Tensor,
+                    mask=None, sm_scale: float | None = None):
+    """Attention entry that replaces the reference's ``flex_fn(xq, xk, xv,
+    block_mask=..., return_aux=AuxRequest(lse=True))`` call
+    (``falcon_perception/model.py:156-162``).  Returns ``(out, lse)`` with out
+    shaped and typed like q and lse (B,Hq,S) fp32.
+
+    Decode: q (B,Hq,1,D), batch_idx (B,), input_pos (B,) or (B,1); ``mask`` may
+    be the step's DecodeStepMask (its tensors are used when given).
+    """
+    if batch_idx.ndim == 1:
+        if isinstance(mask, DecodeStepMask):
+            batch_idx, input_pos = mask.batch_idx, mask.input_pos
+        return kv_cache.decode_attention(layer_id, q, batch_idx, input_pos, sm_scale)
+    raise NotImplementedError("prefill attention entry is not wired yet")

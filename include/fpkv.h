@@ -1,0 +1,174 @@
+/*
+ * fpkv.h - C ABI of libfpkv.so: the paged KV-cache hot path of
+ * Falcon-Perception (page pool, page table, K/V append, paged decode and
+ * prefill attention) as CUDA kernels for sm_100a.
+ *
+ * The reference project is pure Python and has no FFI of its own; the
+ * boundary it offers is two Python call sites.  Every entry point below names
+ * the reference code it replaces (path:line within the reference project).
+ *
+ * Conventions
+ *  - Every pointer marked "device" is device memory owned by the caller (in
+ *    practice a torch tensor's data_ptr()).  Except where an entry point's
+ *    comment says otherwise, the library never allocates, frees or keeps
+ *    device memory and holds no mutable global state, so calls on different
+ *    streams are independent.
+ *  - `stream` is a cudaStream_t passed as void*.  Kernels are enqueued on it
+ *    and the call returns without synchronising, so every entry point may be
+ *    captured in a CUDA graph unless its comment says otherwise.
+ *  - Return value: 0 (FPKV_OK) or a negative FPKV_E* code; fpkv_strerror()
+ *    gives the text.  Arguments are validated on the host before any launch.
+ *  - `status`, where present, is an optional device int32 word (may be NULL).
+ *    Kernels OR FPKV_STATUS_* bits into it when they meet an out-of-range
+ *    slot / position / page id or when a bounded wait runs out; they never
+ *    trap and never spin without a limit.  The caller zeroes and reads it.
+ *  - Strides are in ELEMENTS.  The last (head_dim) dimension is contiguous
+ *    and every row starts on a 16-byte boundary.
+ */
+#ifndef FPKV_H_
+#define FPKV_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#if defined(__GNUC__)
+#define FPKV_API __attribute__((visibility("default")))
+#else
+#define FPKV_API
+#endif
+
+#define FPKV_OK          0
+#define FPKV_EINVAL     -1   /* NULL pointer, negative size, bad enum          */
+#define FPKV_ESHAPE     -2   /* unsupported head_dim / page_size / head ratio  */
+#define FPKV_EALIGN     -3   /* pointer or stride not 16-byte aligned          */
+#define FPKV_EARCH      -4   /* device is not sm_100                           */
+#define FPKV_ELAUNCH    -5   /* CUDA reported an error at launch               */
+#define FPKV_EWORKSPACE -6   /* workspace too small                            */
+#define FPKV_EDTYPE     -7   /* dtype not supported by this entry point        */
+
+#define FPKV_STATUS_BAD_SLOT   1u   /* batch_idx outside [0, max_batch_size)   */
+#define FPKV_STATUS_BAD_POS    2u   /* position outside the page table         */
+#define FPKV_STATUS_BAD_PAGE   4u   /* page id outside [0, n_pages)            */
+#define FPKV_STATUS_TIMEOUT    8u   /* a bounded on-chip wait ran out          */
+
+typedef enum { FPKV_F32 = 0, FPKV_BF16 = 1, FPKV_F16 = 2 } fpkv_dtype;
+typedef enum { FPKV_I32 = 0, FPKV_I64 = 1 } fpkv_itype;
+
+/*
+ * The page pool and its tables: the state of the reference's PagedKVCache
+ * (falcon_perception/paged_attention.py:39-74).
+ *   data                 device, (num_layers, 2, 1, n_heads, n_pages*page_size,
+ *                        head_dim) contiguous, i.e. `kv_cache` (:72-74);
+ *                        n_heads is the number of heads STORED (the KV heads).
+ *   page_table           device int64 (max_batch_size, n_pages)   (:58-59)
+ *   physical_to_logical  device int64 (max_batch_size, n_pages)   (:70)
+ */
+typedef struct fpkv_pool {
+    void*          data;
+    const int64_t* page_table;
+    const int64_t* physical_to_logical;
+    int32_t num_layers;
+    int32_t n_heads;
+    int32_t n_pages;
+    int32_t page_size;
+    int32_t head_dim;
+    int32_t max_batch_size;
+    int32_t dtype;              /* fpkv_dtype */
+    int32_t reserved_;
+} fpkv_pool;
+
+/* Library version (major*10000 + minor*100 + patch). */
+FPKV_API int fpkv_version(void);
+
+/* Text for a return code; never NULL. */
+FPKV_API const char* fpkv_strerror(int code);
+
+/*
+ * Decode append: one new K/V row per sequence, written through the page
+ * table.  Replaces PagedKVCache.assign (paged_attention.py:184-232):
+ *   page = max(page_table[batch_idx[b], input_pos[b] / page_size], 0)
+ *   pool[layer, 0|1, 0, h, page*page_size + input_pos[b] % page_size, :] = k|v[b, h, 0, :]
+ * batch_idx  device int64 (B);  input_pos device (B) of `pos_type`.
+ * k, v       device (B, n_heads, 1, head_dim) of the pool's dtype with
+ *            element strides k_stride_b / k_stride_h (resp. v_*).
+ */
+FPKV_API int fpkv_append_decode(const fpkv_pool* pool, int32_t layer,
+                       const int64_t* batch_idx, const void* input_pos, int32_t pos_type,
+                       const void* k, int64_t k_stride_b, int64_t k_stride_h,
+                       const void* v, int64_t v_stride_b, int64_t v_stride_h,
+                       int32_t B, int32_t* status, void* stream);
+
+/*
+ * Packed prefill append: L tokens of one packed row, each with its own slot
+ * and position.  Replaces PagedKVCache.assign_prefill_no_paging
+ * (paged_attention.py:364-393).  A negative page id is a caller error there
+ * (the engine reserves first, paged_inference.py:1198-1204); here such a row
+ * goes to reserved page 0 and FPKV_STATUS_BAD_PAGE is raised.
+ * batch_idx, input_pos  device (L) (the reference's (1,L) tensors).
+ * k, v                  device (1, n_heads, L, head_dim); strides over the
+ *                       head and token dimensions.
+ */
+FPKV_API int fpkv_append_packed(const fpkv_pool* pool, int32_t layer,
+                       const int64_t* batch_idx, const void* input_pos, int32_t pos_type,
+                       const void* k, int64_t k_stride_h, int64_t k_stride_t,
+                       const void* v, int64_t v_stride_h, int64_t v_stride_t,
+                       int32_t L, int32_t* status, void* stream);
+
+/*
+ * Gather: read logical positions [0, n_tokens) of one slot back through the
+ * page table into contiguous (n_heads, n_tokens, head_dim) buffers.  The
+ * inverse of the two appends; what the reference's attention kernels do
+ * implicitly through kv_indices (paged_attention.py:267-301).  Positions whose
+ * page is unmapped read as zeros.
+ */
+FPKV_API int fpkv_gather(const fpkv_pool* pool, int32_t layer, int32_t slot, int32_t n_tokens,
+                void* k_out, void* v_out, int32_t* status, void* stream);
+
+/*
+ * Bytes of scratch fpkv_decode_attn needs for a batch of B rows with n_q_heads
+ * query heads (an upper bound that does not depend on the context lengths).
+ */
+FPKV_API int fpkv_decode_workspace_bytes(const fpkv_pool* pool, int32_t B, int32_t n_q_heads,
+                                size_t* bytes);
+
+/*
+ * Paged decode attention: one query token per row against logical keys
+ * 0..input_pos[b] of slot batch_idx[b].  Replaces, for S_q == 1, the decode
+ * mask pipeline plus FlexAttention call of the reference:
+ * PagedInferenceEngine.get_decoding_block_mask (paged_inference.py:783-826),
+ * PagedKVCache.convert_logical_block_mask / get_mask_mod
+ * (paged_attention.py:234-333) and compiled_flex_attn_decode
+ * (attention.py:17, called at model.py:156-162).
+ *   score = (q . k) * sm_scale, softmax in fp32,
+ *   out (B, n_q_heads, 1, head_dim) contiguous, dtype of q,
+ *   lse (B, n_q_heads, 1) fp32, natural log; a row with no visible key
+ *   (slot 0, unmapped pages) gives out = 0, lse = -inf.
+ * Query head hq reads stored head hq / (n_q_heads / pool->n_heads).
+ * q: device (B, n_q_heads, 1, head_dim) with element strides q_stride_b/_h.
+ * workspace: device, at least fpkv_decode_workspace_bytes() bytes, 16-byte
+ * aligned; contents need not be initialised and are not kept between calls.
+ * flags: FPKV_DECODE_AUTO picks the TMA + tensor-core kernel when the shape is
+ * in its range (16-bit pool, page_size 128, head_dim 64/128, 1/2/4/8 query
+ * heads per stored head) and the portable CUDA-core kernel otherwise;
+ * FPKV_DECODE_PORTABLE / FPKV_DECODE_TMA force one (the latter returns
+ * FPKV_ESHAPE outside its range).
+ */
+#define FPKV_DECODE_AUTO     0
+#define FPKV_DECODE_PORTABLE 1
+#define FPKV_DECODE_TMA      2
+FPKV_API int fpkv_decode_attn(const fpkv_pool* pool, int32_t layer,
+                     void* out, float* lse,
+                     const void* q, int64_t q_stride_b, int64_t q_stride_h,
+                     const int64_t* batch_idx, const void* input_pos, int32_t pos_type,
+                     int32_t B, int32_t n_q_heads, float sm_scale,
+                     void* workspace, size_t workspace_bytes, int32_t flags,
+                     int32_t* status, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif  /* FPKV_H_ */

@@ -1,0 +1,72 @@
+"""CPU: the C-ABI library loads, exports what include/fpkv.h declares, and
+validates arguments on the host before touching a device."""
+
+import ctypes
+import os
+import re
+
+import torch
+
+from fpkv import _lib
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+def declared_symbols():
+    text = open(os.path.join(ROOT, "include", "fpkv.h")).read()
+    return sorted(set(re.findall(r"FPKV_API\s+[\w\s\*]+?\b(fpkv_\w+)\s*\(", text)))
+
+
+def test_header_symbols_are_exported():
+    names = declared_symbols()
+    assert len(names) >= 7
+    assert sorted(_lib.EXPORTS) == names, "the ctypes binding must cover exactly the header's entry points"
+    raw = ctypes.CDLL(_lib.LIB_PATH)
+    for n in names:
+        assert getattr(raw, n) is not None
+
+
+def test_version_and_strerror():
+    assert _lib.lib.fpkv_version() >= 100
+    assert _lib.strerror(0) == "ok"
+    for code in range(-7, 0):
+        assert "unknown" not in _lib.strerror(code)
+    assert "unknown" in _lib.strerror(-99)
+
+
+def _pool(**kw):
+    buf = torch.zeros(64, dtype=torch.int64)       # any 16-byte aligned host memory: never dereferenced
+    d = dict(data=buf.data_ptr(), page_table=buf.data_ptr(), physical_to_logical=buf.data_ptr(), num_layers=1,
+             n_heads=2, n_pages=4, page_size=16, head_dim=64, max_batch_size=3, dtype=_lib.FPKV_BF16, reserved_=0)
+    d.update(kw)
+    return _lib.FpkvPool(**d), buf
+
+
+def test_validation_happens_before_any_launch():
+    L = _lib.lib
+    p, buf = _pool()
+    ptr = buf.data_ptr()
+    call = lambda pool, **kw: L.fpkv_append_decode(ctypes.byref(pool), kw.get("layer", 0), kw.get("bi", ptr), ptr,
+                                                   kw.get("pt", 0), kw.get("k", ptr), kw.get("sb", 128), 64, ptr,
+                                                   128, 64, kw.get("B", 2), None, None)
+    assert L.fpkv_append_decode(None, 0, ptr, ptr, 0, ptr, 128, 64, ptr, 128, 64, 2, None, None) == -1
+    assert call(_pool(data=0)[0]) == -1                      # null pool data
+    assert call(_pool(dtype=9)[0]) == -7                     # bad dtype
+    assert call(_pool(head_dim=96)[0]) == -2                 # unsupported head_dim
+    assert call(_pool(page_size=24)[0]) == -2                # page_size not a multiple of 16
+    assert call(p, layer=1) == -1                            # layer out of range
+    assert call(p, B=-1) == -1
+    assert call(p, pt=5) == -1                               # bad position type
+    assert call(p, bi=0) == -1                               # null batch_idx
+    assert call(p, k=ptr + 2) == -3                          # misaligned rows
+    assert call(p, sb=100) == -3                             # stride not a multiple of 16 bytes
+    assert call(p, B=0) == 0                                 # empty batch is a no-op
+    need = ctypes.c_size_t(0)
+    assert L.fpkv_decode_workspace_bytes(ctypes.byref(p), 4, 3, ctypes.byref(need)) == -2   # 3 % 2 heads
+    assert L.fpkv_decode_workspace_bytes(ctypes.byref(p), 4, 4, ctypes.byref(need)) == 0 and need.value > 0
+    # decode: workspace too small is caught on the host
+    assert L.fpkv_decode_attn(ctypes.byref(p), 0, ptr, ptr, ptr, 256, 64, ptr, ptr, 0, 2, 4, 0.125, ptr, 16, 0,
+                              None, None) == -6
+    if not torch.cuda.is_available():
+        # valid arguments but no device: refused, never a silent CPU path
+        assert call(p) == -4

@@ -1,0 +1,169 @@
+"""GPU: paged decode attention through the C ABI against the golden vectors
+(reference, fp32) and the CPU oracle, for both kernels."""
+
+import numpy as np
+import pytest
+import torch
+
+from fpkv import _lib, workloads as wl
+from fpkv.paged_attention import PagedKVCache, paged_attention
+from oracle import paged_kv_oracle as orc
+from helpers import assert_attention_close, golden, oracle_from_case, product_from_case
+from test_oracle_golden import DECODE_CASES
+
+pytestmark = pytest.mark.gpu
+
+KERNELS = {"portable": _lib.DECODE_PORTABLE, "tma": _lib.DECODE_TMA}
+
+
+def tma_takes(case):
+    return case.dtype in (torch.bfloat16, torch.float16) and case.P == 128 and case.Hq // case.Hkv in (1, 2, 4, 8)
+
+
+@pytest.mark.parametrize("kernel", sorted(KERNELS))
+@pytest.mark.parametrize("name", sorted(DECODE_CASES))
+def test_decode_against_reference_golden(name, kernel):
+    make, pads = DECODE_CASES[name]
+    case = make()
+    if kernel == "tma" and not tma_takes(case):
+        pytest.skip("shape outside the TMA kernel's range (served by the portable kernel)")
+    g = golden(name)
+    c, slots, bidx, pos, k, v, q = product_from_case(case, pad_rows=pads)
+    c.decode_kernel = KERNELS[kernel]
+    out, lse = paged_attention(q, c, 0, bidx, pos)
+    assert out.dtype == q.dtype and lse.dtype == torch.float32
+    assert tuple(out.shape) == tuple(q.shape) and tuple(lse.shape) == tuple(q.shape[:3])
+    assert_attention_close(out, lse, g["out"], g["lse"], f"{name}/{kernel}")
+    c.check_status()
+
+
+def test_config1_fp32_auto_kernel():
+    """The CPU-runnable configuration, fp32 end to end."""
+    case = wl.config1_case()
+    g = golden("decode_cfg1")
+    c, slots, bidx, pos, k, v, q = product_from_case(case)
+    out, lse = paged_attention(q, c, 0, bidx, pos)
+    assert (out.cpu() - torch.from_numpy(g["out"])).abs().max().item() < 1e-4
+    assert (lse.cpu() - torch.from_numpy(g["lse"])).abs().max().item() < 1e-4
+
+
+def _random_case(seed, **kw):
+    d = dict(B=9, Hq=16, Hkv=8, D=128, P=128, n_pages=96, max_batch_size=12, len_lo=1, len_hi=1100,
+             dtype=torch.bfloat16, value_scale=1.0)
+    d.update(kw)
+    return wl.make_decode_case(seed, **d)
+
+
+@pytest.mark.parametrize("kernel", sorted(KERNELS))
+@pytest.mark.parametrize("kw", [
+    dict(),                                                        # GQA 2:1, D=128 (the headline layout)
+    dict(value_scale=128 ** -0.5),                                 # config-2 value scaling (near-uniform softmax)
+    dict(D=64, Hq=8, Hkv=8),                                       # MHA, D=64
+    dict(Hq=32, Hkv=8, dtype=torch.float16),                       # GQA 4:1 fp16
+    dict(Hq=16, Hkv=2, D=64),                                      # GQA 8:1
+    dict(lens=[127, 128, 129, 255, 256, 257, 0, 1, 1023]),         # page boundaries
+    dict(B=1, lens=[700]),                                         # single row
+], ids=["gqa2", "scaled", "mha64", "gqa4f16", "gqa8", "edges", "one"])
+def test_decode_against_oracle(kw, kernel):
+    case = _random_case(4242, **kw)
+    c, slots, bidx, pos, k, v, q = product_from_case(case, pad_rows=1)
+    c.decode_kernel = KERNELS[kernel]
+    o, _, obidx, opos, ok, ov, oq = oracle_from_case(case, pad_rows=1)
+    ref_out, ref_lse = orc.decode_attention(o, 0, oq.float(), obidx, opos)
+    out, lse = c.decode_attention(0, q, bidx, pos)
+    assert_attention_close(out, lse, ref_out, ref_lse, f"{kw}/{kernel}")
+    # the padding row (slot 0) sees nothing
+    assert out[-1].abs().max().item() == 0 and torch.isneginf(lse[-1]).all()
+    c.check_status()
+
+
+@pytest.mark.parametrize("kernel", sorted(KERNELS))
+def test_one_hot_key_returns_its_value_row(kernel):
+    """A key that matches q with a huge score: the answer is that row of V."""
+    case = _random_case(77, B=4, lens=[300, 513, 128, 90])
+    hot = [17, 400, 127, 0]
+    for i, t in enumerate(hot):
+        kh = case.k_hist[i]
+        kh[0, :, t, :] = 0
+        for h in range(case.Hkv):
+            # both query heads of the group point at +e0; the hot key has a large e0 component
+            kh[0, h, t, 0] = 200.0
+        case.q[i, :, 0, :] = 0
+        case.q[i, :, 0, 0] = 8.0
+    c, slots, bidx, pos, k, v, q = product_from_case(case)
+    c.decode_kernel = KERNELS[kernel]
+    out, lse = c.decode_attention(0, q, bidx, pos)
+    for i, t in enumerate(hot):
+        want = case.v_hist[i][0, :, t, :].repeat_interleave(2, 0).float()
+        assert (out[i, :, 0].float().cpu() - want).abs().max().item() <= 2e-2
+        assert abs(lse[i, 0, 0].item() - 8.0 * 200.0 / 128 ** 0.5) < 0.2
+
+
+def test_multi_layer_and_reused_pages():
+    """Layers are independent planes; pages freed by one sequence and reused by
+    another (non-contiguous tables) read correctly."""
+    torch.manual_seed(3)
+    H, Hq, D, P, NL = 8, 16, 128, 128, 3
+    c = PagedKVCache(40, P, 6, H, D, NL, torch.bfloat16, "cuda")
+    o = orc.OraclePagedKVCache(40, P, 6, H, D, NL, torch.bfloat16)
+
+    def admit(L, layer):
+        s = c.allocate(); assert o.allocate() == s
+        c.reserve(s, None, L + 1); o.reserve(s, L + 1)
+        kh, vh = torch.randn(1, H, L, D).bfloat16(), torch.randn(1, H, L, D).bfloat16()
+        ip, bi = torch.arange(L).view(1, L), torch.full((1, L), s)
+        c.insert_kv(layer, kh.cuda(), vh.cuda(), input_pos=ip.cuda(), batch_idx=bi.cuda())
+        o.append_packed(layer, bi, ip, kh, vh)
+        return s
+    a = admit(700, 1); b = admit(300, 1); d = admit(500, 1)
+    c.erase(b); o.erase(b); c.erase(a); o.erase(a)
+    e = admit(900, 1)                                  # takes a's and b's pages back, out of order
+    assert c.page_table_cpu[e] == o.page_table_cpu[e] and sorted(c.page_table_cpu[e]) != c.page_table_cpu[e]
+    lens = {d: 500, e: 900}
+    bidx = torch.tensor([e, d]); pos = torch.tensor([lens[e], lens[d]], dtype=torch.int32)
+    k, v, q = (torch.randn(2, n, 1, D).bfloat16() for n in (H, H, Hq))
+    c.insert_kv(1, k.cuda(), v.cuda(), input_pos=pos.cuda().view(2, 1), batch_idx=bidx.cuda())
+    o.append_decode(1, bidx, pos, k, v)
+    ref_out, ref_lse = orc.decode_attention(o, 1, q.float(), bidx, pos)
+    for kern in KERNELS.values():
+        c.decode_kernel = kern
+        out, lse = c.decode_attention(1, q.cuda(), bidx.cuda(), pos.cuda())
+        assert_attention_close(out, lse, ref_out, ref_lse, "reused pages")
+    assert c.kv_cache[0].abs().max().item() == 0 and c.kv_cache[2].abs().max().item() == 0
+    c.check_status()
+
+
+def test_kernels_agree_at_config2_size_and_are_deterministic():
+    """Full batch-64, 1K-8K context, permuted pool: too large for the CPU oracle
+    in seconds, so the two independent kernels check each other, a sample of
+    rows is checked against the oracle, and a rerun must be bitwise equal."""
+    case = wl.config2_case(n_pages=8192 * 2, with_history=False)
+    c = PagedKVCache(case.n_pages, case.P, case.max_batch_size, case.Hkv, case.D, 1, torch.bfloat16, "cuda")
+    c.free_pages = list(case.free_pages)
+    g = torch.Generator(device="cuda").manual_seed(5)
+    slots = []
+    for L in case.lens:
+        s = c.allocate(); c.reserve(s, None, L + 1); slots.append(s)
+    # fill every reserved page with N(0,1)/sqrt(D) values directly (the append path is tested elsewhere)
+    used = torch.tensor(sorted(p for s in slots for p in c.page_table_cpu[s]), device="cuda")
+    view = c.kv_cache.view(2, case.Hkv, case.n_pages, case.P, case.D)
+    view[:, :, used] = (torch.randn((2, case.Hkv, used.numel(), case.P, case.D), device="cuda", generator=g)
+                        * case.D ** -0.5).bfloat16()
+    bidx = torch.tensor(slots, device="cuda"); pos = torch.tensor(case.lens, dtype=torch.int32, device="cuda")
+    k, v, q = case.k_new.cuda(), case.v_new.cuda(), case.q.cuda()
+    c.insert_kv(0, k, v, input_pos=pos.view(-1, 1), batch_idx=bidx)
+    c.decode_kernel = _lib.DECODE_TMA
+    out_t, lse_t = c.decode_attention(0, q, bidx, pos)
+    out_t2, lse_t2 = c.decode_attention(0, q, bidx, pos)
+    assert torch.equal(out_t, out_t2) and torch.equal(lse_t, lse_t2)
+    c.decode_kernel = _lib.DECODE_PORTABLE
+    out_p, lse_p = c.decode_attention(0, q, bidx, pos)
+    assert_attention_close(out_t, lse_t, out_p.float().cpu(), lse_p.cpu(), "tma vs portable")
+    # oracle on three rows (gathered through the product's own gather, itself bit-exact-tested)
+    for i in (0, 31, 63):
+        gk, gv = c.gather(0, slots[i], case.lens[i] + 1)
+        s = torch.einsum("hrd,hnd->hrn", q[i, :, 0].float().view(8, 2, 128), gk.float()) * 128 ** -0.5
+        ref = torch.einsum("hrn,hnd->hrd", torch.softmax(s, -1), gv.float()).reshape(16, 128)
+        assert_attention_close(out_t[i, :, 0], lse_t[i, :, 0], ref.cpu(), torch.logsumexp(s, -1).reshape(16).cpu(),
+                               f"row {i}")
+    c.check_status()
