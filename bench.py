@@ -1,0 +1,391 @@
+"""Benchmark of the paged KV-cache decode path (append + paged decode attention).
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl fpkv|reference]
+
+Workload (one "step" = one decode step of one layer over the whole batch):
+bf16, batch 64 per GPU, 16 query heads over 8 stored heads, head_dim 128,
+page 128, context lengths uniform in [1024, 8192], page ids permuted over a
+65 536-page pool (32 GiB), values N(0,1)/sqrt(128); every step appends one
+token per sequence and runs one paged decode attention, then positions advance
+by one.  Inputs are synthetic and seeded; nothing is read from disk or network.
+
+  value      algorithmic KV GB/s of the whole job: bytes the step must move
+             (K/V of every visible key once, the appended rows, q, out, lse)
+             divided by the device time of K steps, summed over GPUs, with the
+             step inputs already resident in HBM.
+  e2e        the same through the public Python API with the step's inputs
+             (q, k, v, slots, positions) coming from pinned host memory and
+             out / lse copied back to the host every step.
+  roofline   the decode-attention kernel alone (its two launches) against the
+             measured HBM copy bandwidth.
+  cpu_baseline / --impl reference
+             the CPU restatement of the reference path (oracle/), timed on the
+             host cores with torch's threads on a bounded sample.
+
+Multi-GPU: one process per GPU (torchrun), each with its own pool and its own
+batch of 64 sequences (weak scaling); no collective on the data path, NCCL is
+used only for the timing barrier and to combine the per-rank numbers.
+"""
+
+import argparse
+import json
+import os
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+for _p in (ROOT, os.path.join(ROOT, "falcon-perception_b200")):
+    if _p not in sys.path:
+        sys.path.insert(0, _p)
+
+import torch  # noqa: E402
+
+HQ, HKV, D, P = 16, 8, 128, 128
+BATCH = 64
+LEN_LO, LEN_HI = 1024, 8192
+N_PAGES = 65536
+FALLBACK_HBM_GBS = 6650.0
+WINDOW = 64          # positions cycle through L .. L+63
+
+
+def step_bytes(lens_before_append):
+    """Algorithmic bytes of one step: K and V of every visible key (context +
+    the appended token) once, the appended K/V rows read and written, q read,
+    out written, lse written.  bf16."""
+    s = 2
+    B = len(lens_before_append)
+    kv = sum((L + 1) * 2 * HKV * D * s for L in lens_before_append)
+    return kv + 2 * B * 2 * HKV * D * s + 2 * B * HQ * D * s + 4 * B * HQ
+
+
+def measured_peak():
+    try:
+        with open(os.path.join(ROOT, "MEASURED_PEAKS.json")) as f:
+            return float(json.load(f)["hbm_gbs"]), "measured"
+    except Exception:
+        return FALLBACK_HBM_GBS, "fallback"
+
+
+class ClockSampler:
+    """SM clock and throttle reasons sampled through NVML (read-only queries)
+    every few milliseconds while the timed regions run."""
+    REASONS = (("hw_slowdown", 0x8), ("hw_thermal_slowdown", 0x40), ("sw_thermal_slowdown", 0x20),
+               ("sw_power_cap", 0x4))
+
+    def __init__(self, device_index, period_s=0.004):
+        self.period, self.samples, self.bits, self.stop_flag, self.thread = period_s, [], 0, False, None
+        self.handle = self.max_mhz = None
+        try:
+            import pynvml
+            self.nv = pynvml
+            pynvml.nvmlInit()
+            uuid = str(torch.cuda.get_device_properties(device_index).uuid)
+            uuid = uuid if uuid.startswith("GPU-") else "GPU-" + uuid
+            try:
+                self.handle = pynvml.nvmlDeviceGetHandleByUUID(uuid.encode())
+            except Exception:
+                self.handle = pynvml.nvmlDeviceGetHandleByUUID(uuid)
+            self.max_mhz = pynvml.nvmlDeviceGetMaxClockInfo(self.handle, pynvml.NVML_CLOCK_SM)
+        except Exception as e:                      # no NVML: report that instead of guessing
+            self.error = repr(e)
+            self.handle = None
+
+    def _loop(self):
+        nv = self.nv
+        while not self.stop_flag:
+            try:
+                self.samples.append(nv.nvmlDeviceGetClockInfo(self.handle, nv.NVML_CLOCK_SM))
+                self.bits |= int(nv.nvmlDeviceGetCurrentClocksEventReasons(self.handle))
+            except Exception:
+                pass
+            time.sleep(self.period)
+
+    def start(self):
+        if self.handle is not None:
+            self.thread = threading.Thread(target=self._loop, daemon=True)
+            self.thread.start()
+
+    def stop(self):
+        if self.thread is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["NVML unavailable: " + getattr(self, "error", "?")],
+                    "samples": 0}
+        self.stop_flag = True
+        self.thread.join(timeout=2)
+        v = sorted(self.samples)
+        return {"sm_mhz": v[len(v) // 2] if v else None, "sm_max_mhz": self.max_mhz,
+                "reasons": [n for n, b in self.REASONS if self.bits & b], "samples": len(v)}
+
+
+def build_gpu_workload(rank, device, n_steps):
+    """Cache with 64 seeded sequences whose context pages hold random values."""
+    from fpkv import workloads as wl
+    from fpkv.paged_attention import PagedKVCache
+    case = wl.config2_case(B=BATCH, n_pages=N_PAGES, len_lo=LEN_LO, len_hi=LEN_HI, seed=2002 + rank)
+    cache = PagedKVCache(N_PAGES, P, BATCH + 1, HKV, D, 1, torch.bfloat16, device)
+    cache.free_pages = list(case.free_pages)
+    slots = []
+    for L in case.lens:
+        s = cache.allocate(); slots.append(s)
+        cache.reserve(s, None, L + 1 + n_steps)
+    gen = torch.Generator(device=device).manual_seed(7 + rank)
+    view = cache.kv_cache.view(2, HKV, N_PAGES, P, D)
+    for s in slots:                                    # context values ~ N(0,1)/sqrt(D), written page-wise
+        pages = torch.tensor(cache.page_table_cpu[s], device=device)
+        view[:, :, pages] = (torch.randn((2, HKV, pages.numel(), P, D), device=device, generator=gen)
+                             * D ** -0.5).to(torch.bfloat16)
+    return case, cache, slots
+
+
+def run_fpkv(args):
+    import torch.distributed as dist
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    assert torch.cuda.is_available(), "bench.py needs a CUDA device; there is no CPU path for the product"
+    torch.cuda.set_device(local)
+    device = torch.device("cuda", local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=device)
+    K, W = args.steps, args.warmup
+    case, cache, slots = build_gpu_workload(rank, device, WINDOW)
+    B = BATCH
+    lens = torch.tensor(case.lens, dtype=torch.int32)
+    bidx_h = torch.tensor(slots, dtype=torch.int64).pin_memory()
+    bidx = bidx_h.to(device)
+    gen = torch.Generator(device="cpu").manual_seed(99 + rank)
+    NV = 4                                             # distinct step inputs, cycled
+    q_h = (torch.randn((NV, B, HQ, 1, D), generator=gen) * D ** -0.5).to(torch.bfloat16).pin_memory()
+    k_h = (torch.randn((NV, B, HKV, 1, D), generator=gen) * D ** -0.5).to(torch.bfloat16).pin_memory()
+    v_h = (torch.randn((NV, B, HKV, 1, D), generator=gen) * D ** -0.5).to(torch.bfloat16).pin_memory()
+    # positions advance by one per step and wrap after WINDOW steps, so that the context stays in range
+    pos_h = (lens.view(1, B) + torch.arange(WINDOW, dtype=torch.int32).view(-1, 1)).contiguous().pin_memory()
+    q_d, k_d, v_d, pos_d = q_h.to(device), k_h.to(device), v_h.to(device), pos_h.to(device)
+    out = torch.empty((B, HQ, 1, D), dtype=torch.bfloat16, device=device)
+    lse = torch.empty((B, HQ, 1), dtype=torch.float32, device=device)
+    stream = torch.cuda.current_stream(device)
+
+    def barrier():
+        torch.cuda.synchronize(device)
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize(device)
+
+    # ---------------- device-resident timing -------------------------------
+    def step_resident(i, ev=None):
+        j = i % NV
+        cache.insert_kv(0, k_d[j], v_d[j], input_pos=pos_d[i % WINDOW].view(B, 1), batch_idx=bidx)
+        if ev is not None:
+            ev[0].record(stream)
+        cache.decode_attention(0, q_d[j], bidx, pos_d[i % WINDOW], out=out, lse=lse)
+        if ev is not None:
+            ev[1].record(stream)
+
+    step = 0
+    for _ in range(W):
+        step_resident(step); step += 1
+    sampler = ClockSampler(local)
+    barrier()
+    if rank == 0:
+        sampler.start()
+    attn_ev = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(K)]
+    t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    first_timed = step
+    t0.record(stream)
+    for i in range(K):
+        step_resident(step, attn_ev[i]); step += 1
+    t1.record(stream)
+    barrier()
+    ms_total = t0.elapsed_time(t1)
+    attn_ms = sum(a.elapsed_time(b) for a, b in attn_ev) / K
+    cache.check_status()
+    bytes_timed = sum(step_bytes([L + (first_timed + i) % WINDOW for L in case.lens]) for i in range(K))
+    attn_bytes = bytes_timed / K - 2 * B * 2 * HKV * D * 2          # attention alone: no append traffic
+
+    # ---------------- end to end through the public API, host buffers ------
+    # One pinned staging buffer per direction: the step's q, k, v, positions and slots travel in one
+    # host-to-device copy, out and lse come back in one device-to-host copy; the API gets views.
+    nq, nk = B * HQ * D * 2, B * HKV * D * 2
+    in_bytes = nq + 2 * nk + B * 4 + B * 8
+    in_h = torch.empty((NV, in_bytes), dtype=torch.uint8).pin_memory()
+    in_d = torch.empty(in_bytes, dtype=torch.uint8, device=device)
+    res_d = torch.empty(nq + B * HQ * 4, dtype=torch.uint8, device=device)
+    res_h = torch.empty_like(res_d, device="cpu").pin_memory()
+
+    def views(buf):
+        o = 0
+        q = buf[o:o + nq].view(torch.bfloat16).view(B, HQ, 1, D); o += nq
+        k = buf[o:o + nk].view(torch.bfloat16).view(B, HKV, 1, D); o += nk
+        v = buf[o:o + nk].view(torch.bfloat16).view(B, HKV, 1, D); o += nk
+        bi = buf[o:o + B * 8].view(torch.int64); o += B * 8
+        ps = buf[o:o + B * 4].view(torch.int32)
+        return q, k, v, bi, ps
+    host_pos = []
+    for j in range(NV):                                # the NV distinct step inputs, staged in pinned memory
+        hq, hk, hv, hbi, hps = views(in_h[j])
+        hq.copy_(q_h[j]); hk.copy_(k_h[j]); hv.copy_(v_h[j]); hbi.copy_(bidx_h)
+        host_pos.append(hps)
+    q_s, k_s, v_s, bidx_s, pos_s = views(in_d)
+    out_s = res_d[:nq].view(torch.bfloat16).view(B, HQ, 1, D)
+    lse_s = res_d[nq:].view(torch.float32).view(B, HQ, 1)
+
+    def step_e2e(i):
+        j = i % NV
+        host_pos[j].copy_(pos_h[i % WINDOW])          # this step's positions, written by the host
+        in_d.copy_(in_h[j], non_blocking=True)
+        cache.insert_kv(0, k_s, v_s, input_pos=pos_s.view(B, 1), batch_idx=bidx_s)
+        cache.decode_attention(0, q_s, bidx_s, pos_s, out=out_s, lse=lse_s)
+        res_h.copy_(res_d, non_blocking=True)
+        stream.synchronize()                           # the step's result is on the host before the next step
+
+    for _ in range(W):
+        step_e2e(step); step += 1
+    barrier()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    first_e2e = step
+    e0.record(stream)
+    for _ in range(K):
+        step_e2e(step); step += 1
+    e1.record(stream)
+    barrier()
+    ms_e2e = e0.elapsed_time(e1)
+    clocks = sampler.stop() if rank == 0 else None
+    cache.check_status()
+    bytes_e2e = sum(step_bytes([L + (first_e2e + i) % WINDOW for L in case.lens]) for i in range(K))
+    h2d, d2h = in_d.numel(), res_h.numel()
+
+    # ---------------- combine ranks: max time, summed work -----------------
+    stats = torch.tensor([ms_total, ms_e2e, attn_ms], dtype=torch.float64, device=device)
+    work = torch.tensor([bytes_timed, bytes_e2e, float(B * K)], dtype=torch.float64, device=device)
+    if world > 1:
+        dist.all_reduce(stats, op=dist.ReduceOp.MAX)
+        dist.all_reduce(work, op=dist.ReduceOp.SUM)
+    ms_total, ms_e2e, attn_ms_max = stats.tolist()
+    bytes_all, bytes_e2e_all, tokens_all = work.tolist()
+
+    if rank == 0:
+        peak, peak_src = measured_peak()
+        achieved = attn_bytes / (attn_ms * 1e-3) / 1e9
+        line = {
+            "metric": "paged_decode_attn_kv_gbps", "value": bytes_all / (ms_total * 1e-3) / 1e9, "unit": "GB/s",
+            "n_gpus": world, "steps": K, "warmup": W, "ms_per_step": ms_total / K, "higher_is_better": True,
+            "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+            "config": {"workload": "config 2: bf16 paged decode, batch 64 per GPU, 16 q heads / 8 kv heads, "
+                                   "head_dim 128, page 128, context uniform [1024,8192], 65536-page pool, "
+                                   "1 append + 1 decode attention per sequence per step",
+                       "batch_per_gpu": B, "layers": 1, "l2": "inputs larger than L2 (about 1.2 GB of KV read per step)",
+                       "seed": 2002},
+            "decode_tokens_per_s": tokens_all / (ms_total * 1e-3),
+            "pct_of_nominal_hbm_8000": 100.0 * bytes_all / world / (ms_total * 1e-3) / 1e9 / 8000.0,
+            "e2e": {"value": bytes_e2e_all / (ms_e2e * 1e-3) / 1e9, "unit": "GB/s", "h2d_bytes_per_step": h2d,
+                    "d2h_bytes_per_step": d2h, "ms_per_step": ms_e2e / K,
+                    "decode_tokens_per_s": tokens_all / (ms_e2e * 1e-3)},
+            "gpu_launches": 3 * K,                       # per rank: append, decode attention, its finish kernel
+            "roofline": {"bound": "hbm", "kernel": "decode_tma_kernel + decode_tma_finish_kernel",
+                         "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
+                         "peak_source": peak_src, "traffic": None, "bytes_per_launch": attn_bytes,
+                         "ms_per_launch": attn_ms},
+            "clocks": clocks,
+        }
+        if world == 1:
+            line["cpu_baseline"] = cpu_baseline_sample()
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.destroy_process_group()
+
+
+# ---------------------------------------------------------------- CPU arm
+def build_cpu_workload(n_seq):
+    """The same workload shape on the CPU oracle, on a pool compacted to the
+    pages in use (the full 32 GiB pool is not needed to time the path)."""
+    from fpkv import workloads as wl
+    from oracle import paged_kv_oracle as orc
+    case = wl.config2_case(B=BATCH, n_pages=N_PAGES, len_lo=LEN_LO, len_hi=LEN_HI, seed=2002)
+    lens = case.lens[:n_seq]
+    n_pages = sum((L + 1 + 64 + P - 1) // P for L in lens) + 1
+    o = orc.OraclePagedKVCache(n_pages, P, n_seq + 1, HKV, D, 1, torch.bfloat16)
+    perm = torch.randperm(n_pages - 1, generator=torch.Generator().manual_seed(1)) + 1
+    o.free_pages = perm.tolist()
+    slots = []
+    for L in lens:
+        s = o.allocate(); o.reserve(s, L + 1 + 64); slots.append(s)
+    g = torch.Generator().manual_seed(2)
+    o.kv_cache.copy_((torch.randn((1, 1, 1, 1, n_pages * P, D), generator=g) * D ** -0.5).to(torch.bfloat16)
+                     .expand(o.kv_shape))
+    q = (torch.randn((n_seq, HQ, 1, D), generator=g) * D ** -0.5).to(torch.bfloat16)
+    k = (torch.randn((n_seq, HKV, 1, D), generator=g) * D ** -0.5).to(torch.bfloat16)
+    v = (torch.randn((n_seq, HKV, 1, D), generator=g) * D ** -0.5).to(torch.bfloat16)
+    return o, slots, lens, q, k, v
+
+
+def time_cpu_path(steps, warmup, n_seq=BATCH, budget_s=25.0):
+    from oracle import paged_kv_oracle as orc
+    o, slots, lens, q, k, v = build_cpu_workload(n_seq)
+    bidx = torch.tensor(slots)
+    times, nbytes = [], []
+    t_start = time.perf_counter()
+    for i in range(warmup + steps):
+        pos = torch.tensor([L + i for L in lens], dtype=torch.int32)
+        t0 = time.perf_counter()
+        o.append_decode(0, bidx, pos, k, v)
+        orc.decode_attention(o, 0, q, bidx, pos)
+        dt = time.perf_counter() - t0
+        if i >= warmup:
+            times.append(dt); nbytes.append(step_bytes([L + i for L in lens]))
+        if i >= warmup and time.perf_counter() - t_start > budget_s:
+            break
+    total = sum(times)
+    return {"gbps": sum(nbytes) / total / 1e9, "ms_per_step": 1e3 * total / len(times), "steps": len(times),
+            "tokens_per_s": n_seq * len(times) / total, "cores": torch.get_num_threads(), "n_seq": n_seq}
+
+
+def cpu_baseline_sample():
+    r = time_cpu_path(steps=5, warmup=1)
+    return {"value": r["gbps"], "unit": "GB/s", "cores": r["cores"], "kind": "port",
+            "sample": f"{r['steps']} steps of all {r['n_seq']} sequences on a compacted pool, "
+                      f"{r['ms_per_step']:.0f} ms per step, host has {os.cpu_count()} logical cores"}
+
+
+def run_reference(args):
+    """The reference project is Python on torch FlexAttention; its checkout is
+    not present on the benchmark machine, so this arm times the CPU port of its
+    path (oracle/) with all host threads torch uses."""
+    rank = int(os.environ.get("RANK", "0"))
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    if rank != 0:
+        return
+    r = time_cpu_path(steps=args.steps, warmup=min(args.warmup, 2), budget_s=120.0)
+    line = {
+        "impl": "reference", "metric": "paged_decode_attn_kv_gbps", "value": r["gbps"], "unit": "GB/s",
+        "n_gpus": world, "steps": r["steps"], "warmup": min(args.warmup, 2), "ms_per_step": r["ms_per_step"],
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16 storage, fp32 math",
+        "data": "synthetic",
+        "config": {"workload": "config 2: bf16 paged decode, batch 64, 16 q heads / 8 kv heads, head_dim 128, "
+                               "page 128, context uniform [1024,8192], pool compacted to the pages in use, "
+                               "1 append + 1 decode attention per sequence per step", "seed": 2002},
+        "decode_tokens_per_s": r["tokens_per_s"],
+        "cpu_baseline": {"value": r["gbps"], "unit": "GB/s", "cores": r["cores"], "kind": "port",
+                         "sample": f"{r['steps']} steps of all {r['n_seq']} sequences, "
+                                   f"host has {os.cpu_count()} logical cores"},
+        "e2e": {"value": r["gbps"], "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+    print(json.dumps(line), flush=True)
+
+
+def main():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=2000)
+    ap.add_argument("--warmup", type=int, default=20)
+    ap.add_argument("--impl", default="fpkv", choices=["fpkv", "reference"])
+    args = ap.parse_args()
+    args.warmup = max(args.warmup, 3)
+    if args.impl == "reference":
+        run_reference(args)
+    else:
+        run_fpkv(args)
+
+
+if __name__ == "__main__":
+    main()

@@ -504,11 +504,13 @@ decode_tma_finish_kernel(const Params prm, int G)
         const int r = e / D, d = e - r * D;
         float M = -INFINITY;
         for (int c = c0; c <= c1; ++c) {
+            if (share_begin(Ttot, c, G) == share_begin(Ttot, c + 1, G)) continue;   // empty share: wrote nothing
             const int slot = (t0 <= share_begin(Ttot, c, G)) ? 0 : 1;
             M = fmaxf(M, prm.ws[(((size_t)c * 2 + slot) * NREP + r) * (D + 2)]);
         }
         float Lsum = 0.f, acc = 0.f;
         for (int c = c0; c <= c1; ++c) {
+            if (share_begin(Ttot, c, G) == share_begin(Ttot, c + 1, G)) continue;
             const int slot = (t0 <= share_begin(Ttot, c, G)) ? 0 : 1;
             const float* src = prm.ws + (((size_t)c * 2 + slot) * NREP + r) * (D + 2);
             const float mc = src[0];

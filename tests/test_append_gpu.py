@@ -82,10 +82,11 @@ def test_strided_views_need_no_copy():
     for _ in range(B):
         s = c.allocate(); o.allocate(); c.reserve(s, None, 40); o.reserve(s, 40); slots.append(s)
     bidx = torch.tensor(slots, device="cuda"); pos = torch.tensor([0, 15, 16, 17, 39], dtype=torch.int32, device="cuda")
-    kbshd = torch.randn(B, 1, H, D, device="cuda").to(torch.bfloat16)
-    vbshd = torch.randn(B, 1, H, D, device="cuda").to(torch.bfloat16)
-    k, v = kbshd.permute(0, 2, 1, 3), vbshd.permute(0, 2, 1, 3)
-    assert not k.is_contiguous() or B == 1
+    # k and v as the model makes them: slices of one fused qkv projection output
+    qkv = torch.randn(B, 1, 4 * H * D, device="cuda").to(torch.bfloat16)
+    k = qkv[..., 2 * H * D:3 * H * D].view(B, 1, H, D).permute(0, 2, 1, 3)
+    v = qkv[..., 3 * H * D:].view(B, 1, H, D).permute(0, 2, 1, 3)
+    assert not k.is_contiguous() and not v.is_contiguous()
     K, V = c.insert_kv(1, k, v, input_pos=pos.view(B, 1), batch_idx=bidx)
     assert K.data_ptr() == c.kv_cache[1, 0].data_ptr() and tuple(K.shape) == (1, H, 32 * P, D)
     o.append_decode(1, bidx.cpu(), pos.cpu(), k.cpu(), v.cpu())
