@@ -117,19 +117,19 @@ class ClockSampler:
                 "reasons": [n for n, b in self.REASONS if self.bits & b], "samples": len(v)}
 
 
-def build_gpu_workload(rank, device, n_steps):
+def build_gpu_workload(rank, device, n_steps, n_pages=N_PAGES):
     """Cache with 64 seeded sequences whose context pages hold random values."""
     from fpkv import workloads as wl
     from fpkv.paged_attention import PagedKVCache
-    case = wl.config2_case(B=BATCH, n_pages=N_PAGES, len_lo=LEN_LO, len_hi=LEN_HI, seed=2002 + rank)
-    cache = PagedKVCache(N_PAGES, P, BATCH + 1, HKV, D, 1, torch.bfloat16, device)
+    case = wl.config2_case(B=BATCH, n_pages=n_pages, len_lo=LEN_LO, len_hi=LEN_HI, seed=2002 + rank)
+    cache = PagedKVCache(n_pages, P, BATCH + 1, HKV, D, 1, torch.bfloat16, device)
     cache.free_pages = list(case.free_pages)
     slots = []
     for L in case.lens:
         s = cache.allocate(); slots.append(s)
         cache.reserve(s, None, L + 1 + n_steps)
     gen = torch.Generator(device=device).manual_seed(7 + rank)
-    view = cache.kv_cache.view(2, HKV, N_PAGES, P, D)
+    view = cache.kv_cache.view(2, HKV, n_pages, P, D)
     for s in slots:                                    # context values ~ N(0,1)/sqrt(D), written page-wise
         pages = torch.tensor(cache.page_table_cpu[s], device=device)
         view[:, :, pages] = (torch.randn((2, HKV, pages.numel(), P, D), device=device, generator=gen)
@@ -148,7 +148,7 @@ def run_fpkv(args):
     if world > 1:
         dist.init_process_group("nccl", device_id=device)
     K, W = args.steps, args.warmup
-    case, cache, slots = build_gpu_workload(rank, device, WINDOW)
+    case, cache, slots = build_gpu_workload(rank, device, WINDOW, args.pool_pages)
     B = BATCH
     lens = torch.tensor(case.lens, dtype=torch.int32)
     bidx_h = torch.tensor(slots, dtype=torch.int64).pin_memory()
@@ -238,17 +238,21 @@ def run_fpkv(args):
         res_h.copy_(res_d, non_blocking=True)
         stream.synchronize()                           # the step's result is on the host before the next step
 
-    for _ in range(W):
-        step_e2e(step); step += 1
-    barrier()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     first_e2e = step
-    e0.record(stream)
-    for _ in range(K):
-        step_e2e(step); step += 1
-    e1.record(stream)
-    barrier()
-    ms_e2e = e0.elapsed_time(e1)
+    if args.kernels_only:                              # profiling runs: device-resident loop only
+        ms_e2e = float("nan")
+    else:
+        for _ in range(W):
+            step_e2e(step); step += 1
+        barrier()
+        first_e2e = step
+        e0.record(stream)
+        for _ in range(K):
+            step_e2e(step); step += 1
+        e1.record(stream)
+        barrier()
+        ms_e2e = e0.elapsed_time(e1)
     clocks = sampler.stop() if rank == 0 else None
     cache.check_status()
     bytes_e2e = sum(step_bytes([L + (first_e2e + i) % WINDOW for L in case.lens]) for i in range(K))
@@ -280,15 +284,17 @@ def run_fpkv(args):
             "e2e": {"value": bytes_e2e_all / (ms_e2e * 1e-3) / 1e9, "unit": "GB/s", "h2d_bytes_per_step": h2d,
                     "d2h_bytes_per_step": d2h, "ms_per_step": ms_e2e / K,
                     "decode_tokens_per_s": tokens_all / (ms_e2e * 1e-3)},
-            "gpu_launches": 3 * K,                       # per rank: append, decode attention, its finish kernel
-            "roofline": {"bound": "hbm", "kernel": "decode_tma_kernel + decode_tma_finish_kernel",
+            "gpu_launches": 2 * K,                       # per rank: append kernel + decode-attention kernel
+            "roofline": {"bound": "hbm", "kernel": "decode_tma_kernel",
                          "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
                          "peak_source": peak_src, "traffic": None, "bytes_per_launch": attn_bytes,
                          "ms_per_launch": attn_ms},
             "clocks": clocks,
         }
-        if world == 1:
+        if world == 1 and not args.kernels_only:
             line["cpu_baseline"] = cpu_baseline_sample()
+        if args.pool_pages != N_PAGES:
+            line["config"]["pool_pages"] = args.pool_pages
         print(json.dumps(line), flush=True)
     if world > 1:
         dist.destroy_process_group()
@@ -379,6 +385,10 @@ def main():
     ap.add_argument("--steps", type=int, default=2000)
     ap.add_argument("--warmup", type=int, default=20)
     ap.add_argument("--impl", default="fpkv", choices=["fpkv", "reference"])
+    ap.add_argument("--pool-pages", type=int, default=N_PAGES,
+                    help="pages in the pool (default 65536 = 32 GiB; profiling captures use a small pool)")
+    ap.add_argument("--kernels-only", action="store_true",
+                    help="run only the device-resident loop (no host-buffer loop, no CPU baseline): for profilers")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3)
     if args.impl == "reference":

@@ -7,6 +7,8 @@ using namespace fpkv;
 
 namespace {
 
+constexpr size_t kCounterBytes = 1024;   // head of the decode workspace: arrival counters of the TMA kernel
+
 inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
 
 int esize_of(int dtype) {
@@ -130,7 +132,7 @@ int fpkv_decode_workspace_bytes(const fpkv_pool* pool, int32_t B, int32_t n_q_he
     if (rc) return rc;
     if (bytes == nullptr || B < 0 || n_q_heads <= 0) return FPKV_EINVAL;
     if (n_q_heads % pv.H) return FPKV_ESHAPE;
-    size_t a = decode_portable_workspace_bytes(B, n_q_heads, pv.D);
+    size_t a = decode_portable_workspace_bytes(B, n_q_heads, pv.D) + kCounterBytes;
     size_t b = decode_tma_workspace_bytes(n_q_heads, pv.H, pv.D);
     *bytes = (a > b ? a : b) + 256;
     return FPKV_OK;
@@ -155,15 +157,17 @@ int fpkv_decode_attn(const fpkv_pool* pool, int32_t layer, void* out, float* lse
     const bool tma_ok = decode_tma_supported(pv, n_q_heads);
     if (which == FPKV_DECODE_TMA && !tma_ok) return FPKV_ESHAPE;
     const bool use_tma = which == FPKV_DECODE_TMA || (which == FPKV_DECODE_AUTO && tma_ok);
+    // both kernels leave the counter words at the head of the workspace alone or at zero
     const size_t need = use_tma ? decode_tma_workspace_bytes(n_q_heads, pv.H, pv.D)
-                                : decode_portable_workspace_bytes(B, n_q_heads, pv.D);
+                                : decode_portable_workspace_bytes(B, n_q_heads, pv.D) + kCounterBytes;
     if (workspace_bytes < need) return FPKV_EWORKSPACE;
     if ((rc = check_arch())) return rc;
     cudaStream_t s = static_cast<cudaStream_t>(stream);
     return use_tma ? launch_decode_tma(pv, layer, out, lse, q, q_stride_b, q_stride_h, batch_idx, input_pos,
                                        pos_type, B, n_q_heads, sm_scale, workspace, status, s)
                    : launch_decode_portable(pv, layer, out, lse, q, q_stride_b, q_stride_h, batch_idx,
-                                            input_pos, pos_type, B, n_q_heads, sm_scale, workspace, status, s);
+                                            input_pos, pos_type, B, n_q_heads, sm_scale,
+                                            static_cast<char*>(workspace) + kCounterBytes, status, s);
 }
 
 }  // extern "C"

@@ -10,9 +10,11 @@
 //    over (row b, stored head h, logical page) and the flat range is cut into
 //    gridDim.x equal contiguous shares, one persistent CTA per SM.  A share can
 //    start and end in the middle of a (b, h) segment; such a piece leaves an
-//    unnormalised partial (m, l, acc) in the workspace and a small second
-//    kernel merges the pieces.  Segments that lie inside one share are
-//    normalised and written directly.
+//    unnormalised partial (m, l, acc) in the workspace and takes a ticket; the
+//    CTA that takes a segment's last ticket merges the pieces and writes the
+//    result (nobody waits).  Segments that lie inside one share are normalised
+//    and written directly.  The ticket words must be zero on entry and are
+//    left zero, so the workspace is zero-filled once, not per call.
 //  * One producer warp walks the share, looks page ids up in the page table
 //    (32 tiles per coalesced read, two lookups ahead of use) and issues one
 //    TMA tensor copy per K or V tile into a ring of shared-memory slots; the
@@ -141,7 +143,7 @@ struct Params {
     void* out;
     float* lse;
     float* ws;                 // partials [gridDim.x][2][NREP][D+2]
-    int* ws_cum;               // [B+1] tiles before each row, written by CTA 0
+    int* tickets;              // [gridDim.x] arrival counts of cut segments, indexed by first owner; zero between calls
     int32_t* status;
     long long q_stride_b, q_stride_h;
     int B, Hkv, n_pages, max_batch;
@@ -161,7 +163,6 @@ decode_tma_kernel(const __grid_constant__ CUtensorMap tmap, const Params prm)
     using L = Layout<D, P, NREP>;
     constexpr int NS = L::kSlots;
     constexpr int kTile = L::kTileBytes;
-    constexpr int KH = D / 64;                        // 128-byte column groups per row
     constexpr int RW = P / kConsumerWarps;            // token rows per consumer warp (16 at P=128)
     constexpr int NB = RW / 8;                        // n8 score blocks per warp
     static_assert(RW % 16 == 0, "page_size must be a multiple of 128 rows / 8 warps * 16");
@@ -174,6 +175,7 @@ decode_tma_kernel(const __grid_constant__ CUtensorMap tmap, const Params prm)
     uint64_t* bars = reinterpret_cast<uint64_t*>(merge + 2 * L::kMergeFloats); // full[NS], empty[NS]
     int* slot_valid = reinterpret_cast<int*>(bars + 32);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(slot_valid + 16);
+    int* last_flag = const_cast<int*>(reinterpret_cast<volatile int*>(abort_flag) + 1);
     int* cum = const_cast<int*>(reinterpret_cast<volatile int*>(abort_flag) + 4);   // [B+1] tiles before row b
     long long* slot_of = reinterpret_cast<long long*>(cum + kMaxBatchPerLaunch + 1 + ((kMaxBatchPerLaunch + 1) & 1));
 
@@ -213,7 +215,16 @@ decode_tma_kernel(const __grid_constant__ CUtensorMap tmap, const Params prm)
     __syncthreads();
     const long long Ttot = cum[B];
     const int G = gridDim.x, cta = blockIdx.x;
-    if (cta == 0) for (int i = tid; i <= B; i += kThreads) prm.ws_cum[i] = cum[i];   // for the finish kernel
+    // rows without any tile (bad slot or position): out = 0, lse = -inf, one CTA per such row
+    {
+        const int Hq = Hkv * NREP;
+        T* out0 = reinterpret_cast<T*>(prm.out);
+        for (int b = cta; b < B; b += G) {
+            if (cum[b + 1] != cum[b]) continue;
+            for (int e = tid; e < Hq * D; e += kThreads) out0[(size_t)b * Hq * D + e] = ElemTraits<T>::from_float(0.f);
+            for (int e = tid; e < Hq; e += kThreads) prm.lse[(size_t)b * Hq + e] = -INFINITY;
+        }
+    }
     const int r0 = (int)share_begin(Ttot, cta, G), r1 = (int)share_begin(Ttot, cta + 1, G);
 
     // Row that owns flat tile t (cum[b] <= t < cum[b+1]); B >= 1 and t < Ttot.
@@ -445,6 +456,7 @@ decode_tma_kernel(const __grid_constant__ CUtensorMap tmap, const Params prm)
         }
         consumer_bar();
         if (*abort_flag) break;
+        const int Hq = Hkv * NREP;
         for (int e = tid; e < NREP * D; e += kConsumerWarps * 32) {
             const int r = e / D, d = e - r * D;
             float M = -INFINITY;
@@ -463,67 +475,63 @@ decode_tma_kernel(const __grid_constant__ CUtensorMap tmap, const Params prm)
             }
             const int hq = h * NREP + r;
             if (direct) {
-                out[((size_t)b * (Hkv * NREP) + hq) * D + d] = ElemTraits<T>::from_float(Lsum > 0.f ? acc / Lsum : 0.f);
-                if (d == 0) prm.lse[(size_t)b * (Hkv * NREP) + hq] = Lsum > 0.f ? (M + log2f(Lsum)) * kLn2 : -INFINITY;
+                out[((size_t)b * Hq + hq) * D + d] = ElemTraits<T>::from_float(Lsum > 0.f ? acc / Lsum : 0.f);
+                if (d == 0) prm.lse[(size_t)b * Hq + hq] = Lsum > 0.f ? (M + log2f(Lsum)) * kLn2 : -INFINITY;
             } else {
                 float* dst = prm.ws + (((size_t)cta * 2 + ws_slot) * NREP + r) * (D + 2);
-                dst[2 + d] = acc;
-                if (d == 0) { dst[0] = M; dst[1] = Lsum; }
+                __stcg(dst + 2 + d, acc);
+                if (d == 0) { __stcg(dst, M); __stcg(dst + 1, Lsum); }
+            }
+        }
+        if (!direct) {
+            // Segment cut by share boundaries: publish the partial, take a ticket; the last of the
+            // segment's pieces to arrive merges them all.  The ticket word belongs to the share that
+            // owns the segment's first tile and goes back to zero for the next call.
+            const int c_first = (int)(((long long)(seg0 + 1) * G - 1) / Ttot);
+            const int c_last = (int)(((long long)seg1 * G - 1) / Ttot);
+            __threadfence();
+            consumer_bar();
+            if (tid == 0) {
+                int expected = 0;
+                for (int c = c_first; c <= c_last; ++c)
+                    expected += share_begin(Ttot, c, G) != share_begin(Ttot, c + 1, G);
+                const int prev = atomicAdd(prm.tickets + c_first, 1);
+                *last_flag = (prev + 1 == expected);
+                if (prev + 1 == expected) prm.tickets[c_first] = 0;
+            }
+            consumer_bar();
+            if (*last_flag) {
+                __threadfence();
+                for (int e = tid; e < NREP * D; e += kConsumerWarps * 32) {
+                    const int r = e / D, d = e - r * D;
+                    float M = -INFINITY;
+                    for (int c = c_first; c <= c_last; ++c) {
+                        if (share_begin(Ttot, c, G) == share_begin(Ttot, c + 1, G)) continue;   // empty share
+                        const int slot = (seg0 <= share_begin(Ttot, c, G)) ? 0 : 1;
+                        M = fmaxf(M, __ldcg(prm.ws + (((size_t)c * 2 + slot) * NREP + r) * (D + 2)));
+                    }
+                    float Lsum = 0.f, acc = 0.f;
+                    for (int c = c_first; c <= c_last; ++c) {
+                        if (share_begin(Ttot, c, G) == share_begin(Ttot, c + 1, G)) continue;
+                        const int slot = (seg0 <= share_begin(Ttot, c, G)) ? 0 : 1;
+                        const float* src = prm.ws + (((size_t)c * 2 + slot) * NREP + r) * (D + 2);
+                        const float mc = __ldcg(src);
+                        if (mc != -INFINITY) {
+                            const float wgt = exp2f(mc - M);
+                            Lsum += __ldcg(src + 1) * wgt;
+                            acc += __ldcg(src + 2 + d) * wgt;
+                        }
+                    }
+                    const int hq = h * NREP + r;
+                    out[((size_t)b * Hq + hq) * D + d] = ElemTraits<T>::from_float(Lsum > 0.f ? acc / Lsum : 0.f);
+                    if (d == 0) prm.lse[(size_t)b * Hq + hq] = Lsum > 0.f ? (M + log2f(Lsum)) * kLn2 : -INFINITY;
+                }
             }
         }
         t = piece_end;
     }
 }
 
-
-// Second kernel, one CTA per (row b, stored head h): rows without any tile get
-// out = 0 / lse = -inf, and a segment cut by share boundaries is merged from
-// the partials its pieces left in the workspace.  Segments that one share
-// covered were written by the main kernel and are skipped here.
-template <typename T, int D, int NREP>
-__global__ void __launch_bounds__(128)
-decode_tma_finish_kernel(const Params prm, int G)
-{
-    const int b = blockIdx.x / prm.Hkv, h = blockIdx.x % prm.Hkv;
-    const int Hq = prm.Hkv * NREP;
-    const int npg = (prm.ws_cum[b + 1] - prm.ws_cum[b]) / prm.Hkv;
-    const long long Ttot = prm.ws_cum[prm.B];
-    T* out = reinterpret_cast<T*>(prm.out);
-    if (npg == 0) {
-        for (int e = threadIdx.x; e < NREP * D; e += blockDim.x) {
-            const int r = e / D, d = e - r * D;
-            out[((size_t)b * Hq + h * NREP + r) * D + d] = ElemTraits<T>::from_float(0.f);
-            if (d == 0) prm.lse[(size_t)b * Hq + h * NREP + r] = -INFINITY;
-        }
-        return;
-    }
-    const long long t0 = prm.ws_cum[b] + (long long)h * npg, t1 = t0 + npg;
-    const int c0 = (int)(((t0 + 1) * G - 1) / Ttot), c1 = (int)((t1 * G - 1) / Ttot);   // shares owning t0, t1-1
-    if (c0 == c1) return;
-    for (int e = threadIdx.x; e < NREP * D; e += blockDim.x) {
-        const int r = e / D, d = e - r * D;
-        float M = -INFINITY;
-        for (int c = c0; c <= c1; ++c) {
-            if (share_begin(Ttot, c, G) == share_begin(Ttot, c + 1, G)) continue;   // empty share: wrote nothing
-            const int slot = (t0 <= share_begin(Ttot, c, G)) ? 0 : 1;
-            M = fmaxf(M, prm.ws[(((size_t)c * 2 + slot) * NREP + r) * (D + 2)]);
-        }
-        float Lsum = 0.f, acc = 0.f;
-        for (int c = c0; c <= c1; ++c) {
-            if (share_begin(Ttot, c, G) == share_begin(Ttot, c + 1, G)) continue;
-            const int slot = (t0 <= share_begin(Ttot, c, G)) ? 0 : 1;
-            const float* src = prm.ws + (((size_t)c * 2 + slot) * NREP + r) * (D + 2);
-            const float mc = src[0];
-            if (mc != -INFINITY) {
-                const float w = exp2f(mc - M);
-                Lsum += src[1] * w;
-                acc += src[2 + d] * w;
-            }
-        }
-        out[((size_t)b * Hq + h * NREP + r) * D + d] = ElemTraits<T>::from_float(Lsum > 0.f ? acc / Lsum : 0.f);
-        if (d == 0) prm.lse[(size_t)b * Hq + h * NREP + r] = Lsum > 0.f ? (M + log2f(Lsum)) * kLn2 : -INFINITY;
-    }
-}
 
 // ------------------------------------------------------------------- host
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
@@ -552,7 +560,7 @@ int sm_count() {
     return n;
 }
 
-constexpr size_t kCumBytes = ((kMaxBatchPerLaunch + 1) * sizeof(int) + 255) / 256 * 256;
+constexpr size_t kTicketBytes = 1024;              // one int per share (<= 256 SMs)
 
 template <typename T, int D, int P, int NREP, typename PosT>
 int launch_one(const CUtensorMap& map, Params prm, int G, cudaStream_t stream)
@@ -563,8 +571,6 @@ int launch_one(const CUtensorMap& map, Params prm, int G, cudaStream_t stream)
     if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, L::kSmemBytes) != cudaSuccess)
         return FPKV_ELAUNCH;
     kern<<<G, kThreads, L::kSmemBytes, stream>>>(map, prm);
-    if (cudaGetLastError() != cudaSuccess) return FPKV_ELAUNCH;
-    decode_tma_finish_kernel<T, D, NREP><<<prm.B * prm.Hkv, 128, 0, stream>>>(prm, G);
     return cudaGetLastError() == cudaSuccess ? FPKV_OK : FPKV_ELAUNCH;
 }
 
@@ -604,7 +610,7 @@ bool decode_tma_supported(const PoolView& pv, int Hq)
 size_t decode_tma_workspace_bytes(int Hq, int Hkv, int D)
 {
     const int nrep = Hq / Hkv;
-    return kCumBytes + (size_t)sm_count() * 2 * nrep * (D + 2) * sizeof(float);
+    return kTicketBytes + (size_t)sm_count() * 2 * nrep * (D + 2) * sizeof(float);
 }
 
 int launch_decode_tma(const PoolView& pv, int layer, void* out, float* lse, const void* q,
@@ -626,7 +632,7 @@ int launch_decode_tma(const PoolView& pv, int layer, void* out, float* lse, cons
                     CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
         return FPKV_ELAUNCH;
 
-    const int G = sm_count();
+    const int G = sm_count() < 256 ? sm_count() : 256;
     const size_t esz = 2;
     for (int b0 = 0; b0 < B; b0 += kMaxBatchPerLaunch) {
         Params prm;
@@ -636,8 +642,8 @@ int launch_decode_tma(const PoolView& pv, int layer, void* out, float* lse, cons
         prm.q = (const char*)q + (size_t)b0 * q_stride_b * esz;
         prm.out = (char*)out + (size_t)b0 * Hq * pv.D * esz;
         prm.lse = lse + (size_t)b0 * Hq;
-        prm.ws_cum = (int*)workspace;
-        prm.ws = (float*)((char*)workspace + kCumBytes);
+        prm.tickets = (int*)workspace;
+        prm.ws = (float*)((char*)workspace + kTicketBytes);
         prm.status = status;
         prm.q_stride_b = q_stride_b; prm.q_stride_h = q_stride_h;
         prm.B = (B - b0 < kMaxBatchPerLaunch) ? B - b0 : kMaxBatchPerLaunch;

@@ -251,7 +251,8 @@ class PagedKVCache(KVCacheBase):
         _lib.check(_lib.lib.fpkv_decode_workspace_bytes(ctypes.byref(self._pool), B, Hq, ctypes.byref(need)),
                    "fpkv_decode_workspace_bytes")
         if self._workspace is None or self._workspace.numel() < need.value:
-            self._workspace = torch.empty(need.value, dtype=torch.uint8, device=self._dev)
+            # zero-filled once: the head of the workspace holds arrival counters the kernel leaves at zero
+            self._workspace = torch.zeros(need.value, dtype=torch.uint8, device=self._dev)
         return self._workspace
 
     def decode_attention(self, layer_id: int, q: Tensor, batch_idx: Tensor, input_pos: Tensor,

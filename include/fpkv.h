@@ -150,7 +150,11 @@ FPKV_API int fpkv_decode_workspace_bytes(const fpkv_pool* pool, int32_t B, int32
  * Query head hq reads stored head hq / (n_q_heads / pool->n_heads).
  * q: device (B, n_q_heads, 1, head_dim) with element strides q_stride_b/_h.
  * workspace: device, at least fpkv_decode_workspace_bytes() bytes, 16-byte
- * aligned; contents need not be initialised and are not kept between calls.
+ * aligned.  Its first 1024 bytes hold arrival counters that must be ZERO on
+ * entry; every call that completes leaves them zero, so zero-fill the
+ * workspace once when it is allocated (and again after a call that raised
+ * FPKV_STATUS_TIMEOUT).  The rest needs no initialisation.  Two calls that
+ * share a workspace must not overlap on the device.
  * flags: FPKV_DECODE_AUTO picks the TMA + tensor-core kernel when the shape is
  * in its range (16-bit pool, page_size 128, head_dim 64/128, 1/2/4/8 query
  * heads per stored head) and the portable CUDA-core kernel otherwise;
