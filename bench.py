@@ -117,12 +117,12 @@ class ClockSampler:
                 "reasons": [n for n, b in self.REASONS if self.bits & b], "samples": len(v)}
 
 
-def build_gpu_workload(rank, device, n_steps, n_pages=N_PAGES):
+def build_gpu_workload(rank, device, n_steps, n_pages=N_PAGES, batch=BATCH, len_lo=LEN_LO, len_hi=LEN_HI):
     """Cache with 64 seeded sequences whose context pages hold random values."""
     from fpkv import workloads as wl
     from fpkv.paged_attention import PagedKVCache
-    case = wl.config2_case(B=BATCH, n_pages=n_pages, len_lo=LEN_LO, len_hi=LEN_HI, seed=2002 + rank)
-    cache = PagedKVCache(n_pages, P, BATCH + 1, HKV, D, 1, torch.bfloat16, device)
+    case = wl.config2_case(B=batch, n_pages=n_pages, len_lo=len_lo, len_hi=len_hi, seed=2002 + rank)
+    cache = PagedKVCache(n_pages, P, batch + 1, HKV, D, 1, torch.bfloat16, device)
     cache.free_pages = list(case.free_pages)
     slots = []
     for L in case.lens:
@@ -148,8 +148,8 @@ def run_fpkv(args):
     if world > 1:
         dist.init_process_group("nccl", device_id=device)
     K, W = args.steps, args.warmup
-    case, cache, slots = build_gpu_workload(rank, device, WINDOW, args.pool_pages)
-    B = BATCH
+    case, cache, slots = build_gpu_workload(rank, device, WINDOW, args.pool_pages, args.batch, args.len_lo, args.len_hi)
+    B = args.batch
     lens = torch.tensor(case.lens, dtype=torch.int32)
     bidx_h = torch.tensor(slots, dtype=torch.int64).pin_memory()
     bidx = bidx_h.to(device)
@@ -172,14 +172,10 @@ def run_fpkv(args):
         torch.cuda.synchronize(device)
 
     # ---------------- device-resident timing -------------------------------
-    def step_resident(i, ev=None):
+    # One step = the fused public call (append, then attention whose set-up overlaps the append).
+    def step_resident(i):
         j = i % NV
-        cache.insert_kv(0, k_d[j], v_d[j], input_pos=pos_d[i % WINDOW].view(B, 1), batch_idx=bidx)
-        if ev is not None:
-            ev[0].record(stream)
-        cache.decode_attention(0, q_d[j], bidx, pos_d[i % WINDOW], out=out, lse=lse)
-        if ev is not None:
-            ev[1].record(stream)
+        cache.decode_step(0, q_d[j], k_d[j], v_d[j], bidx, pos_d[i % WINDOW], out=out, lse=lse)
 
     step = 0
     for _ in range(W):
@@ -188,18 +184,27 @@ def run_fpkv(args):
     barrier()
     if rank == 0:
         sampler.start()
-    attn_ev = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(K)]
     t0, t1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     first_timed = step
     t0.record(stream)
     for i in range(K):
-        step_resident(step, attn_ev[i]); step += 1
+        step_resident(step); step += 1
     t1.record(stream)
     barrier()
     ms_total = t0.elapsed_time(t1)
-    attn_ms = sum(a.elapsed_time(b) for a, b in attn_ev) / K
     cache.check_status()
     bytes_timed = sum(step_bytes([L + (first_timed + i) % WINDOW for L in case.lens]) for i in range(K))
+
+    # The decode-attention kernel alone (main kernel + its finish kernel), same positions as the
+    # timed steps, one pair of events per launch on the launching stream: the roofline numerator.
+    attn_ev = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(K)]
+    for i in range(K):
+        j = (first_timed + i) % NV
+        attn_ev[i][0].record(stream)
+        cache.decode_attention(0, q_d[j], bidx, pos_d[(first_timed + i) % WINDOW], out=out, lse=lse)
+        attn_ev[i][1].record(stream)
+    barrier()
+    attn_ms = sum(a.elapsed_time(b) for a, b in attn_ev) / K
     attn_bytes = bytes_timed / K - 2 * B * 2 * HKV * D * 2          # attention alone: no append traffic
 
     # ---------------- end to end through the public API, host buffers ------
@@ -233,8 +238,7 @@ def run_fpkv(args):
         j = i % NV
         host_pos[j].copy_(pos_h[i % WINDOW])          # this step's positions, written by the host
         in_d.copy_(in_h[j], non_blocking=True)
-        cache.insert_kv(0, k_s, v_s, input_pos=pos_s.view(B, 1), batch_idx=bidx_s)
-        cache.decode_attention(0, q_s, bidx_s, pos_s, out=out_s, lse=lse_s)
+        cache.decode_step(0, q_s, k_s, v_s, bidx_s, pos_s, out=out_s, lse=lse_s)
         res_h.copy_(res_d, non_blocking=True)
         stream.synchronize()                           # the step's result is on the host before the next step
 
@@ -284,8 +288,8 @@ def run_fpkv(args):
             "e2e": {"value": bytes_e2e_all / (ms_e2e * 1e-3) / 1e9, "unit": "GB/s", "h2d_bytes_per_step": h2d,
                     "d2h_bytes_per_step": d2h, "ms_per_step": ms_e2e / K,
                     "decode_tokens_per_s": tokens_all / (ms_e2e * 1e-3)},
-            "gpu_launches": 2 * K,                       # per rank: append kernel + decode-attention kernel
-            "roofline": {"bound": "hbm", "kernel": "decode_tma_kernel",
+            "gpu_launches": 3 * K,                       # per rank and step: append, decode attention, its finish kernel
+            "roofline": {"bound": "hbm", "kernel": "decode_tma_kernel + decode_tma_finish_kernel (one decode-attention call), timed alone",
                          "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
                          "peak_source": peak_src, "traffic": None, "bytes_per_launch": attn_bytes,
                          "ms_per_launch": attn_ms},
@@ -295,6 +299,10 @@ def run_fpkv(args):
             line["cpu_baseline"] = cpu_baseline_sample()
         if args.pool_pages != N_PAGES:
             line["config"]["pool_pages"] = args.pool_pages
+        if (args.batch, args.len_lo, args.len_hi) != (BATCH, LEN_LO, LEN_HI):      # not the headline workload
+            line["config"]["workload"] = (f"variant: bf16 paged decode, batch {args.batch} per GPU, 16 q heads / 8 kv "
+                                          f"heads, head_dim 128, page 128, context uniform [{args.len_lo},{args.len_hi}]")
+            line["config"]["batch_per_gpu"] = args.batch
         print(json.dumps(line), flush=True)
     if world > 1:
         dist.destroy_process_group()
@@ -387,6 +395,9 @@ def main():
     ap.add_argument("--impl", default="fpkv", choices=["fpkv", "reference"])
     ap.add_argument("--pool-pages", type=int, default=N_PAGES,
                     help="pages in the pool (default 65536 = 32 GiB; profiling captures use a small pool)")
+    ap.add_argument("--batch", type=int, default=BATCH, help="sequences per GPU (default 64: the headline workload)")
+    ap.add_argument("--len-lo", type=int, default=LEN_LO)
+    ap.add_argument("--len-hi", type=int, default=LEN_HI)
     ap.add_argument("--kernels-only", action="store_true",
                     help="run only the device-resident loop (no host-buffer loop, no CPU baseline): for profilers")
     args = ap.parse_args()

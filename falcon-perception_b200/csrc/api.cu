@@ -7,7 +7,7 @@ using namespace fpkv;
 
 namespace {
 
-constexpr size_t kCounterBytes = 1024;   // head of the decode workspace: arrival counters of the TMA kernel
+constexpr size_t kCounterBytes = 16384;  // head of the decode workspace: counters of the TMA kernel
 
 inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
 
@@ -164,7 +164,8 @@ int fpkv_decode_attn(const fpkv_pool* pool, int32_t layer, void* out, float* lse
     if ((rc = check_arch())) return rc;
     cudaStream_t s = static_cast<cudaStream_t>(stream);
     return use_tma ? launch_decode_tma(pv, layer, out, lse, q, q_stride_b, q_stride_h, batch_idx, input_pos,
-                                       pos_type, B, n_q_heads, sm_scale, workspace, status, s)
+                                       pos_type, B, n_q_heads, sm_scale, workspace, status, s,
+                                       (flags & FPKV_DECODE_AFTER_APPEND) != 0)
                    : launch_decode_portable(pv, layer, out, lse, q, q_stride_b, q_stride_h, batch_idx,
                                             input_pos, pos_type, B, n_q_heads, sm_scale,
                                             static_cast<char*>(workspace) + kCounterBytes, status, s);

@@ -24,6 +24,11 @@ append_kernel(char* __restrict__ pool_layer,           // plane(layer, 0, 0)
               const char* __restrict__ v, long long v_tok_bytes, long long v_head_bytes,
               int n_tok, int vec_per_row, bool decode_mode, int32_t* status)
 {
+    // Launched with programmatic stream serialisation: the grid may become resident while the
+    // preceding kernel drains; nothing is read or written before that kernel is complete.  A kernel
+    // launched the same way behind this one may start its own set-up now.
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+    asm volatile("griddepcontrol.launch_dependents;");
     const long long total = (long long)n_tok * H * vec_per_row;
     const int kv = blockIdx.y;
     const char* src = kv ? v : k;
@@ -69,16 +74,24 @@ int launch_append(const PoolView& pv, int layer, const int64_t* batch_idx, const
     dim3 grid((unsigned)blocks, 2);
     char* pool_layer = pv.plane(layer, 0, 0);
     const long long es = pv.esize;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid; cfg.blockDim = dim3(threads); cfg.dynamicSmemBytes = 0; cfg.stream = stream;
+    cfg.attrs = attr; cfg.numAttrs = 1;
+    cudaError_t err;
     if (pos_type == FPKV_I32)
-        append_kernel<int32_t><<<grid, threads, 0, stream>>>(pool_layer, pv.plane_bytes(), pv.H, pv.page_table,
+        err = cudaLaunchKernelEx(&cfg, append_kernel<int32_t>, pool_layer, pv.plane_bytes(), pv.H, pv.page_table,
             pv.n_pages, pv.max_batch, pv.P, batch_idx, (const int32_t*)pos,
             (const char*)k, k_stride_tok * es, k_stride_h * es, (const char*)v, v_stride_tok * es, v_stride_h * es,
             n_tok, vec_per_row, decode_mode, status);
     else
-        append_kernel<int64_t><<<grid, threads, 0, stream>>>(pool_layer, pv.plane_bytes(), pv.H, pv.page_table,
+        err = cudaLaunchKernelEx(&cfg, append_kernel<int64_t>, pool_layer, pv.plane_bytes(), pv.H, pv.page_table,
             pv.n_pages, pv.max_batch, pv.P, batch_idx, (const int64_t*)pos,
             (const char*)k, k_stride_tok * es, k_stride_h * es, (const char*)v, v_stride_tok * es, v_stride_h * es,
             n_tok, vec_per_row, decode_mode, status);
+    if (err != cudaSuccess) return FPKV_ELAUNCH;
     return cudaGetLastError() == cudaSuccess ? FPKV_OK : FPKV_ELAUNCH;
 }
 

@@ -69,6 +69,6 @@ size_t decode_tma_workspace_bytes(int Hq, int Hkv, int D);
 int launch_decode_tma(const PoolView& pv, int layer, void* out, float* lse, const void* q,
                       long long q_stride_b, long long q_stride_h, const int64_t* batch_idx,
                       const void* pos, int pos_type, int B, int Hq, float sm_scale,
-                      void* workspace, int32_t* status, cudaStream_t stream);
+                      void* workspace, int32_t* status, cudaStream_t stream, bool after_append);
 
 }  // namespace fpkv

@@ -4,29 +4,41 @@
 // The kernel is bound by HBM reads of K and V.  Everything is arranged so that
 // every SM streams an equal share of the batch's pages at full rate:
 //
-//  * Work unit ("tile") = one page of one stored head of one row: a K tile and
-//    a V tile of page_size x head_dim elements, each contiguous in the pool
-//    (32 KiB at page 128, head_dim 128, 16-bit).  Tiles are numbered row-major
-//    over (row b, stored head h, logical page) and the flat range is cut into
-//    gridDim.x equal contiguous shares, one persistent CTA per SM.  A share can
-//    start and end in the middle of a (b, h) segment; such a piece leaves an
-//    unnormalised partial (m, l, acc) in the workspace and takes a ticket; the
-//    CTA that takes a segment's last ticket merges the pieces and writes the
-//    result (nobody waits).  Segments that lie inside one share are normalised
-//    and written directly.  The ticket words must be zero on entry and are
-//    left zero, so the workspace is zero-filled once, not per call.
-//  * One producer warp walks the share, looks page ids up in the page table
-//    (32 tiles per coalesced read, two lookups ahead of use) and issues one
-//    TMA tensor copy per K or V tile into a ring of shared-memory slots; the
-//    copy lands with the 128-byte swizzle so that ldmatrix reads are free of
-//    bank conflicts.  Every copy targets this CTA's own shared memory only.
+//  * "Tile" = one page of one stored head of one row: a K tile and a V tile of
+//    page_size x head_dim elements, each contiguous in the pool (32 KiB at
+//    page 128, head_dim 128, 16-bit).  Tiles are numbered row-major over
+//    (row b, stored head h, logical page).
+//  * SMs do not all pull the same bandwidth, so equal static shares leave the
+//    fast ones idle at the end (measured: exits spread over 150..190 us).  The
+//    flat tile range is therefore cut into "units" of decreasing size (eight
+//    phases, each covering half of what is left with gridDim.x units) and the
+//    persistent CTAs, one per SM, claim units in order from an atomic counter.
+//  * A unit can start and end in the middle of a (b, h) segment; such a piece
+//    leaves an unnormalised partial (m, l, acc) in the workspace.  A second,
+//    small kernel, launched with programmatic stream serialisation so that its
+//    CTAs are already resident when the main grid drains, merges the partials
+//    of every cut segment in parallel.  (Merging inside the main kernel with
+//    arrival tickets was measured: a fence + atomic round trip costs ~5 us
+//    under a saturated memory system and the merges pile up at the end.)
+//    Segments inside one unit are normalised and written directly.  The unit
+//    counter must be zero on entry and is left zero, so the workspace is
+//    zero-filled once, not per call.
+//  * Warp roles: a scout warp claims units, publishes them to the consumers
+//    and resolves each tile to a pool row through the page table and its
+//    inverse (32 tiles per coalesced read, up to 256 tiles ahead, so the
+//    dependent global loads are off the critical path); an issue warp turns
+//    resolved tiles into TMA tensor copies, one per K or V tile, into a ring
+//    of shared-memory slots.  A copy lands with the 128-byte swizzle so that
+//    ldmatrix reads are free of bank conflicts, and targets this CTA's own
+//    shared memory only.
 //  * Eight consumer warps each own page_size/8 token rows of every tile.  The
 //    GQA group's query heads are the M rows of mma.sync.m16n8k16 (zero padded
 //    to 16), so all query heads of a stored head consume the one staged tile.
 //    Scores stay in registers; the row maximum is a two-step quad shuffle;
 //    probabilities are repacked in place as the A operand of the P.V product.
-//  * Every mbarrier wait is bounded: when the limit is hit the CTA raises
-//    FPKV_STATUS_TIMEOUT, all roles leave their loops, the producer drains the
+//  * Every wait in the kernel is a bounded mbarrier wait (the consumers'
+//    CTA-level barrier included): when a limit is hit the CTA raises
+//    FPKV_STATUS_TIMEOUT, every role leaves its loop, the issue warp drains the
 //    copies it has in flight (again bounded) and the kernel returns.
 //
 // Semantics: the reference's decode mask + FlexAttention call
@@ -41,8 +53,17 @@ namespace fpkv {
 namespace {
 
 constexpr int kConsumerWarps = 8;
-constexpr int kThreads = (kConsumerWarps + 1) * 32;
-constexpr int kMaxBatchPerLaunch = 1024;
+constexpr int kIssueWarp = kConsumerWarps, kScoutWarp = kConsumerWarps + 1;
+constexpr int kThreads = (kConsumerWarps + 2) * 32;
+#ifndef FPKV_PHASES
+#define FPKV_PHASES 6
+#endif
+constexpr int kPhases = FPKV_PHASES;           // unit sizes halve from phase to phase
+constexpr int kDescBlocks = 8;                 // resolved-tile blocks (32 tiles each) between scout and issue warp
+constexpr int kUnitQueue = 8;                  // claimed units in flight between scout and consumers
+constexpr int kClaimAhead = 4;                 // tiles before a unit's start at which the scout claims the unit after it
+constexpr int kMaxGrid = 256;
+constexpr int kMaxBatchPerLaunch = 512;
 constexpr uint32_t kSpinLimit = 1u << 22;      // try_wait attempts before giving up
 constexpr int kSmemBudget = 227 * 1024;
 
@@ -115,22 +136,18 @@ template <> struct Mma<__half> {
         return *reinterpret_cast<uint32_t*>(&v);
     }
 };
-__device__ __forceinline__ void consumer_bar() {           // the 8 consumer warps only
-    asm volatile("bar.sync 1, %0;" ::"n"(kConsumerWarps * 32) : "memory");
-}
-
 // ------------------------------------------------------------ shared layout
 template <int D, int P, int NREP>
 struct Layout {
     static constexpr int kTileBytes = P * D * 2;                       // one K or V tile
     static constexpr int kMergeFloats = kConsumerWarps * NREP * (D + 2);
-    static constexpr int kFixedBytes = 2 * kMergeFloats * 4             // double-buffered merge area
-                                       + 2 * 16 * 8                     // mbarriers (<= 16 slots)
-                                       + 16 * 4 + 64;                   // slot flags, abort flag, pad
-    static constexpr int kBatchBytes = (kMaxBatchPerLaunch + 1) * 4 + kMaxBatchPerLaunch * 8;
-    static constexpr int kSlotsFit = (kSmemBudget - 1024 - kFixedBytes - kBatchBytes) / kTileBytes;
+    static constexpr int kBarWords = 80;                                // mbarriers (8 bytes each)
+    static constexpr int kSmallInts = kDescBlocks * 33 + kUnitQueue + 16 + 4 + (kPhases + 1) + 3;
+    static constexpr int kBatchInts = (kMaxBatchPerLaunch + 1) + kMaxBatchPerLaunch + (kPhases * kMaxGrid + 1);
+    static constexpr int kFixedBytes = 2 * kMergeFloats * 4 + kBarWords * 8 + (kSmallInts + kBatchInts) * 4 + 64;
+    static constexpr int kSlotsFit = (kSmemBudget - 1024 - kFixedBytes) / kTileBytes;
     static constexpr int kSlots = (kSlotsFit > 12 ? 12 : kSlotsFit) & ~1;   // K and V alternate: even
-    static constexpr int kSmemBytes = 1024 + kSlots * kTileBytes + kFixedBytes + kBatchBytes;
+    static constexpr int kSmemBytes = 1024 + kSlots * kTileBytes + kFixedBytes;
     static_assert(kSlots >= 4, "ring too small");
 };
 
@@ -142,18 +159,38 @@ struct Params {
     const void* q;
     void* out;
     float* lse;
-    float* ws;                 // partials [gridDim.x][2][NREP][D+2]
-    int* tickets;              // [gridDim.x] arrival counts of cut segments, indexed by first owner; zero between calls
+    int* counters;             // [0] unit counter, zero between calls
+    int4* seginfo;             // [B * Hkv] per segment: first unit, last unit, slot of the first piece | has-empty-units << 1, total tiles
+    float* ws;                 // partials [units][2][NREP][D+2]
     int32_t* status;
     long long q_stride_b, q_stride_h;
     int B, Hkv, n_pages, max_batch;
-    int row_base_k;            // first pool row (in tokens) of plane (layer, K, head 0), relative to the map
-    int rows_per_plane;        // n_pages * P
+    int after_append;          // 1: the preceding kernel on the stream is this library's append and writes only the pool
+    int rows_per_plane;        // n_pages * P: token rows of one (K|V, head) plane
     float scale_log2;
 };
 
-// CTA share [r0, r1) of the flat tile range.
-__device__ __forceinline__ long long share_begin(long long T, int c, int G) { return T * c / G; }
+#ifdef FPKV_PROFILE
+// Development aid: per-CTA time stamps (kernel entry, first unit started, last piece merged, exit).
+__device__ unsigned long long g_cta_times[256][12];
+__device__ __forceinline__ unsigned long long gtime() {
+    unsigned long long t; asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t)); return t;
+}
+#define FPKV_STAMP(i) do { if (tid == 0) g_cta_times[blockIdx.x][i] = gtime(); } while (0)
+#define FPKV_STAMP_LANE0(i) do { if (lane == 0) g_cta_times[blockIdx.x][i] = gtime(); } while (0)
+#else
+#define FPKV_STAMP_LANE0(i) do { } while (0)
+#define FPKV_STAMP(i) do { } while (0)
+#endif
+
+// Unit schedule.  Phase p covers half of the tiles left after phase p-1 (the last one all of them) and
+// is cut into G equal units; unit id u = p * G + j.  ub[u] = first flat tile of unit u, ub[NU] = total;
+// the table is filled once per CTA so that every later use is a shared-memory read.
+__device__ __forceinline__ int unit_of(const int* ub, int NU, int t) {     // ub[u] <= t < ub[u+1], t < ub[NU]
+    int lo = 0, hi = NU;
+    while (hi - lo > 1) { const int mid = (lo + hi) >> 1; if (ub[mid] <= t) lo = mid; else hi = mid; }
+    return lo;
+}
 
 // ------------------------------------------------------------------ kernel
 template <typename T, int D, int P, int NREP, typename PosT>
@@ -167,26 +204,50 @@ decode_tma_kernel(const __grid_constant__ CUtensorMap tmap, const Params prm)
     constexpr int NB = RW / 8;                        // n8 score blocks per warp
     static_assert(RW % 16 == 0, "page_size must be a multiple of 128 rows / 8 warps * 16");
     static_assert(NREP <= 8, "query heads per stored head must fit the lower 8 MMA rows");
+    static_assert(2 * NS + 2 * kDescBlocks + 2 * kUnitQueue + 1 <= L::kBarWords, "barrier area too small");
 
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
     uint8_t* ring = smem;
     float* merge = reinterpret_cast<float*>(ring + NS * kTile);               // [2][W][NREP][D+2]
-    uint64_t* bars = reinterpret_cast<uint64_t*>(merge + 2 * L::kMergeFloats); // full[NS], empty[NS]
-    int* slot_valid = reinterpret_cast<int*>(bars + 32);
-    volatile int* abort_flag = reinterpret_cast<volatile int*>(slot_valid + 16);
-    int* last_flag = const_cast<int*>(reinterpret_cast<volatile int*>(abort_flag) + 1);
-    int* cum = const_cast<int*>(reinterpret_cast<volatile int*>(abort_flag) + 4);   // [B+1] tiles before row b
-    long long* slot_of = reinterpret_cast<long long*>(cum + kMaxBatchPerLaunch + 1 + ((kMaxBatchPerLaunch + 1) & 1));
+    uint64_t* bars = reinterpret_cast<uint64_t*>(merge + 2 * L::kMergeFloats);
+    int* ints = reinterpret_cast<int*>(bars + L::kBarWords);
+    int* dcount = ints;                               // [kDescBlocks] tiles in the block, -1 = end of work
+    int* drow = dcount + kDescBlocks;                 // [kDescBlocks][32] pool row of the K tile, -1 = unmapped page
+    int* uq = drow + kDescBlocks * 32;                // [kUnitQueue] claimed unit ids, -1 = end of work
+    int* slot_valid = uq + kUnitQueue;                // [16] per ring slot
+    volatile int* abort_flag = slot_valid + 16;       // [4]: abort flag, tiles issued so far
+    volatile int* issued = abort_flag + 1;
+    int* pb = const_cast<int*>(abort_flag) + 4;       // [kPhases + 1] phase boundaries
+    int* cum = pb + kPhases + 1;                      // [B + 1] tiles before row b
+    int* slot_of = cum + kMaxBatchPerLaunch + 1;      // [B] slot of row b
+    int* ub = slot_of + kMaxBatchPerLaunch;           // [kPhases * G + 1] first tile of each unit
 
     const int tid = threadIdx.x, warp = tid / 32, lane = tid % 32;
     const int B = prm.B, Hkv = prm.Hkv;
-    const uint32_t full0 = smem_u32(bars), empty0 = smem_u32(bars + NS);
+    const int G = gridDim.x;
+    const int NU = kPhases * G;
+    // Launched with programmatic stream serialisation.  Standalone, nothing may be read before the
+    // preceding kernel is complete.  Behind this library's append kernel (which writes only the pool)
+    // everything up to the first pool read may overlap it; the issue warp waits before its first copy.
+    if (!prm.after_append) asm volatile("griddepcontrol.wait;" ::: "memory");
+    FPKV_STAMP(0);
+#ifdef FPKV_PROFILE
+    if (tid == 0) for (int i = 8; i < 12; ++i) g_cta_times[blockIdx.x][i] = 0;
+#endif
+    const uint32_t full0 = smem_u32(bars), empty0 = full0 + 8 * NS;
+    const uint32_t dfull0 = empty0 + 8 * NS, dempty0 = dfull0 + 8 * kDescBlocks;
+    const uint32_t ufull0 = dempty0 + 8 * kDescBlocks, uempty0 = ufull0 + 8 * kUnitQueue;
+    const uint32_t cbar = uempty0 + 8 * kUnitQueue;   // CTA-level barrier of the consumer warps
 
     // ---- prologue: barriers, per-row page counts, exclusive scan -----------
     if (tid == 0) {
         for (int s = 0; s < NS; ++s) { mbar_init(full0 + 8 * s, 1); mbar_init(empty0 + 8 * s, kConsumerWarps); }
+        for (int s = 0; s < kDescBlocks; ++s) { mbar_init(dfull0 + 8 * s, 1); mbar_init(dempty0 + 8 * s, 1); }
+        for (int s = 0; s < kUnitQueue; ++s) { mbar_init(ufull0 + 8 * s, 1); mbar_init(uempty0 + 8 * s, kConsumerWarps); }
+        mbar_init(cbar, kConsumerWarps);
         *abort_flag = 0;
+        *issued = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     for (int b = tid; b < B; b += kThreads) {
@@ -196,7 +257,7 @@ decode_tma_kernel(const __grid_constant__ CUtensorMap tmap, const Params prm)
         if (slot < 0 || slot >= prm.max_batch) raise_status(prm.status, FPKV_STATUS_BAD_SLOT);
         else if (p < 0 || p / P >= prm.n_pages) raise_status(prm.status, FPKV_STATUS_BAD_POS);
         else npg = (int)(p / P) + 1;
-        slot_of[b] = (npg > 0) ? slot : 0;
+        slot_of[b] = (npg > 0) ? (int)slot : 0;
         cum[b + 1] = npg * Hkv;                        // scanned below
     }
     __syncthreads();
@@ -210,22 +271,30 @@ decode_tma_kernel(const __grid_constant__ CUtensorMap tmap, const Params prm)
             if (i < B) cum[i + 1] = v + carry;
             carry += __shfl_sync(0xffffffffu, v, 31);
         }
-        if (lane == 0) cum[0] = 0;
+        if (lane == 0) {
+            cum[0] = 0;
+            int at = 0;                                // phase p takes half of what is left, the last one all of it
+            for (int p = 0; p < kPhases; ++p) { pb[p] = at; at += (p == kPhases - 1) ? carry - at : (carry - at + 1) / 2; }
+            pb[kPhases] = carry;
+        }
     }
     __syncthreads();
-    const long long Ttot = cum[B];
-    const int G = gridDim.x, cta = blockIdx.x;
+    for (int u = tid; u <= NU; u += kThreads) {
+        const int p = u / G, j = u - p * G;
+        ub[u] = (p >= kPhases) ? pb[kPhases] : pb[p] + (int)((long long)(pb[p + 1] - pb[p]) * j / G);
+    }
+    __syncthreads();
+    asm volatile("griddepcontrol.launch_dependents;");   // the finish kernel may take its seats now
     // rows without any tile (bad slot or position): out = 0, lse = -inf, one CTA per such row
     {
         const int Hq = Hkv * NREP;
         T* out0 = reinterpret_cast<T*>(prm.out);
-        for (int b = cta; b < B; b += G) {
+        for (int b = blockIdx.x; b < B; b += G) {
             if (cum[b + 1] != cum[b]) continue;
             for (int e = tid; e < Hq * D; e += kThreads) out0[(size_t)b * Hq * D + e] = ElemTraits<T>::from_float(0.f);
             for (int e = tid; e < Hq; e += kThreads) prm.lse[(size_t)b * Hq + e] = -INFINITY;
         }
     }
-    const int r0 = (int)share_begin(Ttot, cta, G), r1 = (int)share_begin(Ttot, cta + 1, G);
 
     // Row that owns flat tile t (cum[b] <= t < cum[b+1]); B >= 1 and t < Ttot.
     auto row_of = [&](int t) {
@@ -233,305 +302,404 @@ decode_tma_kernel(const __grid_constant__ CUtensorMap tmap, const Params prm)
         while (hi - lo > 1) { const int mid = (lo + hi) >> 1; if (cum[mid] <= t) lo = mid; else hi = mid; }
         return lo;
     };
+    auto give_up = [&]() {                             // a bounded wait ran out (or another role gave up)
+        if (!*abort_flag) raise_status(prm.status, FPKV_STATUS_TIMEOUT);
+        *abort_flag = 1;
+    };
 
-    if (warp == kConsumerWarps) {
-        // =========================== producer warp ==========================
-        // Lane j of lookup round c resolves tile r0 + 32*c + j: pool row of its
-        // K tile, or -1 when the page is unmapped.  Page ids are read one round
-        // ahead of the inverse-table check, which is read one round ahead of use.
-        auto tile_page = [&](int t, long long& pt_index, int& h) -> bool {   // false: t outside the share
-            if (t >= r1) return false;
-            const int b = row_of(t);
-            const int npg = (cum[b + 1] - cum[b]) / Hkv;
-            const int rel = t - cum[b];
-            h = rel / npg;
-            pt_index = slot_of[b] * prm.n_pages + (rel - h * npg);
-            return true;
-        };
-        auto load_page = [&](int t, int& h, long long& slot_row) -> long long {
-            long long idx;
-            if (!tile_page(t, idx, h)) { slot_row = 0; return -1; }
-            slot_row = idx / prm.n_pages * prm.n_pages;
-            return prm.page_table[idx];
-        };
-        int h_c = 0, h_n = 0, h_nn = 0;
-        long long sr_c, sr_n, sr_nn;
-        long long pg_c = load_page(r0 + lane, h_c, sr_c);
-        long long pg_n = load_page(r0 + 32 + lane, h_n, sr_n);
-        auto check = [&](long long pg, long long slot_row) -> long long {   // -> inverse-table entry (or -1)
-            if (pg < 0) return -1;
-            if (pg >= prm.n_pages) { raise_status(prm.status, FPKV_STATUS_BAD_PAGE); return -1; }
-            return prm.p2l[slot_row + pg];
-        };
-        long long inv_c = check(pg_c, sr_c);
-        uint32_t it = 0;                               // ring position (one per K or V tile)
+    if (warp == kScoutWarp) {
+        // ============================ scout warp ============================
+        // The first unit of a CTA is its own index; later ones come from the grid-wide counter, claimed
+        // only when the issue warp is about to run out of resolved tiles, so that a slow SM does not
+        // hoard work that a fast one could take.
+        uint32_t qn = 0, blk = 0;                      // units published, descriptor blocks written
+        int resolved = 0;                              // tiles handed to the issue warp so far
+        int u = blockIdx.x;
         bool ok = true;
-        for (int base = r0; base < r1 && ok; base += 32) {
-            const long long inv_n = check(pg_n, sr_n);
-            const long long pg_nn = load_page(base + 64 + lane, h_nn, sr_nn);
-            const int n_here = min(32, r1 - base);
-            const int row_k = (inv_c >= 0) ? prm.row_base_k + h_c * prm.rows_per_plane + (int)pg_c * P : -1;
-            for (int j = 0; j < n_here; ++j) {
-                const int rk = __shfl_sync(0xffffffffu, row_k, j);
+        while (ok) {
+            if (u >= NU) {                             // nothing left; the very last claim of the grid rearms the counter
+                if (lane == 0 && u == NU + G - 1) prm.counters[0] = 0;
+                u = -1;
+            }
+            int r0 = 0, r1 = 0;
+            if (u >= 0) { r0 = ub[u]; r1 = ub[u + 1]; }
+            if (u < 0 || r1 > r0) {                    // empty units are skipped without telling anyone
                 if (lane == 0) {
-#pragma unroll
-                    for (int kv = 0; kv < 2; ++kv, ++it) {
-                        const uint32_t s = it % NS, ph = (it / NS) & 1u;
-                        if (!mbar_wait(empty0 + 8 * s, ph ^ 1u, abort_flag)) { ok = false; break; }
-                        slot_valid[s] = rk >= 0;
-                        if (rk >= 0) {
-                            mbar_arrive_expect_tx(full0 + 8 * s, kTile);
-                            tma_load_3d(smem_u32(ring + s * kTile), &tmap, 0,
-                                        rk + kv * Hkv * prm.rows_per_plane, 0, full0 + 8 * s);
-                        } else {
-                            mbar_arrive(full0 + 8 * s);
-                        }
-                    }
+                    const uint32_t s = qn % kUnitQueue, ph = (qn / kUnitQueue) & 1u;
+                    ok = mbar_wait(uempty0 + 8 * s, ph ^ 1u, abort_flag);
+                    if (ok) { uq[s] = u; mbar_arrive(ufull0 + 8 * s); }
                 }
                 ok = __shfl_sync(0xffffffffu, ok, 0);
-                if (!ok) break;
+                ++qn;
             }
-            pg_c = pg_n; sr_c = sr_n; h_c = h_n; inv_c = inv_n;
-            pg_n = pg_nn; sr_n = sr_nn; h_n = h_nn;
+            if (!ok || u < 0) break;
+            for (int base = r0; base < r1 && ok; base += 32) {
+                const int t = base + lane;
+                int row_k = -1;
+                if (t < r1) {
+                    const int b = row_of(t);
+                    const int npg = (cum[b + 1] - cum[b]) / Hkv;
+                    const int rel = t - cum[b];
+                    const int h = rel / npg;
+                    const long long trow = (long long)slot_of[b] * prm.n_pages;
+                    const long long pg = prm.page_table[trow + (rel - h * npg)];
+                    if (pg >= prm.n_pages) raise_status(prm.status, FPKV_STATUS_BAD_PAGE);
+                    else if (pg >= 0 && prm.p2l[trow + pg] >= 0) row_k = h * prm.rows_per_plane + (int)pg * P;
+                }
+                const uint32_t s = blk % kDescBlocks, ph = (blk / kDescBlocks) & 1u;
+                if (lane == 0) ok = mbar_wait(dempty0 + 8 * s, ph ^ 1u, abort_flag);
+                ok = __shfl_sync(0xffffffffu, ok, 0);
+                if (!ok) break;
+                drow[s * 32 + lane] = row_k;
+                if (lane == 0) dcount[s] = min(32, r1 - base);
+                __syncwarp();
+                if (lane == 0) mbar_arrive(dfull0 + 8 * s);
+                ++blk;
+            }
+            if (!ok) break;
+            const int unit_start = resolved;           // position of this unit in the CTA's own tile stream
+            resolved += r1 - r0;
+            // Claim the next unit only when the issue warp is about to begin this one: the CTA then
+            // holds the unit in progress plus one resolved unit, enough to hide the claim and the two
+            // dependent table reads, and no more.
+            if (lane == 0) {
+                uint32_t spins = 0;
+                while (*issued + kClaimAhead < unit_start && !*abort_flag && ++spins < kSpinLimit) __nanosleep(100);
+                ok = spins < kSpinLimit && !*abort_flag;
+                if (ok) u = G + atomicAdd(prm.counters, 1);
+            }
+            ok = __shfl_sync(0xffffffffu, ok, 0);
+            u = __shfl_sync(0xffffffffu, u, 0);
         }
         if (lane == 0) {
-            if (!ok) {
-                if (!*abort_flag) raise_status(prm.status, FPKV_STATUS_TIMEOUT);
-                *abort_flag = 1;
-                // drain: every copy issued has an expect_tx on its full barrier; wait for each once
-                const uint32_t first = it > (uint32_t)NS ? it - NS : 0;
-                for (uint32_t i = first; i < it; ++i) {
-                    const uint32_t s = i % NS, ph = (i / NS) & 1u;
-                    for (uint32_t k = 0; k < kSpinLimit && !mbar_try_wait(full0 + 8 * s, ph); ++k) {}
-                }
+            if (!ok) give_up();
+            else {                                     // end marker for the issue warp
+                const uint32_t s = blk % kDescBlocks, ph = (blk / kDescBlocks) & 1u;
+                if (mbar_wait(dempty0 + 8 * s, ph ^ 1u, abort_flag)) { dcount[s] = -1; mbar_arrive(dfull0 + 8 * s); }
+                else give_up();
             }
         }
+        FPKV_STAMP_LANE0(4);
+        return;
+    }
+
+    if (warp == kIssueWarp) {
+        // ============================ issue warp ============================
+        if (lane != 0) return;
+        if (prm.after_append) asm volatile("griddepcontrol.wait;" ::: "memory");   // the appended rows are in the pool
+        uint32_t it = 0, blk = 0;                      // ring position (one per K or V tile), descriptor block
+        bool ok = true;
+        while (ok) {
+            const uint32_t ds = blk % kDescBlocks, dph = (blk / kDescBlocks) & 1u;
+            if (!mbar_wait(dfull0 + 8 * ds, dph, abort_flag)) { ok = false; break; }
+            const int cnt = dcount[ds];
+            if (cnt < 0) break;
+            for (int j = 0; j < cnt && ok; ++j) {
+                const int rk = drow[ds * 32 + j];
+#pragma unroll
+                for (int kv = 0; kv < 2; ++kv, ++it) {
+                    const uint32_t s = it % NS, ph = (it / NS) & 1u;
+                    if (!mbar_wait(empty0 + 8 * s, ph ^ 1u, abort_flag)) { ok = false; break; }
+                    slot_valid[s] = rk >= 0;
+                    if (rk >= 0) {
+                        mbar_arrive_expect_tx(full0 + 8 * s, kTile);
+                        tma_load_3d(smem_u32(ring + s * kTile), &tmap, 0, rk + kv * Hkv * prm.rows_per_plane, 0,
+                                    full0 + 8 * s);
+                    } else {
+                        mbar_arrive(full0 + 8 * s);
+                    }
+                }
+                *issued = (int)(it >> 1);              // tiles issued so far: paces the scout's claims
+            }
+            mbar_arrive(dempty0 + 8 * ds);
+            ++blk;
+        }
+        if (!ok) {
+            give_up();
+            // drain: every copy issued has an expect_tx on its full barrier; wait for each once
+            const uint32_t first = it > (uint32_t)NS ? it - NS : 0;
+            for (uint32_t i = first; i < it; ++i) {
+                const uint32_t s = i % NS, ph = (i / NS) & 1u;
+                for (uint32_t k = 0; k < kSpinLimit && !mbar_try_wait(full0 + 8 * s, ph); ++k) {}
+            }
+        }
+        FPKV_STAMP_LANE0(6);
         return;
     }
 
     // ============================ consumer warps ============================
+    // While the first tiles are in flight: tell the finish kernel which units hold each segment.
+    for (int sgi = blockIdx.x + G * tid; sgi < B * Hkv; sgi += G * kConsumerWarps * 32) {
+        const int b = sgi / Hkv, h = sgi - b * Hkv;
+        const int npg = (cum[b + 1] - cum[b]) / Hkv;
+        int4 info = make_int4(-1, -1, 0, cum[B]);
+        if (npg > 0) {
+            const int seg0 = cum[b] + h * npg;
+            info.x = unit_of(ub, NU, seg0);
+            info.y = unit_of(ub, NU, seg0 + npg - 1);
+            info.z = ((seg0 <= ub[info.x]) ? 0 : 1) | ((cum[B] < 2 * NU) ? 2 : 0);
+        }
+        __stcg(prm.seginfo + sgi, info);
+    }
     const int g = lane >> 2, tq = lane & 3;            // MMA row group / thread-in-quad
     const T* qbase = reinterpret_cast<const T*>(prm.q);
     T* out = reinterpret_cast<T*>(prm.out);
-    uint32_t it = 0;
+    const int Hq = Hkv * NREP;
+    uint32_t it = 0, qn = 0, nbar = 0;
     int piece = 0;
     bool alive = true;
+    // CTA-level barrier of the consumer warps, bounded like every other wait
+    auto consumer_bar = [&]() -> bool {
+        __syncwarp();
+        if (lane == 0) mbar_arrive(cbar);
+        const bool ok = mbar_wait(cbar, nbar & 1u, abort_flag);
+        ++nbar;
+        return ok;
+    };
 
-    for (int t = r0; t < r1; ++piece) {
-        // ---- piece = part of one (b, h) segment inside this share ----------
-        const int b = row_of(t);
-        const int npg = (cum[b + 1] - cum[b]) / Hkv;
-        const int rel = t - cum[b];
-        const int h = rel / npg, pg0 = rel - h * npg;
-        const int seg0 = cum[b] + h * npg, seg1 = seg0 + npg;
-        const int piece_end = min(seg1, r1);
-        const bool direct = seg0 >= r0 && seg1 <= r1;
-        const int ws_slot = (t == r0) ? 0 : 1;
-        const long long n_keys = load_pos<PosT>(prm.pos, b) + 1;
-
-        // query fragments: rows g < NREP are heads h*NREP + g, the rest zero
-        uint32_t qa[D / 16][2];
+    while (alive) {
+        // ---- next unit claimed by the scout --------------------------------
+        int u;
         {
-            const T* qrow = qbase + b * prm.q_stride_b + (long long)(h * NREP + g) * prm.q_stride_h;
-#pragma unroll
-            for (int kk = 0; kk < D / 16; ++kk) {
-                qa[kk][0] = (g < NREP) ? *reinterpret_cast<const uint32_t*>(qrow + kk * 16 + 2 * tq) : 0u;
-                qa[kk][1] = (g < NREP) ? *reinterpret_cast<const uint32_t*>(qrow + kk * 16 + 8 + 2 * tq) : 0u;
-            }
-        }
-        float m = -INFINITY, l = 0.f;
-        float o[D / 8][2];
-#pragma unroll
-        for (int n = 0; n < D / 8; ++n) { o[n][0] = 0.f; o[n][1] = 0.f; }
-
-        for (int pg = pg0; pg < pg0 + (piece_end - t); ++pg) {
-            // ---------------- S = Q K^T for this warp's RW tokens -----------
-            uint32_t s = it % NS, ph = (it / NS) & 1u;
-            if (!mbar_wait(full0 + 8 * s, ph, abort_flag)) { alive = false; break; }
-            const bool valid = slot_valid[s] != 0;
-            float sc[NB][4];
-#pragma unroll
-            for (int j = 0; j < NB; ++j) { sc[j][0] = sc[j][1] = sc[j][2] = sc[j][3] = 0.f; }
-            if (valid) {
-                const uint32_t kt = smem_u32(ring + s * kTile);
-#pragma unroll
-                for (int j = 0; j < NB; ++j) {
-                    const int row = warp * RW + j * 8 + (lane & 7);
-#pragma unroll
-                    for (int kp = 0; kp < D / 32; ++kp) {              // two k-steps per ldmatrix.x4
-                        const int chunk = kp * 4 + (lane >> 3);        // 16-byte column chunk 0..D/8-1
-                        const uint32_t addr = kt + (chunk >> 3) * (P * 128) + row * 128 +
-                                              (((chunk & 7) ^ (row & 7)) << 4);
-                        uint32_t b0, b1, b2, b3;
-                        ldsm_x4(addr, b0, b1, b2, b3);
-                        Mma<T>::run(sc[j], qa[2 * kp][0], 0u, qa[2 * kp][1], 0u, b0, b1);
-                        Mma<T>::run(sc[j], qa[2 * kp + 1][0], 0u, qa[2 * kp + 1][1], 0u, b2, b3);
-                    }
-                }
-            }
+            const uint32_t s = qn % kUnitQueue, ph = (qn / kUnitQueue) & 1u;
+            if (!mbar_wait(ufull0 + 8 * s, ph, abort_flag)) { alive = false; break; }
+            u = uq[s];
             __syncwarp();
-            if (lane == 0) mbar_arrive(empty0 + 8 * s);
-            ++it;
+            if (lane == 0) mbar_arrive(uempty0 + 8 * s);
+            ++qn;
+        }
+        if (u < 0) break;
+        const int r0 = ub[u], r1 = ub[u + 1];
+        if (qn == 1) FPKV_STAMP(1);
 
-            // ---------------- online softmax (row g only) -------------------
-            uint32_t pa[NB];                                            // packed probabilities, A-operand order
-            if (valid) {
-                const long long n_here = n_keys - (long long)pg * P;    // tokens of this page that exist
-                float mx = -INFINITY;
-#pragma unroll
-                for (int j = 0; j < NB; ++j) {
-#pragma unroll
-                    for (int e = 0; e < 2; ++e) {
-                        const int tok = warp * RW + j * 8 + 2 * tq + e;
-                        const float v = (tok < n_here) ? sc[j][e] * prm.scale_log2 : -INFINITY;
-                        sc[j][e] = v;
-                        mx = fmaxf(mx, v);
-                    }
-                }
-                mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 1));
-                mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 2));
-                const float m_new = fmaxf(m, mx);
-                const float m_ref = (m_new == -INFINITY) ? 0.f : m_new;
-                const float alpha = exp2f(m - m_ref);
-                float psum = 0.f;
-#pragma unroll
-                for (int j = 0; j < NB; ++j) {
-                    const float p0 = exp2f(sc[j][0] - m_ref), p1 = exp2f(sc[j][1] - m_ref);
-                    psum += p0 + p1;
-                    pa[j] = Mma<T>::pack(p0, p1);
-                }
-                l = l * alpha + psum;
-                m = m_new;
-                if (alpha != 1.f) {
-#pragma unroll
-                    for (int n = 0; n < D / 8; ++n) { o[n][0] *= alpha; o[n][1] *= alpha; }
-                }
-            }
+        for (int t = r0; t < r1 && alive; ++piece) {
+            // ---- piece = part of one (b, h) segment inside this unit -------
+            const int b = row_of(t);
+            const int npg = (cum[b + 1] - cum[b]) / Hkv;
+            const int rel = t - cum[b];
+            const int h = rel / npg, pg0 = rel - h * npg;
+            const int seg0 = cum[b] + h * npg, seg1 = seg0 + npg;
+            const int piece_end = min(seg1, r1);
+            const bool direct = seg0 >= r0 && seg1 <= r1;
+            const int ws_slot = (t == r0) ? 0 : 1;
+            const long long n_keys = load_pos<PosT>(prm.pos, b) + 1;
 
-            // ---------------- O += P V --------------------------------------
-            s = it % NS; ph = (it / NS) & 1u;
-            if (!mbar_wait(full0 + 8 * s, ph, abort_flag)) { alive = false; break; }
-            if (valid) {
-                const uint32_t vt = smem_u32(ring + s * kTile);
+            // query fragments: rows g < NREP are heads h*NREP + g, the rest zero
+            uint32_t qa[D / 16][2];
+            {
+                const T* qrow = qbase + b * prm.q_stride_b + (long long)(h * NREP + g) * prm.q_stride_h;
 #pragma unroll
-                for (int ks = 0; ks < RW / 16; ++ks) {                  // 16 tokens per k-step
-                    const int row = warp * RW + ks * 16 + (lane & 15);  // matrices 0/2: tokens 0-7, 1/3: 8-15
-#pragma unroll
-                    for (int np = 0; np < D / 16; ++np) {               // two n8 blocks of head_dim per ldmatrix
-                        const int chunk = np * 2 + (lane >> 4);
-                        const uint32_t addr = vt + (chunk >> 3) * (P * 128) + row * 128 +
-                                              (((chunk & 7) ^ (row & 7)) << 4);
-                        uint32_t b0, b1, b2, b3;
-                        ldsm_x4_t(addr, b0, b1, b2, b3);
-                        float c0[4] = {o[2 * np][0], o[2 * np][1], 0.f, 0.f};
-                        float c1[4] = {o[2 * np + 1][0], o[2 * np + 1][1], 0.f, 0.f};
-                        Mma<T>::run(c0, pa[2 * ks], 0u, pa[2 * ks + 1], 0u, b0, b1);
-                        Mma<T>::run(c1, pa[2 * ks], 0u, pa[2 * ks + 1], 0u, b2, b3);
-                        o[2 * np][0] = c0[0]; o[2 * np][1] = c0[1];
-                        o[2 * np + 1][0] = c1[0]; o[2 * np + 1][1] = c1[1];
-                    }
+                for (int kk = 0; kk < D / 16; ++kk) {
+                    qa[kk][0] = (g < NREP) ? *reinterpret_cast<const uint32_t*>(qrow + kk * 16 + 2 * tq) : 0u;
+                    qa[kk][1] = (g < NREP) ? *reinterpret_cast<const uint32_t*>(qrow + kk * 16 + 8 + 2 * tq) : 0u;
                 }
             }
-            __syncwarp();
-            if (lane == 0) mbar_arrive(empty0 + 8 * s);
-            ++it;
-        }
-        // A warp whose wait ran out still joins the barrier below, so that no
-        // consumer is left waiting for it; all of them then leave together.
-        if (!alive && lane == 0) {
-            if (!*abort_flag) raise_status(prm.status, FPKV_STATUS_TIMEOUT);
-            *abort_flag = 1;
-        }
+            float m = -INFINITY, l = 0.f;
+            float o[D / 8][2];
+#pragma unroll
+            for (int n = 0; n < D / 8; ++n) { o[n][0] = 0.f; o[n][1] = 0.f; }
 
-        // ---- merge the 8 warps' states, then write out or a partial ---------
-        l += __shfl_xor_sync(0xffffffffu, l, 1);
-        l += __shfl_xor_sync(0xffffffffu, l, 2);
-        float* mb = merge + (piece & 1) * L::kMergeFloats;
-        if (alive && g < NREP) {
-            float* dst = mb + (warp * NREP + g) * (D + 2);
-            if (tq == 0) { dst[0] = m; dst[1] = l; }
+            for (int pg = pg0; pg < pg0 + (piece_end - t); ++pg) {
+                // ---------------- S = Q K^T for this warp's RW tokens -------
+                uint32_t s = it % NS, ph = (it / NS) & 1u;
+                if (!mbar_wait(full0 + 8 * s, ph, abort_flag)) { alive = false; break; }
+                const bool valid = slot_valid[s] != 0;
+                float sc[NB][4];
 #pragma unroll
-            for (int n = 0; n < D / 8; ++n)
-                *reinterpret_cast<float2*>(dst + 2 + n * 8 + 2 * tq) = make_float2(o[n][0], o[n][1]);
-        }
-        consumer_bar();
-        if (*abort_flag) break;
-        const int Hq = Hkv * NREP;
-        for (int e = tid; e < NREP * D; e += kConsumerWarps * 32) {
-            const int r = e / D, d = e - r * D;
-            float M = -INFINITY;
+                for (int j = 0; j < NB; ++j) { sc[j][0] = sc[j][1] = sc[j][2] = sc[j][3] = 0.f; }
+                if (valid) {
+                    const uint32_t kt = smem_u32(ring + s * kTile);
 #pragma unroll
-            for (int w = 0; w < kConsumerWarps; ++w) M = fmaxf(M, mb[(w * NREP + r) * (D + 2)]);
-            float Lsum = 0.f, acc = 0.f;
+                    for (int j = 0; j < NB; ++j) {
+                        const int row = warp * RW + j * 8 + (lane & 7);
 #pragma unroll
-            for (int w = 0; w < kConsumerWarps; ++w) {
-                const float* src = mb + (w * NREP + r) * (D + 2);
-                const float mw = src[0];
-                if (mw != -INFINITY) {
-                    const float wgt = exp2f(mw - M);
-                    Lsum += src[1] * wgt;
-                    acc += src[2 + d] * wgt;
-                }
-            }
-            const int hq = h * NREP + r;
-            if (direct) {
-                out[((size_t)b * Hq + hq) * D + d] = ElemTraits<T>::from_float(Lsum > 0.f ? acc / Lsum : 0.f);
-                if (d == 0) prm.lse[(size_t)b * Hq + hq] = Lsum > 0.f ? (M + log2f(Lsum)) * kLn2 : -INFINITY;
-            } else {
-                float* dst = prm.ws + (((size_t)cta * 2 + ws_slot) * NREP + r) * (D + 2);
-                __stcg(dst + 2 + d, acc);
-                if (d == 0) { __stcg(dst, M); __stcg(dst + 1, Lsum); }
-            }
-        }
-        if (!direct) {
-            // Segment cut by share boundaries: publish the partial, take a ticket; the last of the
-            // segment's pieces to arrive merges them all.  The ticket word belongs to the share that
-            // owns the segment's first tile and goes back to zero for the next call.
-            const int c_first = (int)(((long long)(seg0 + 1) * G - 1) / Ttot);
-            const int c_last = (int)(((long long)seg1 * G - 1) / Ttot);
-            __threadfence();
-            consumer_bar();
-            if (tid == 0) {
-                int expected = 0;
-                for (int c = c_first; c <= c_last; ++c)
-                    expected += share_begin(Ttot, c, G) != share_begin(Ttot, c + 1, G);
-                const int prev = atomicAdd(prm.tickets + c_first, 1);
-                *last_flag = (prev + 1 == expected);
-                if (prev + 1 == expected) prm.tickets[c_first] = 0;
-            }
-            consumer_bar();
-            if (*last_flag) {
-                __threadfence();
-                for (int e = tid; e < NREP * D; e += kConsumerWarps * 32) {
-                    const int r = e / D, d = e - r * D;
-                    float M = -INFINITY;
-                    for (int c = c_first; c <= c_last; ++c) {
-                        if (share_begin(Ttot, c, G) == share_begin(Ttot, c + 1, G)) continue;   // empty share
-                        const int slot = (seg0 <= share_begin(Ttot, c, G)) ? 0 : 1;
-                        M = fmaxf(M, __ldcg(prm.ws + (((size_t)c * 2 + slot) * NREP + r) * (D + 2)));
-                    }
-                    float Lsum = 0.f, acc = 0.f;
-                    for (int c = c_first; c <= c_last; ++c) {
-                        if (share_begin(Ttot, c, G) == share_begin(Ttot, c + 1, G)) continue;
-                        const int slot = (seg0 <= share_begin(Ttot, c, G)) ? 0 : 1;
-                        const float* src = prm.ws + (((size_t)c * 2 + slot) * NREP + r) * (D + 2);
-                        const float mc = __ldcg(src);
-                        if (mc != -INFINITY) {
-                            const float wgt = exp2f(mc - M);
-                            Lsum += __ldcg(src + 1) * wgt;
-                            acc += __ldcg(src + 2 + d) * wgt;
+                        for (int kp = 0; kp < D / 32; ++kp) {          // two k-steps per ldmatrix.x4
+                            const int chunk = kp * 4 + (lane >> 3);    // 16-byte column chunk 0..D/8-1
+                            const uint32_t addr = kt + (chunk >> 3) * (P * 128) + row * 128 +
+                                                  (((chunk & 7) ^ (row & 7)) << 4);
+                            uint32_t b0, b1, b2, b3;
+                            ldsm_x4(addr, b0, b1, b2, b3);
+                            Mma<T>::run(sc[j], qa[2 * kp][0], 0u, qa[2 * kp][1], 0u, b0, b1);
+                            Mma<T>::run(sc[j], qa[2 * kp + 1][0], 0u, qa[2 * kp + 1][1], 0u, b2, b3);
                         }
                     }
-                    const int hq = h * NREP + r;
+                }
+                __syncwarp();
+                if (lane == 0) mbar_arrive(empty0 + 8 * s);
+                ++it;
+
+                // ---------------- online softmax (row g only) ---------------
+                uint32_t pa[NB];                                        // packed probabilities, A-operand order
+                if (valid) {
+                    const long long n_here = n_keys - (long long)pg * P;   // tokens of this page that exist
+                    float mx = -INFINITY;
+#pragma unroll
+                    for (int j = 0; j < NB; ++j) {
+#pragma unroll
+                        for (int e = 0; e < 2; ++e) {
+                            const int tok = warp * RW + j * 8 + 2 * tq + e;
+                            const float v = (tok < n_here) ? sc[j][e] * prm.scale_log2 : -INFINITY;
+                            sc[j][e] = v;
+                            mx = fmaxf(mx, v);
+                        }
+                    }
+                    mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 1));
+                    mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, 2));
+                    const float m_new = fmaxf(m, mx);
+                    const float m_ref = (m_new == -INFINITY) ? 0.f : m_new;
+                    const float alpha = exp2f(m - m_ref);
+                    float psum = 0.f;
+#pragma unroll
+                    for (int j = 0; j < NB; ++j) {
+                        const float p0 = exp2f(sc[j][0] - m_ref), p1 = exp2f(sc[j][1] - m_ref);
+                        psum += p0 + p1;
+                        pa[j] = Mma<T>::pack(p0, p1);
+                    }
+                    l = l * alpha + psum;
+                    m = m_new;
+                    if (alpha != 1.f) {
+#pragma unroll
+                        for (int n = 0; n < D / 8; ++n) { o[n][0] *= alpha; o[n][1] *= alpha; }
+                    }
+                }
+
+                // ---------------- O += P V ----------------------------------
+                s = it % NS; ph = (it / NS) & 1u;
+                if (!mbar_wait(full0 + 8 * s, ph, abort_flag)) { alive = false; break; }
+                if (valid) {
+                    const uint32_t vt = smem_u32(ring + s * kTile);
+#pragma unroll
+                    for (int ks = 0; ks < RW / 16; ++ks) {              // 16 tokens per k-step
+                        const int row = warp * RW + ks * 16 + (lane & 15);   // matrices 0/2: tokens 0-7, 1/3: 8-15
+#pragma unroll
+                        for (int np = 0; np < D / 16; ++np) {           // two n8 blocks of head_dim per ldmatrix
+                            const int chunk = np * 2 + (lane >> 4);
+                            const uint32_t addr = vt + (chunk >> 3) * (P * 128) + row * 128 +
+                                                  (((chunk & 7) ^ (row & 7)) << 4);
+                            uint32_t b0, b1, b2, b3;
+                            ldsm_x4_t(addr, b0, b1, b2, b3);
+                            float c0[4] = {o[2 * np][0], o[2 * np][1], 0.f, 0.f};
+                            float c1[4] = {o[2 * np + 1][0], o[2 * np + 1][1], 0.f, 0.f};
+                            Mma<T>::run(c0, pa[2 * ks], 0u, pa[2 * ks + 1], 0u, b0, b1);
+                            Mma<T>::run(c1, pa[2 * ks], 0u, pa[2 * ks + 1], 0u, b2, b3);
+                            o[2 * np][0] = c0[0]; o[2 * np][1] = c0[1];
+                            o[2 * np + 1][0] = c1[0]; o[2 * np + 1][1] = c1[1];
+                        }
+                    }
+                }
+                __syncwarp();
+                if (lane == 0) mbar_arrive(empty0 + 8 * s);
+                ++it;
+            }
+            if (!alive) break;
+
+            // ---- merge the 8 warps' states, then write out or a partial -----
+            l += __shfl_xor_sync(0xffffffffu, l, 1);
+            l += __shfl_xor_sync(0xffffffffu, l, 2);
+            float* mb = merge + (piece & 1) * L::kMergeFloats;
+            if (g < NREP) {
+                float* dst = mb + (warp * NREP + g) * (D + 2);
+                if (tq == 0) { dst[0] = m; dst[1] = l; }
+#pragma unroll
+                for (int n = 0; n < D / 8; ++n)
+                    *reinterpret_cast<float2*>(dst + 2 + n * 8 + 2 * tq) = make_float2(o[n][0], o[n][1]);
+            }
+            if (!consumer_bar()) { alive = false; break; }
+            FPKV_STAMP(2);
+            for (int e = tid; e < NREP * D; e += kConsumerWarps * 32) {
+                const int r = e / D, d = e - r * D;
+                float M = -INFINITY;
+#pragma unroll
+                for (int w = 0; w < kConsumerWarps; ++w) M = fmaxf(M, mb[(w * NREP + r) * (D + 2)]);
+                float Lsum = 0.f, acc = 0.f;
+#pragma unroll
+                for (int w = 0; w < kConsumerWarps; ++w) {
+                    const float* src = mb + (w * NREP + r) * (D + 2);
+                    const float mw = src[0];
+                    if (mw != -INFINITY) {
+                        const float wgt = exp2f(mw - M);
+                        Lsum += src[1] * wgt;
+                        acc += src[2 + d] * wgt;
+                    }
+                }
+                const int hq = h * NREP + r;
+                if (direct) {
                     out[((size_t)b * Hq + hq) * D + d] = ElemTraits<T>::from_float(Lsum > 0.f ? acc / Lsum : 0.f);
                     if (d == 0) prm.lse[(size_t)b * Hq + hq] = Lsum > 0.f ? (M + log2f(Lsum)) * kLn2 : -INFINITY;
+                } else {
+                    float* dst = prm.ws + (((size_t)u * 2 + ws_slot) * NREP + r) * (D + 2);
+                    __stcg(dst + 2 + d, acc);
+                    if (d == 0) { __stcg(dst, M); __stcg(dst + 1, Lsum); }
                 }
             }
+            t = piece_end;
         }
-        t = piece_end;
     }
+    if (!alive) { if (lane == 0) give_up(); return; }
+    FPKV_STAMP(3);
 }
 
+// Second kernel, one CTA per (row b, stored head h) segment.  A segment that unit boundaries cut is
+// merged from the partials its pieces left in the workspace; segments inside one unit were written
+// by the main kernel.  Launched with programmatic stream serialisation: its CTAs may become resident
+// while the main grid is still busy and wait for it in griddepcontrol.wait.  After that it is two
+// rounds of loads (the row's tile counts, then all partials at once) and a store.
+#ifdef FPKV_PROFILE
+__device__ unsigned long long g_fin_times[1024][3];
+#endif
+template <typename T, int D, int NREP>
+__global__ void __launch_bounds__(NREP * D >= 256 ? 256 : NREP * D)
+decode_tma_finish_kernel(const Params prm, int G)
+{
+    const int b = blockIdx.x / prm.Hkv, h = blockIdx.x % prm.Hkv;
+    const int Hq = prm.Hkv * NREP;
+    T* out = reinterpret_cast<T*>(prm.out);
+    asm volatile("griddepcontrol.wait;" ::: "memory");
+#ifdef FPKV_PROFILE
+    if (threadIdx.x == 0) { g_fin_times[blockIdx.x % 1024][0] = gtime(); g_fin_times[blockIdx.x % 1024][1] = 0; g_fin_times[blockIdx.x % 1024][2] = 0; }
+#endif
+    asm volatile("griddepcontrol.launch_dependents;");   // a following kernel launched the same way may take its seats
+    const int4 info = __ldcg(prm.seginfo + blockIdx.x);
+    const int u_first = info.x, u_last = info.y, first_slot = info.z & 1;
+#ifdef FPKV_PROFILE
+    if (threadIdx.x == 0) g_fin_times[blockIdx.x % 1024][1] = gtime();
+#endif
+    if (u_first == u_last) return;                     // inside one unit (written by the main kernel) or no tile
+    const bool maybe_empty = (info.z & 2) != 0;        // only tiny batches have units without tiles
+    const int Ttot = info.w;
+    auto empty_unit = [&](int u) -> bool {             // the main kernel's unit schedule, by arithmetic
+        int at = 0, lo = Ttot, len = 0;
+        const int p = u / G, j = u - p * G;
+#pragma unroll
+        for (int pp = 0; pp < kPhases; ++pp) {
+            const int step = (pp == kPhases - 1) ? Ttot - at : (Ttot - at + 1) / 2;
+            if (pp == p) { lo = at; len = step; }
+            at += step;
+        }
+        return (int)((long long)len * j / G) == (int)((long long)len * (j + 1) / G);
+    };
+    for (int e = threadIdx.x; e < NREP * D; e += blockDim.x) {
+        const int r = e / D, d = e - r * D;
+        float M = -INFINITY, Lsum = 0.f, acc = 0.f;
+#pragma unroll 8
+        for (int c = u_first; c <= u_last; ++c) {
+            if (maybe_empty && empty_unit(c)) continue;                        // an empty unit wrote nothing
+            const float* src = prm.ws + (((size_t)c * 2 + (c == u_first ? first_slot : 0)) * NREP + r) * (D + 2);
+            const float mc = __ldcg(src), lc = __ldcg(src + 1), x = __ldcg(src + 2 + d);
+            const float Mn = fmaxf(M, mc);
+            const float a = (Mn == -INFINITY) ? 0.f : exp2f(M - Mn), w = (mc == -INFINITY) ? 0.f : exp2f(mc - Mn);
+            Lsum = Lsum * a + lc * w;
+            acc = acc * a + x * w;
+            M = Mn;
+        }
+        const int hq = h * NREP + r;
+        out[((size_t)b * Hq + hq) * D + d] = ElemTraits<T>::from_float(Lsum > 0.f ? acc / Lsum : 0.f);
+        if (d == 0) prm.lse[(size_t)b * Hq + hq] = Lsum > 0.f ? (M + log2f(Lsum)) * kLn2 : -INFINITY;
+    }
+#ifdef FPKV_PROFILE
+    if (threadIdx.x == 0) g_fin_times[blockIdx.x % 1024][2] = gtime();
+#endif
+}
 
 // ------------------------------------------------------------------- host
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
@@ -560,7 +728,11 @@ int sm_count() {
     return n;
 }
 
-constexpr size_t kTicketBytes = 1024;              // one int per share (<= 256 SMs)
+constexpr size_t kCounterBytes = 16384;            // [0] unit counter (zero between calls)
+
+size_t partial_bytes(int G, int nrep, int D) {
+    return ((size_t)kPhases * G * 2 * nrep * (D + 2) * sizeof(float) + 255) / 256 * 256;
+}
 
 template <typename T, int D, int P, int NREP, typename PosT>
 int launch_one(const CUtensorMap& map, Params prm, int G, cudaStream_t stream)
@@ -570,8 +742,21 @@ int launch_one(const CUtensorMap& map, Params prm, int G, cudaStream_t stream)
     // per device and idempotent; set on every call so that the library keeps no state
     if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, L::kSmemBytes) != cudaSuccess)
         return FPKV_ELAUNCH;
-    kern<<<G, kThreads, L::kSmemBytes, stream>>>(map, prm);
-    return cudaGetLastError() == cudaSuccess ? FPKV_OK : FPKV_ELAUNCH;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    {
+        cudaLaunchConfig_t cfg = {};
+        cfg.gridDim = dim3(G); cfg.blockDim = dim3(kThreads); cfg.dynamicSmemBytes = L::kSmemBytes; cfg.stream = stream;
+        cfg.attrs = attr; cfg.numAttrs = 1;
+        if (cudaLaunchKernelEx(&cfg, kern, map, prm) != cudaSuccess) return FPKV_ELAUNCH;
+    }
+    // the finish kernel may become resident while the main grid runs; it waits for it on the device
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(prm.B * prm.Hkv); cfg.blockDim = dim3(NREP * D >= 256 ? 256 : NREP * D); cfg.dynamicSmemBytes = 0; cfg.stream = stream;
+    cfg.attrs = attr; cfg.numAttrs = 1;
+    return cudaLaunchKernelEx(&cfg, decode_tma_finish_kernel<T, D, NREP>, prm, G) == cudaSuccess ? FPKV_OK
+                                                                                                  : FPKV_ELAUNCH;
 }
 
 template <typename T, int D, int P, typename PosT>
@@ -595,6 +780,13 @@ int launch_shape(int D, int nrep, const CUtensorMap& map, const Params& prm, int
 
 }  // namespace
 
+#ifdef FPKV_PROFILE
+extern "C" __attribute__((visibility("default"))) int fpkv_debug_cta_times(unsigned long long* host_out) {
+    cudaMemcpyFromSymbol(host_out + 256 * 12, g_fin_times, sizeof(unsigned long long) * 1024 * 3);
+    return (int)cudaMemcpyFromSymbol(host_out, g_cta_times, sizeof(unsigned long long) * 256 * 12);
+}
+#endif
+
 bool decode_tma_supported(const PoolView& pv, int Hq)
 {
     if (pv.dtype != FPKV_BF16 && pv.dtype != FPKV_F16) return false;
@@ -610,13 +802,14 @@ bool decode_tma_supported(const PoolView& pv, int Hq)
 size_t decode_tma_workspace_bytes(int Hq, int Hkv, int D)
 {
     const int nrep = Hq / Hkv;
-    return kTicketBytes + (size_t)sm_count() * 2 * nrep * (D + 2) * sizeof(float);
+    const int G = sm_count() < kMaxGrid ? sm_count() : kMaxGrid;
+    return kCounterBytes + partial_bytes(G, nrep, D) + (size_t)kMaxBatchPerLaunch * Hkv * sizeof(int4);
 }
 
 int launch_decode_tma(const PoolView& pv, int layer, void* out, float* lse, const void* q,
                       long long q_stride_b, long long q_stride_h, const int64_t* batch_idx,
                       const void* pos, int pos_type, int B, int Hq, float sm_scale,
-                      void* workspace, int32_t* status, cudaStream_t stream)
+                      void* workspace, int32_t* status, cudaStream_t stream, bool after_append)
 {
     if (B == 0) return FPKV_OK;
     const int nrep = Hq / pv.H;
@@ -632,7 +825,7 @@ int launch_decode_tma(const PoolView& pv, int layer, void* out, float* lse, cons
                     CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
         return FPKV_ELAUNCH;
 
-    const int G = sm_count() < 256 ? sm_count() : 256;
+    const int G = sm_count() < kMaxGrid ? sm_count() : kMaxGrid;
     const size_t esz = 2;
     for (int b0 = 0; b0 < B; b0 += kMaxBatchPerLaunch) {
         Params prm;
@@ -642,13 +835,15 @@ int launch_decode_tma(const PoolView& pv, int layer, void* out, float* lse, cons
         prm.q = (const char*)q + (size_t)b0 * q_stride_b * esz;
         prm.out = (char*)out + (size_t)b0 * Hq * pv.D * esz;
         prm.lse = lse + (size_t)b0 * Hq;
-        prm.tickets = (int*)workspace;
-        prm.ws = (float*)((char*)workspace + kTicketBytes);
+        prm.counters = (int*)workspace;
+        prm.ws = (float*)((char*)workspace + kCounterBytes);
+        prm.seginfo = (int4*)((char*)workspace + kCounterBytes + partial_bytes(G, nrep, pv.D));
         prm.status = status;
         prm.q_stride_b = q_stride_b; prm.q_stride_h = q_stride_h;
         prm.B = (B - b0 < kMaxBatchPerLaunch) ? B - b0 : kMaxBatchPerLaunch;
         prm.Hkv = pv.H; prm.n_pages = pv.n_pages; prm.max_batch = pv.max_batch;
-        prm.row_base_k = 0; prm.rows_per_plane = pv.n_pages * pv.P;
+        prm.after_append = (after_append && b0 == 0) ? 1 : 0;
+        prm.rows_per_plane = pv.n_pages * pv.P;
         prm.scale_log2 = sm_scale * kLog2e;
         int rc;
         if (pv.dtype == FPKV_BF16)

@@ -15,6 +15,7 @@ LIB_PATH = os.path.join(_HERE, "libfpkv.so")
 FPKV_F32, FPKV_BF16, FPKV_F16 = 0, 1, 2
 FPKV_I32, FPKV_I64 = 0, 1
 DECODE_AUTO, DECODE_PORTABLE, DECODE_TMA = 0, 1, 2
+DECODE_AFTER_APPEND = 4
 STATUS_BAD_SLOT, STATUS_BAD_POS, STATUS_BAD_PAGE, STATUS_TIMEOUT = 1, 2, 4, 8
 
 # every symbol include/fpkv.h declares

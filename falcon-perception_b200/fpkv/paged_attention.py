@@ -255,8 +255,21 @@ class PagedKVCache(KVCacheBase):
             self._workspace = torch.zeros(need.value, dtype=torch.uint8, device=self._dev)
         return self._workspace
 
+    def decode_step(self, layer_id: int, q: Tensor, k: Tensor, v: Tensor, batch_idx: Tensor, input_pos: Tensor,
+                    sm_scale: float | None = None, out: Tensor | None = None, lse: Tensor | None = None):
+        """Append k, v (B,H,1,D) and attend with q (B,Hq,1,D) in one go: what
+        ``Attention.forward`` does per layer in a decode step (``insert_kv``
+        followed by the attention call, ``falcon_perception/model.py:150-162``).
+        Same results as the two separate calls; because the attention kernel
+        knows that the append is what runs right before it, its set-up overlaps
+        the append instead of waiting for it."""
+        B = q.shape[0]
+        self.assign(layer_id, batch_idx, input_pos.reshape(B, 1), k, v)
+        return self.decode_attention(layer_id, q, batch_idx, input_pos, sm_scale, out, lse, _after_append=True)
+
     def decode_attention(self, layer_id: int, q: Tensor, batch_idx: Tensor, input_pos: Tensor,
-                         sm_scale: float | None = None, out: Tensor | None = None, lse: Tensor | None = None):
+                         sm_scale: float | None = None, out: Tensor | None = None, lse: Tensor | None = None,
+                         _after_append: bool = False):
         """One query token per row against keys 0..input_pos[b] of slot
         batch_idx[b].  q (B,Hq,1,D) -> out (B,Hq,1,D) in q's dtype, lse (B,Hq,1)
         fp32.  Call after ``insert_kv`` of the same step, as the model does."""
@@ -268,21 +281,25 @@ class PagedKVCache(KVCacheBase):
         input_pos = input_pos.reshape(-1)
         assert input_pos.shape == (B,), "input_pos must have one entry per row"
         self._require_cuda(q, batch_idx, input_pos)
+        q_in, bi_in, ip_in = q, batch_idx, input_pos
         if batch_idx.dtype != torch.int64:
             batch_idx = batch_idx.to(torch.int64)
         if not input_pos.is_contiguous():
             input_pos = input_pos.contiguous()
         q = self._rows16(q)
+        if q is not q_in or batch_idx is not bi_in or input_pos is not ip_in:
+            _after_append = False                      # a conversion kernel now sits between append and attention
         if out is None:
             out = torch.empty((B, Hq, 1, D), dtype=q.dtype, device=q.device)
         if lse is None:
             lse = torch.empty((B, Hq, 1), dtype=torch.float32, device=q.device)
         ws = self._get_workspace(B, Hq)
         scale = (1.0 / math.sqrt(D)) if sm_scale is None else float(sm_scale)
+        flags = int(self.decode_kernel) | (_lib.DECODE_AFTER_APPEND if _after_append else 0)
         _lib.check(_lib.lib.fpkv_decode_attn(
             ctypes.byref(self._pool), layer_id, out.data_ptr(), lse.data_ptr(), q.data_ptr(), q.stride(0),
             q.stride(1), batch_idx.data_ptr(), input_pos.data_ptr(), _pos_type(input_pos), B, Hq, scale,
-            ws.data_ptr(), ws.numel(), int(self.decode_kernel), self._status_ptr(), _stream(self._dev)),
+            ws.data_ptr(), ws.numel(), flags, self._status_ptr(), _stream(self._dev)),
             "fpkv_decode_attn")
         return out, lse
 

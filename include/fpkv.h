@@ -150,7 +150,7 @@ FPKV_API int fpkv_decode_workspace_bytes(const fpkv_pool* pool, int32_t B, int32
  * Query head hq reads stored head hq / (n_q_heads / pool->n_heads).
  * q: device (B, n_q_heads, 1, head_dim) with element strides q_stride_b/_h.
  * workspace: device, at least fpkv_decode_workspace_bytes() bytes, 16-byte
- * aligned.  Its first 1024 bytes hold arrival counters that must be ZERO on
+ * aligned.  Its first 16 KiB hold work counters that must be ZERO on
  * entry; every call that completes leaves them zero, so zero-fill the
  * workspace once when it is allocated (and again after a call that raised
  * FPKV_STATUS_TIMEOUT).  The rest needs no initialisation.  Two calls that
@@ -164,6 +164,13 @@ FPKV_API int fpkv_decode_workspace_bytes(const fpkv_pool* pool, int32_t B, int32
 #define FPKV_DECODE_AUTO     0
 #define FPKV_DECODE_PORTABLE 1
 #define FPKV_DECODE_TMA      2
+/* OR into flags when the call directly follows fpkv_append_decode of the same
+ * step on the same stream, with nothing enqueued in between: the attention
+ * kernel then starts its set-up (index reads, page-table walk) while the
+ * append is still running and waits for it only before the first pool read.
+ * Never set it after anything else: the kernel would read batch_idx,
+ * input_pos and q before the preceding work is known to be complete. */
+#define FPKV_DECODE_AFTER_APPEND 4
 FPKV_API int fpkv_decode_attn(const fpkv_pool* pool, int32_t layer,
                      void* out, float* lse,
                      const void* q, int64_t q_stride_b, int64_t q_stride_h,

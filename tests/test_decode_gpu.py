@@ -72,10 +72,10 @@ def test_decode_against_oracle(kw, kernel):
     ref_out, ref_lse = orc.decode_attention(o, 0, oq.float(), obidx, opos)
     out, lse = c.decode_attention(0, q, bidx, pos)
     assert_attention_close(out, lse, ref_out, ref_lse, f"{kw}/{kernel}")
-    # scratch contents must not matter: poison the workspace (NaN bit patterns) past its 1 KiB of
-    # arrival counters (which every call leaves at zero) and rerun
+    # scratch contents must not matter: poison the workspace (NaN bit patterns) past its 16 KiB header
+    # (whose counter words every call leaves at zero) and rerun
     assert int(c._workspace[:1024].max().item()) == 0
-    c._workspace[1024:].fill_(255)
+    c._workspace[16384:].fill_(255)
     out2, lse2 = c.decode_attention(0, q, bidx, pos)
     assert torch.equal(out, out2) and torch.equal(lse, lse2)
     # the padding row (slot 0) sees nothing
@@ -173,3 +173,30 @@ def test_kernels_agree_at_config2_size_and_are_deterministic():
         assert_attention_close(out_t[i, :, 0], lse_t[i, :, 0], ref.cpu(), torch.logsumexp(s, -1).reshape(16).cpu(),
                                f"row {i}")
     c.check_status()
+
+
+def test_decode_step_equals_separate_calls():
+    """The fused step (append, then attention whose set-up overlaps the append)
+    gives bit-identical results to insert_kv + paged_attention, step after step."""
+    case = _random_case(515, B=12, lens=[5, 127, 128, 300, 511, 640, 900, 1023, 64, 33, 700, 256], n_pages=160,
+                        max_batch_size=14)
+    ca, slots, bidx, pos, k, v, q = product_from_case(case)
+    cb, *_ = product_from_case(case)
+    o, _, obidx, opos, ok, ov, oq = oracle_from_case(case)
+    g = torch.Generator().manual_seed(1)
+    for step in range(1, 6):
+        kn, vn, qn = (torch.randn(12, n, 1, 128, generator=g).bfloat16() for n in (8, 8, 16))
+        p = pos + step
+        for s_ in slots:
+            ca.reserve(s_, None, 1100); cb.reserve(s_, None, 1100)
+        ca.insert_kv(0, kn.cuda(), vn.cuda(), input_pos=p.view(-1, 1), batch_idx=bidx)
+        out_a, lse_a = paged_attention(qn.cuda(), ca, 0, bidx, p)
+        out_b, lse_b = cb.decode_step(0, qn.cuda(), kn.cuda(), vn.cuda(), bidx, p)
+        assert torch.equal(out_a, out_b) and torch.equal(lse_a, lse_b)
+        assert torch.equal(ca.kv_cache, cb.kv_cache)
+        for s_ in slots:
+            o.reserve(s_, 1100)
+        o.append_decode(0, obidx, p.cpu(), kn, vn)
+        ref_out, ref_lse = orc.decode_attention(o, 0, qn.float(), obidx, p.cpu())
+        assert_attention_close(out_b, lse_b, ref_out, ref_lse, f"step {step}")
+    ca.check_status(); cb.check_status()
