@@ -195,16 +195,19 @@ def run_fpkv(args):
     cache.check_status()
     bytes_timed = sum(step_bytes([L + (first_timed + i) % WINDOW for L in case.lens]) for i in range(K))
 
-    # The decode-attention kernel alone (main kernel + its finish kernel), same positions as the
-    # timed steps, one pair of events per launch on the launching stream: the roofline numerator.
-    attn_ev = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(K)]
+    # The decode-attention call alone (main kernel + its finish kernel), same positions as the timed
+    # steps, K launches back to back between one pair of events on the launching stream: the average
+    # launch duration is the roofline's denominator.  (Events between the launches would serialise what
+    # the kernels overlap on their own, so they bracket the loop, not each launch.)
+    a0, a1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    barrier()
+    a0.record(stream)
     for i in range(K):
         j = (first_timed + i) % NV
-        attn_ev[i][0].record(stream)
         cache.decode_attention(0, q_d[j], bidx, pos_d[(first_timed + i) % WINDOW], out=out, lse=lse)
-        attn_ev[i][1].record(stream)
+    a1.record(stream)
     barrier()
-    attn_ms = sum(a.elapsed_time(b) for a, b in attn_ev) / K
+    attn_ms = a0.elapsed_time(a1) / K
     attn_bytes = bytes_timed / K - 2 * B * 2 * HKV * D * 2          # attention alone: no append traffic
 
     # ---------------- end to end through the public API, host buffers ------
@@ -228,19 +231,38 @@ def run_fpkv(args):
     host_pos = []
     for j in range(NV):                                # the NV distinct step inputs, staged in pinned memory
         hq, hk, hv, hbi, hps = views(in_h[j])
-        hq.copy_(q_h[j]); hk.copy_(k_h[j]); hv.copy_(v_h[j]); hbi.copy_(bidx_h)
+        hq.copy_(q_h[j]); hk.copy_(k_h[j]); hv.copy_(v_h[j]); hbi.copy_(bidx_h); hps.copy_(pos_h[0])
         host_pos.append(hps)
     q_s, k_s, v_s, bidx_s, pos_s = views(in_d)
     out_s = res_d[:nq].view(torch.bfloat16).view(B, HQ, 1, D)
     lse_s = res_d[nq:].view(torch.float32).view(B, HQ, 1)
 
+    # As the reference engine does for decode, the step (copy in, append + attention, copy out) is
+    # captured once per staging buffer in a CUDA graph and replayed; the host writes the step's
+    # positions into pinned memory, replays, and waits for the result.
+    graphs = []
+    if not args.kernels_only:
+        side = torch.cuda.Stream(device)
+        for j in range(NV):
+            side.wait_stream(stream)
+            with torch.cuda.stream(side):              # warm the path on the capture stream first
+                in_d.copy_(in_h[j], non_blocking=True)
+                cache.decode_step(0, q_s, k_s, v_s, bidx_s, pos_s, out=out_s, lse=lse_s)
+                res_h.copy_(res_d, non_blocking=True)
+            side.synchronize()
+            gr = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(gr, stream=side):
+                in_d.copy_(in_h[j], non_blocking=True)
+                cache.decode_step(0, q_s, k_s, v_s, bidx_s, pos_s, out=out_s, lse=lse_s)
+                res_h.copy_(res_d, non_blocking=True)
+            graphs.append(gr)
+        torch.cuda.synchronize(device)
+
     def step_e2e(i):
         j = i % NV
         host_pos[j].copy_(pos_h[i % WINDOW])          # this step's positions, written by the host
-        in_d.copy_(in_h[j], non_blocking=True)
-        cache.decode_step(0, q_s, k_s, v_s, bidx_s, pos_s, out=out_s, lse=lse_s)
-        res_h.copy_(res_d, non_blocking=True)
-        stream.synchronize()                           # the step's result is on the host before the next step
+        graphs[j].replay()
+        torch.cuda.current_stream(device).synchronize()   # the step's result is on the host before the next step
 
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     first_e2e = step
