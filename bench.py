@@ -47,6 +47,9 @@ LEN_LO, LEN_HI = 1024, 8192
 N_PAGES = 65536
 FALLBACK_HBM_GBS = 6650.0
 WINDOW = 64          # positions cycle through L .. L+63
+# dram__bytes_read.sum + dram__bytes_write.sum of one decode_tma_kernel launch on this workload, from the
+# ncu capture summarised in profiles/decode_tma_kernel_config2.md
+NCU_TRAFFIC_BYTES = 1.1868e9
 
 
 def step_bytes(lens_before_append):
@@ -295,6 +298,7 @@ def run_fpkv(args):
 
     if rank == 0:
         peak, peak_src = measured_peak()
+        headline = (args.batch, args.len_lo, args.len_hi) == (BATCH, LEN_LO, LEN_HI)
         achieved = attn_bytes / (attn_ms * 1e-3) / 1e9
         line = {
             "metric": "paged_decode_attn_kv_gbps", "value": bytes_all / (ms_total * 1e-3) / 1e9, "unit": "GB/s",
@@ -313,7 +317,8 @@ def run_fpkv(args):
             "gpu_launches": 3 * K,                       # per rank and step: append, decode attention, its finish kernel
             "roofline": {"bound": "hbm", "kernel": "decode_tma_kernel + decode_tma_finish_kernel (one decode-attention call), timed alone",
                          "achieved": achieved, "peak": peak, "unit": "GB/s", "frac": achieved / peak,
-                         "peak_source": peak_src, "traffic": None, "bytes_per_launch": attn_bytes,
+                         "peak_source": peak_src, "traffic": NCU_TRAFFIC_BYTES if headline else None,
+                         "bytes_per_launch": attn_bytes,
                          "ms_per_launch": attn_ms},
             "clocks": clocks,
         }
