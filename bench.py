@@ -120,11 +120,29 @@ class ClockSampler:
                 "reasons": [n for n, b in self.REASONS if self.bits & b], "samples": len(v)}
 
 
+def rank_seed(rank):
+    """Every rank owns its own pool and its own batch of sequences: shard r of the job is the seeded
+    config-2 draw with seed 2002 + r (rank 0 alone is the single-GPU workload)."""
+    return 2002 + rank
+
+
+def reduce_over_ranks(times_ms, work, device, world):
+    """Whole-job numbers from per-rank ones: a time is the MAX over ranks (the job ends when the slowest
+    rank does), work (bytes, tokens) is the SUM.  The only communication of the benchmark."""
+    import torch.distributed as dist
+    t = torch.tensor(times_ms, dtype=torch.float64, device=device)
+    w = torch.tensor(work, dtype=torch.float64, device=device)
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        dist.all_reduce(w, op=dist.ReduceOp.SUM)
+    return t.tolist(), w.tolist()
+
+
 def build_gpu_workload(rank, device, n_steps, n_pages=N_PAGES, batch=BATCH, len_lo=LEN_LO, len_hi=LEN_HI):
     """Cache with 64 seeded sequences whose context pages hold random values."""
     from fpkv import workloads as wl
     from fpkv.paged_attention import PagedKVCache
-    case = wl.config2_case(B=batch, n_pages=n_pages, len_lo=len_lo, len_hi=len_hi, seed=2002 + rank)
+    case = wl.config2_case(B=batch, n_pages=n_pages, len_lo=len_lo, len_hi=len_hi, seed=rank_seed(rank))
     cache = PagedKVCache(n_pages, P, batch + 1, HKV, D, 1, torch.bfloat16, device)
     cache.free_pages = list(case.free_pages)
     slots = []
@@ -288,13 +306,8 @@ def run_fpkv(args):
     h2d, d2h = in_d.numel(), res_h.numel()
 
     # ---------------- combine ranks: max time, summed work -----------------
-    stats = torch.tensor([ms_total, ms_e2e, attn_ms], dtype=torch.float64, device=device)
-    work = torch.tensor([bytes_timed, bytes_e2e, float(B * K)], dtype=torch.float64, device=device)
-    if world > 1:
-        dist.all_reduce(stats, op=dist.ReduceOp.MAX)
-        dist.all_reduce(work, op=dist.ReduceOp.SUM)
-    ms_total, ms_e2e, attn_ms_max = stats.tolist()
-    bytes_all, bytes_e2e_all, tokens_all = work.tolist()
+    (ms_total, ms_e2e, attn_ms_max), (bytes_all, bytes_e2e_all, tokens_all) = reduce_over_ranks(
+        [ms_total, ms_e2e, attn_ms], [bytes_timed, bytes_e2e, float(B * K)], device, world)
 
     if rank == 0:
         peak, peak_src = measured_peak()
