@@ -70,6 +70,7 @@ const char* fpkv_strerror(int code) {
         case FPKV_ELAUNCH: return "CUDA error at kernel launch";
         case FPKV_EWORKSPACE: return "workspace too small";
         case FPKV_EDTYPE: return "dtype not supported by this entry point";
+        case FPKV_ESTATIC: return "request needs more scratch than the library's built-in static array holds";
     }
     return "unknown fpkv error code";
 }

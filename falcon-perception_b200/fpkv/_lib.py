@@ -16,11 +16,13 @@ FPKV_F32, FPKV_BF16, FPKV_F16 = 0, 1, 2
 FPKV_I32, FPKV_I64 = 0, 1
 DECODE_AUTO, DECODE_PORTABLE, DECODE_TMA = 0, 1, 2
 DECODE_AFTER_APPEND = 4
+STATIC_SCRATCH_BYTES = 4 << 20
+ESTATIC = -8
 STATUS_BAD_SLOT, STATUS_BAD_POS, STATUS_BAD_PAGE, STATUS_TIMEOUT = 1, 2, 4, 8
 
 # every symbol include/fpkv.h declares
 EXPORTS = ("fpkv_version", "fpkv_strerror", "fpkv_append_decode", "fpkv_append_packed", "fpkv_gather",
-           "fpkv_decode_workspace_bytes", "fpkv_decode_attn")
+           "fpkv_decode_workspace_bytes", "fpkv_decode_attn", "fpkv_decode_attn_static")
 
 
 class FpkvPool(ctypes.Structure):
@@ -61,6 +63,8 @@ def _load():
     lib.fpkv_decode_attn.restype = ctypes.c_int
     lib.fpkv_decode_attn.argtypes = [pool, i32, vp, vp, vp, i64, i64, vp, vp, i32, i32, i32, f32, vp,
                                      ctypes.c_size_t, i32, vp, vp]
+    lib.fpkv_decode_attn_static.restype = ctypes.c_int
+    lib.fpkv_decode_attn_static.argtypes = [pool, i32, vp, vp, vp, i64, i64, vp, vp, i32, i32, i32, f32, vp, vp]
     return lib
 
 

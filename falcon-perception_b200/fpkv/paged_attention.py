@@ -303,6 +303,33 @@ class PagedKVCache(KVCacheBase):
             "fpkv_decode_attn")
         return out, lse
 
+    def decode_attention_noalloc(self, layer_id: int, q: Tensor, batch_idx: Tensor, input_pos: Tensor,
+                                 out: Tensor, lse: Tensor, sm_scale: float | None = None):
+        """``decode_attention`` for code that must not allocate on the device:
+        an engine whose page pool already holds all free HBM, a decode loop
+        that cannot take ``cudaMalloc``'s device-wide stall, a host whose
+        memory manager forbids it.  Nothing is allocated here, by torch or by
+        CUDA: the caller passes ``out`` (B,Hq,1,D) and ``lse`` (B,Hq,1) and
+        already-typed index tensors (int64 ``batch_idx``, contiguous int32 or
+        int64 ``input_pos``), and the kernel's scratch is a 4 MiB array built
+        into the library and shared by every call on this GPU -- so calls that
+        overlap on the GPU race, and head layouts that need more scratch
+        (head_dim 128 with more than 4 query heads per stored head) are refused."""
+        B, Hq, S, D = q.shape
+        assert S == 1 and D == self.head_dim and Hq % self.n_heads == 0 and q.dtype == self.dtype
+        assert batch_idx.dtype == torch.int64 and batch_idx.shape == (B,) and batch_idx.is_contiguous()
+        input_pos = input_pos.view(-1)
+        assert input_pos.shape == (B,) and input_pos.is_contiguous()
+        assert tuple(out.shape) == (B, Hq, 1, D) and out.is_contiguous() and out.dtype == q.dtype
+        assert tuple(lse.shape) == (B, Hq, 1) and lse.is_contiguous() and lse.dtype == torch.float32
+        self._require_cuda(q, batch_idx, input_pos, out, lse)
+        scale = (1.0 / math.sqrt(D)) if sm_scale is None else float(sm_scale)
+        _lib.check(_lib.lib.fpkv_decode_attn_static(
+            ctypes.byref(self._pool), layer_id, out.data_ptr(), lse.data_ptr(), q.data_ptr(), q.stride(0),
+            q.stride(1), batch_idx.data_ptr(), input_pos.data_ptr(), _pos_type(input_pos), B, Hq, scale,
+            self._status_ptr(), _stream(self._dev)), "fpkv_decode_attn_static")
+        return out, lse
+
     # ------------------------------------------------------------ mask builders
     def create_causal_blockmask(self, B: int, L: int) -> CausalDecodeMask:
         """Logical causal mask for decode steps with page_size blocks."""

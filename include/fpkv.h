@@ -179,6 +179,40 @@ FPKV_API int fpkv_decode_attn(const fpkv_pool* pool, int32_t layer,
                      void* workspace, size_t workspace_bytes, int32_t flags,
                      int32_t* status, void* stream);
 
+/*
+ * fpkv_decode_attn without the workspace argument, for callers that cannot
+ * allocate device memory.  It has no counterpart in the reference.
+ *
+ * Who needs it: an engine that gave all free HBM to its page pool at start-up
+ * and so has nothing to cudaMalloc from later; a decode loop that must not
+ * call cudaMalloc because that call synchronises the whole device; a host that
+ * runs this library under its own memory manager and allows no allocation in
+ * plugin code.  The scratch is a fixed array of FPKV_STATIC_SCRATCH_BYTES
+ * inside the library image: every GPU that loads libfpkv.so holds it until
+ * the process exits.  The call itself allocates and frees nothing.
+ *
+ * Arguments, results and error codes are those of fpkv_decode_attn with the
+ * TMA + tensor-core kernel forced (16-bit pool, page_size 128, head_dim
+ * 64/128, 1/2/4/8 query heads per stored head; FPKV_ESHAPE otherwise).
+ * A head layout whose scratch need exceeds FPKV_STATIC_SCRATCH_BYTES is
+ * refused with FPKV_ESTATIC (at head_dim 128: more than 4 query heads per
+ * stored head).  There is no FPKV_DECODE_AFTER_APPEND mode.
+ *
+ * The first call on each GPU looks up the array's device address (with that
+ * GPU current) and keeps it; make that first call before any stream capture.
+ * All calls on a GPU share the one array, which keeps the last call's
+ * contents; the words that must be zero are cleared at the head of each call.
+ * Calls that overlap on the same GPU race on it: issue them in order.
+ */
+#define FPKV_STATIC_SCRATCH_BYTES (4u << 20)
+#define FPKV_ESTATIC    -8   /* needs more scratch than the built-in array has */
+FPKV_API int fpkv_decode_attn_static(const fpkv_pool* pool, int32_t layer,
+                                     void* out, float* lse,
+                                     const void* q, int64_t q_stride_b, int64_t q_stride_h,
+                                     const int64_t* batch_idx, const void* input_pos, int32_t pos_type,
+                                     int32_t B, int32_t n_q_heads, float sm_scale,
+                                     int32_t* status, void* stream);
+
 #ifdef __cplusplus
 }
 #endif
