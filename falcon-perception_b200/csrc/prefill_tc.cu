@@ -1,0 +1,502 @@
+// Paged prefill / chunked-prefill attention on the 5th-generation tensor cores
+// (tcgen05.mma, accumulators in tensor memory) for 16-bit pools, page_size 128,
+// head_dim 128.
+//
+// Mask.  The reference's prefill mask (falcon_perception/paged_attention.py:343-362,
+// falcon_perception/attention.py:75-96) lets query t see key u of the same
+// sequence iff u <= t, or t and u lie in the same image span.  An image span
+// is a contiguous run of positions that contains t, so the visible set of a
+// query is always a PREFIX of its own sequence: [0, extent_t) with
+//     extent_t = pos_t + 1                      outside an image span,
+//     extent_t = end of t's image span          inside one.
+// The host passes extent_t per packed token (0 for pad tokens) and the kernel
+// needs nothing else: block sparsity is "key tiles below ceil(max extent/128)",
+// the element mask is "key position < extent of the row".
+//
+// Keys and values are read from the page pool through the page table (the
+// sequence's K/V, including the later positions of an image span, must have
+// been appended before its queries run), so the same kernel serves a whole
+// prompt, a chunk of one, or a step that mixes both.
+//
+// One CTA = one 128-row query tile of one query head.  Warps 0-3 (128 threads,
+// thread i owns query row i = TMEM lane i) do the online softmax; warp 4 is the
+// TMA producer; warp 5 issues the MMAs:
+//     S = Q K^T    128x128x128, A = Q (shared, K-major), B = K tile (shared, K-major) -> TMEM
+//     O += P V     128x128x128, A = P (shared, K-major), B = V tile (shared, MN-major) -> TMEM
+// S is double-buffered in TMEM so that the scores of tile j+1 are computed
+// while the softmax of tile j runs.  The running maximum is only raised when a
+// tile exceeds it by more than 2^8 (probabilities stay below 256, exact in
+// fp32 and harmless in bf16), so O in TMEM is rarely rescaled.
+// Every wait is a bounded mbarrier wait; on expiry the CTA raises
+// FPKV_STATUS_TIMEOUT, every role leaves its loop, TMEM is freed and the
+// kernel returns.
+
+#include <cuda.h>
+#include "common.cuh"
+
+namespace fpkv {
+namespace {
+
+constexpr int kTileM = 128, kTileN = 128, kHeadDim = 128, kPage = 128;
+constexpr int kTileBytes = 128 * 128 * 2;              // any 128 x 128 16-bit tile
+constexpr int kHalfBytes = kTileBytes / 2;             // 64 columns (128 bytes) x 128 rows
+constexpr int kStages = 2;
+constexpr int kSoftmaxWarps = 4, kLoadWarp = 4, kMmaWarp = 5;
+constexpr int kPrefillThreads = 6 * 32;
+constexpr int kMaxKeyTiles = 512;                      // 65 536 keys per sequence
+constexpr uint32_t kSpin = 1u << 22;
+constexpr uint32_t kTmemCols = 512;                    // S0 [0,128) S1 [128,256) O [256,384)
+constexpr float kRescaleThreshold = 8.f;
+
+__device__ __forceinline__ uint32_t s32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+__device__ __forceinline__ void bar_init(uint32_t bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count));
+}
+__device__ __forceinline__ void bar_arrive(uint32_t bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void bar_expect_tx(uint32_t bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ uint32_t bar_try(uint32_t bar, uint32_t parity) {
+    uint32_t ok;
+    asm volatile("{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\tselp.u32 %0, 1, 0, p;\n\t}"
+                 : "=r"(ok) : "r"(bar), "r"(parity) : "memory");
+    return ok;
+}
+__device__ __forceinline__ bool bar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag) {
+    for (uint32_t i = 0; i < kSpin; ++i) {
+        if (bar_try(bar, parity)) return true;
+        if ((i & 255u) == 255u && *abort_flag) return false;
+    }
+    return false;
+}
+__device__ __forceinline__ void tma_3d(uint32_t dst, const CUtensorMap* map, int c0, int c1, int c2, uint32_t bar) {
+    asm volatile("cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4}], [%5];"
+                 ::"r"(dst), "l"(map), "r"(c0), "r"(c1), "r"(c2), "r"(bar) : "memory");
+}
+__device__ __forceinline__ void tma_4d(uint32_t dst, const CUtensorMap* map, int c0, int c1, int c2, int c3, uint32_t bar) {
+    asm volatile("cp.async.bulk.tensor.4d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4, %5}], [%6];"
+                 ::"r"(dst), "l"(map), "r"(c0), "r"(c1), "r"(c2), "r"(c3), "r"(bar) : "memory");
+}
+
+// ---- tcgen05 --------------------------------------------------------------
+// Shared-memory operand descriptor, 128-byte swizzle, version 1 (sm_100).
+//   K-major tile  (rows of 128 bytes = 64 elements of the contraction dim):
+//       SBO = 1024 (8 rows), LBO unused.
+//   MN-major tile (rows of 128 bytes = 64 elements of the M/N dim, one row per contraction index):
+//       SBO = 1024 (8 contraction indices), LBO = distance between 64-element column groups.
+__device__ __forceinline__ uint64_t umma_desc(uint32_t smem_addr, uint32_t lbo_bytes, uint32_t sbo_bytes) {
+    uint64_t d = 0;
+    d |= (uint64_t)((smem_addr & 0x3FFFF) >> 4);
+    d |= (uint64_t)((lbo_bytes >> 4) & 0x3FFF) << 16;
+    d |= (uint64_t)((sbo_bytes >> 4) & 0x3FFF) << 32;
+    d |= (uint64_t)1 << 46;                            // descriptor version
+    d |= (uint64_t)2 << 61;                            // SWIZZLE_128B
+    return d;
+}
+// Instruction descriptor for kind::f16: D = f32, A/B = bf16 or f16, M = 128, N = 128.
+__device__ __forceinline__ uint32_t umma_idesc(bool bf16, bool b_mn_major) {
+    uint32_t d = 0;
+    d |= 1u << 4;                                      // accumulator format f32
+    d |= (bf16 ? 1u : 0u) << 7;                        // A format
+    d |= (bf16 ? 1u : 0u) << 10;                       // B format
+    d |= (b_mn_major ? 1u : 0u) << 16;                 // B major: 0 = K, 1 = MN
+    d |= (uint32_t)(kTileN >> 3) << 17;
+    d |= (uint32_t)(kTileM >> 4) << 24;
+    return d;
+}
+__device__ __forceinline__ void umma(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
+    asm volatile("{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+                 "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+                 ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate) : "memory");
+}
+__device__ __forceinline__ void umma_commit(uint32_t bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+// 32 lanes x 32 columns of 32-bit: thread t of the warp gets lane (warp%4)*32 + t, columns [col, col+32)
+__device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
+    asm volatile("tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+                 "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,"
+                 "%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+                   "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]),
+                   "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),
+                   "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+                 : "r"(taddr) : "memory");
+    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_st32(uint32_t taddr, const uint32_t (&r)[32]) {
+    asm volatile("tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], "
+                 "{%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,"
+                 "%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31,%32};"
+                 ::"r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]),
+                   "r"(r[8]), "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15]),
+                   "r"(r[16]), "r"(r[17]), "r"(r[18]), "r"(r[19]), "r"(r[20]), "r"(r[21]), "r"(r[22]), "r"(r[23]),
+                   "r"(r[24]), "r"(r[25]), "r"(r[26]), "r"(r[27]), "r"(r[28]), "r"(r[29]), "r"(r[30]), "r"(r[31])
+                 : "memory");
+    asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
+}
+
+struct PrefillParams {
+    const int64_t* page_table;
+    const int64_t* p2l;
+    const int64_t* batch_idx;   // [L] slot of each packed token (0 = pad)
+    const int32_t* extent;      // [L] number of visible keys of each packed token
+    void* out;                  // (Hq, L, D) contiguous
+    float* lse;                 // (Hq, L)
+    int32_t* status;
+    int L, Hq, Hkv, n_pages, max_batch;
+    int rows_per_plane;         // n_pages * page_size
+    float scale_log2;
+    int is_bf16;
+};
+
+template <typename T>
+__global__ void __launch_bounds__(kPrefillThreads, 1)
+prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constant__ CUtensorMap kv_map,
+                  const PrefillParams prm)
+{
+    extern __shared__ uint8_t smem_raw[];
+    uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+    uint8_t* q_s = smem;                                   // 32 KiB
+    uint8_t* k_s = q_s + kTileBytes;                       // kStages x 32 KiB
+    uint8_t* v_s = k_s + kStages * kTileBytes;             // kStages x 32 KiB
+    uint8_t* p_s = v_s + kStages * kTileBytes;             // 32 KiB
+    uint64_t* bars = reinterpret_cast<uint64_t*>(p_s + kTileBytes);
+    int* ints = reinterpret_cast<int*>(bars + 16);
+    volatile int* abort_flag = ints;                       // [0] abort, [1] TMEM base, [2] tile slot, [3] key tiles
+    int* tmem_slot = ints + 1;
+    int* tile_slot = ints + 2;
+    int* n_key_tiles = ints + 3;
+    int* warp_red = ints + 4;                              // [8] per-warp reductions of the prologue
+    int* page_row = ints + 16;                             // [kMaxKeyTiles] pool row of key tile j (page 0 when unmapped)
+    unsigned char* page_ok = reinterpret_cast<unsigned char*>(page_row + kMaxKeyTiles);   // [kMaxKeyTiles]
+
+    const uint32_t q_full = s32(bars + 0);
+    const uint32_t k_full0 = s32(bars + 1), v_full0 = s32(bars + 3), kv_empty0 = s32(bars + 5);
+    const uint32_t s_full0 = s32(bars + 7), s_free0 = s32(bars + 9);
+    const uint32_t p_full = s32(bars + 11), o_done = s32(bars + 12);
+
+    const int tid = threadIdx.x, warp = tid / 32, lane = tid % 32;
+    const int t0 = blockIdx.x * kTileM;                    // first packed token of the query tile
+    const int hq = blockIdx.y;
+    const int hkv = hq / (prm.Hq / prm.Hkv);
+
+    // ---- prologue ----------------------------------------------------------
+    if (tid == 0) {
+        bar_init(q_full, 1);
+        for (int s = 0; s < kStages; ++s) {
+            bar_init(k_full0 + 8 * s, 1); bar_init(v_full0 + 8 * s, 1); bar_init(kv_empty0 + 8 * s, 1);
+            bar_init(s_full0 + 8 * s, 1); bar_init(s_free0 + 8 * s, kSoftmaxWarps);
+        }
+        bar_init(p_full, kSoftmaxWarps); bar_init(o_done, 1);
+        *abort_flag = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == kMmaWarp) {                                // TMEM allocation is a whole-warp operation
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(s32(tmem_slot)), "r"(kTmemCols) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    // slot and extent of this thread's row; the tile's slot is the largest one (pads are slot 0)
+    int my_slot = 0, my_extent = 0;
+    if (tid < kTileM && t0 + tid < prm.L) {
+        const long long s = prm.batch_idx[t0 + tid];
+        if (s < 0 || s >= prm.max_batch) raise_status(prm.status, FPKV_STATUS_BAD_SLOT);
+        else { my_slot = (int)s; my_extent = s > 0 ? prm.extent[t0 + tid] : 0; }
+        if (my_extent < 0) my_extent = 0;
+    }
+    {
+        int sl = my_slot;
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) sl = max(sl, __shfl_xor_sync(0xffffffffu, sl, o));
+        if (lane == 0 && warp < kSoftmaxWarps) warp_red[warp] = sl;
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const int slot = max(max(warp_red[0], warp_red[1]), max(warp_red[2], warp_red[3]));
+    if (my_slot != 0 && my_slot != slot) {                 // two live sequences in one query tile: not supported
+        raise_status(prm.status, FPKV_STATUS_BAD_SLOT);
+        my_extent = 0;
+    }
+    if ((long long)my_extent > (long long)prm.n_pages * kPage) { raise_status(prm.status, FPKV_STATUS_BAD_POS); my_extent = 0; }
+    {
+        int ex = my_extent;
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) ex = max(ex, __shfl_xor_sync(0xffffffffu, ex, o));
+        if (lane == 0 && warp < kSoftmaxWarps) warp_red[4 + warp] = ex;
+    }
+    __syncthreads();
+    int n_tiles = (max(max(warp_red[4], warp_red[5]), max(warp_red[6], warp_red[7])) + kTileN - 1) / kTileN;
+    if (n_tiles > kMaxKeyTiles) { if (tid == 0) raise_status(prm.status, FPKV_STATUS_BAD_POS); n_tiles = kMaxKeyTiles; }
+    // page ids of all key tiles, resolved once (coalesced) instead of one dependent load per tile
+    for (int j = tid; j < n_tiles; j += kPrefillThreads) {
+        const long long trow = (long long)slot * prm.n_pages;
+        const long long pg = prm.page_table[trow + j];
+        bool ok = pg >= 0 && pg < prm.n_pages;
+        if (pg >= prm.n_pages) raise_status(prm.status, FPKV_STATUS_BAD_PAGE);
+        if (ok) ok = prm.p2l[trow + pg] >= 0;
+        page_row[j] = hkv * prm.rows_per_plane + (ok ? (int)pg : 0) * kPage;   // unmapped: reserved page 0 (finite junk, masked)
+        page_ok[j] = ok;
+    }
+    __syncthreads();
+    const uint32_t tmem = (uint32_t)*tmem_slot;
+    const uint32_t tmem_s0 = tmem, tmem_o = tmem + 256;
+    bool alive = true;
+
+    if (warp == kLoadWarp) {
+        // ============================== TMA producer ========================
+        if (lane == 0 && n_tiles > 0) {
+            bar_expect_tx(q_full, kTileBytes);
+            tma_4d(s32(q_s), &q_map, 0, t0, 0, hq, q_full);
+            for (int j = 0; j < n_tiles; ++j) {
+                const int st = j % kStages;
+                const uint32_t ph = (j / kStages) & 1u;
+                if (!bar_wait(kv_empty0 + 8 * st, ph ^ 1u, abort_flag)) { alive = false; break; }
+                bar_expect_tx(k_full0 + 8 * st, kTileBytes);
+                tma_3d(s32(k_s + st * kTileBytes), &kv_map, 0, page_row[j], 0, k_full0 + 8 * st);
+                bar_expect_tx(v_full0 + 8 * st, kTileBytes);
+                tma_3d(s32(v_s + st * kTileBytes), &kv_map, 0, page_row[j] + prm.Hkv * prm.rows_per_plane, 0, v_full0 + 8 * st);
+            }
+        }
+    } else if (warp == kMmaWarp) {
+        // ============================== MMA issuer ==========================
+        if (lane == 0 && n_tiles > 0) {
+            const uint32_t idesc_qk = umma_idesc(prm.is_bf16 != 0, false);
+            const uint32_t idesc_pv = umma_idesc(prm.is_bf16 != 0, true);
+            auto issue_qk = [&](int j) -> bool {           // S[j % 2] = Q K_j^T
+                const int st = j % kStages;
+                if (!bar_wait(k_full0 + 8 * st, (j / kStages) & 1u, abort_flag)) return false;
+                if (j >= 2 && !bar_wait(s_free0 + 8 * (j & 1), ((j - 2) >> 1) & 1u, abort_flag)) return false;
+                tc_fence_after();
+                const uint32_t a0 = s32(q_s), b0 = s32(k_s + st * kTileBytes);
+#pragma unroll
+                for (int k = 0; k < kHeadDim / 16; ++k) {  // 16 contraction elements = 32 bytes per step
+                    const uint32_t off = (k >> 2) * kHalfBytes + (k & 3) * 32;
+                    umma(tmem_s0 + (j & 1) * kTileN, umma_desc(a0 + off, 0, 1024), umma_desc(b0 + off, 0, 1024),
+                         idesc_qk, k > 0);
+                }
+                umma_commit(s_full0 + 8 * (j & 1));
+                return true;
+            };
+            alive = bar_wait(q_full, 0, abort_flag);
+            if (alive) alive = issue_qk(0);
+            for (int j = 0; j < n_tiles && alive; ++j) {
+                if (j + 1 < n_tiles) { if (!issue_qk(j + 1)) { alive = false; break; } }
+                const int st = j % kStages;
+                if (!bar_wait(p_full, j & 1u, abort_flag)) { alive = false; break; }
+                if (!bar_wait(v_full0 + 8 * st, (j / kStages) & 1u, abort_flag)) { alive = false; break; }
+                tc_fence_after();
+                const uint32_t a0 = s32(p_s), b0 = s32(v_s + st * kTileBytes);
+#pragma unroll
+                for (int k = 0; k < kTileN / 16; ++k) {    // 16 keys per step
+                    const uint32_t a_off = (k >> 2) * kHalfBytes + (k & 3) * 32;      // P is K-major over keys
+                    const uint32_t b_off = k * 16 * 128;                             // V: 16 key rows of 128 bytes
+                    umma(tmem_o, umma_desc(a0 + a_off, 0, 1024), umma_desc(b0 + b_off, kHalfBytes, 1024),
+                         idesc_pv, (j > 0 || k > 0));
+                }
+                umma_commit(o_done);
+                umma_commit(kv_empty0 + 8 * st);
+            }
+        }
+    } else {
+        // ============================== softmax warps =======================
+        const int row = tid;                               // TMEM lane = query row of the tile
+        const uint32_t lane_base = (uint32_t)(warp * 32) << 16;
+        float m_ref = -INFINITY, l = 0.f;
+        uint32_t v[32];
+        for (int j = 0; j < n_tiles && alive; ++j) {
+            if (!bar_wait(s_full0 + 8 * (j & 1), (j >> 1) & 1u, abort_flag)) { alive = false; break; }
+            tc_fence_after();
+            const uint32_t ts = tmem_s0 + (j & 1) * kTileN + lane_base;
+            const int valid_cols = page_ok[j] ? min(kTileN, my_extent - j * kTileN) : 0;   // <= 0: nothing visible
+            // pass 1: row maximum of the visible scores
+            float mx = -INFINITY;
+#pragma unroll 1
+            for (int c4 = 0; c4 < 4; ++c4) {
+                tmem_ld32(ts + c4 * 32, v);
+#pragma unroll
+                for (int c = 0; c < 32; ++c)
+                    if (c4 * 32 + c < valid_cols) mx = fmaxf(mx, __uint_as_float(v[c]) * prm.scale_log2);
+            }
+            // raise the reference maximum only when this tile is far above it
+            const bool raise = mx > m_ref + kRescaleThreshold || (m_ref == -INFINITY && mx > -INFINITY);
+            const bool warp_raise = __any_sync(0xffffffffu, raise);
+            if (j > 0) {                                   // O of tile j-1 complete; P buffer free again
+                if (!bar_wait(o_done, (j - 1) & 1u, abort_flag)) { alive = false; break; }
+                tc_fence_after();
+            }
+            if (warp_raise) {
+                const float m_new = raise ? mx : m_ref;
+                const float alpha = (m_ref == -INFINITY) ? 0.f : exp2f(m_ref - m_new);
+                if (j > 0) {                               // rescale this row of O in tensor memory
+#pragma unroll 1
+                    for (int c4 = 0; c4 < 4; ++c4) {
+                        tmem_ld32(tmem_o + lane_base + c4 * 32, v);
+#pragma unroll
+                        for (int c = 0; c < 32; ++c) v[c] = __float_as_uint(__uint_as_float(v[c]) * alpha);
+                        tmem_st32(tmem_o + lane_base + c4 * 32, v);
+                    }
+                }
+                l *= alpha;
+                m_ref = m_new;
+            }
+            // pass 2: probabilities -> bf16 -> P tile in shared memory (K-major, 128-byte swizzle)
+            float rsum = 0.f;
+            const float m_use = (m_ref == -INFINITY) ? 0.f : m_ref;
+#pragma unroll 1
+            for (int c4 = 0; c4 < 4; ++c4) {
+                tmem_ld32(ts + c4 * 32, v);
+                uint32_t packed[16];
+#pragma unroll
+                for (int c = 0; c < 32; c += 2) {
+                    const float p0 = (c4 * 32 + c < valid_cols) ? exp2f(__uint_as_float(v[c]) * prm.scale_log2 - m_use) : 0.f;
+                    const float p1 = (c4 * 32 + c + 1 < valid_cols) ? exp2f(__uint_as_float(v[c + 1]) * prm.scale_log2 - m_use) : 0.f;
+                    rsum += p0 + p1;
+                    if (prm.is_bf16) { __nv_bfloat162 b = __floats2bfloat162_rn(p0, p1); packed[c / 2] = *reinterpret_cast<uint32_t*>(&b); }
+                    else { __half2 b = __floats2half2_rn(p0, p1); packed[c / 2] = *reinterpret_cast<uint32_t*>(&b); }
+                }
+                // 32 columns = 4 chunks of 16 bytes; chunk index within the 128-byte row is XORed with row % 8
+                uint8_t* prow = p_s + (c4 >> 1) * kHalfBytes + row * 128;
+#pragma unroll
+                for (int q4 = 0; q4 < 4; ++q4) {
+                    const int chunk = (c4 & 1) * 4 + q4;
+                    *reinterpret_cast<uint4*>(prow + ((chunk ^ (row & 7)) << 4)) =
+                        make_uint4(packed[q4 * 4], packed[q4 * 4 + 1], packed[q4 * 4 + 2], packed[q4 * 4 + 3]);
+                }
+            }
+            l += rsum;
+            // hand S[j % 2] back and P over: generic-proxy writes must be visible to the tensor core
+            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) { bar_arrive(s_free0 + 8 * (j & 1)); bar_arrive(p_full); }
+        }
+        // ---- epilogue: O / l -> out, lse --------------------------------------
+        T* out = reinterpret_cast<T*>(prm.out);
+        const int tok = t0 + row;
+        if (n_tiles > 0 && alive) {
+            if (!bar_wait(o_done, (n_tiles - 1) & 1u, abort_flag)) alive = false;
+            tc_fence_after();
+        }
+        if (alive) {
+            const float inv = l > 0.f ? 1.f / l : 0.f;
+#pragma unroll 1
+            for (int c4 = 0; c4 < 4; ++c4) {
+                if (n_tiles > 0) tmem_ld32(tmem_o + lane_base + c4 * 32, v);
+                if (tok < prm.L) {
+                    T* dst = out + ((size_t)hq * prm.L + tok) * kHeadDim + c4 * 32;
+#pragma unroll
+                    for (int c = 0; c < 32; c += 8) {
+                        uint32_t w[4];
+#pragma unroll
+                        for (int e = 0; e < 4; ++e) {
+                            const float a = (n_tiles > 0 && l > 0.f) ? __uint_as_float(v[c + 2 * e]) * inv : 0.f;
+                            const float b = (n_tiles > 0 && l > 0.f) ? __uint_as_float(v[c + 2 * e + 1]) * inv : 0.f;
+                            if (prm.is_bf16) { __nv_bfloat162 x = __floats2bfloat162_rn(a, b); w[e] = *reinterpret_cast<uint32_t*>(&x); }
+                            else { __half2 x = __floats2half2_rn(a, b); w[e] = *reinterpret_cast<uint32_t*>(&x); }
+                        }
+                        *reinterpret_cast<uint4*>(dst + c) = make_uint4(w[0], w[1], w[2], w[3]);
+                    }
+                }
+            }
+            if (tok < prm.L) prm.lse[(size_t)hq * prm.L + tok] = l > 0.f ? (m_ref + log2f(l)) * kLn2 : -INFINITY;
+        }
+    }
+    if (!alive && lane == 0) {
+        if (!*abort_flag) raise_status(prm.status, FPKV_STATUS_TIMEOUT);
+        *abort_flag = 1;
+    }
+    // ---- teardown: everyone meets here, then the allocating warp frees TMEM ---
+    tc_fence_before();
+    __syncthreads();
+    if (warp == kLoadWarp && lane == 0 && *abort_flag) {
+        // copies still in flight target this CTA's shared memory: give them a bounded time to land
+        for (int s = 0; s < kStages; ++s)
+            for (uint32_t k = 0; k < (1u << 16) && !bar_try(k_full0 + 8 * s, 0) && !bar_try(k_full0 + 8 * s, 1); ++k) {}
+    }
+    if (warp == kMmaWarp) {
+        tc_fence_after();
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(kTmemCols) : "memory");
+    }
+}
+
+typedef CUresult (*EncodeFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
+                             const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                             CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+EncodeFn encoder() {
+    static EncodeFn fn = [] {
+        void* p = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) != cudaSuccess ||
+            q != cudaDriverEntryPointSuccess)
+            p = nullptr;
+        return reinterpret_cast<EncodeFn>(p);
+    }();
+    return fn;
+}
+
+constexpr int kPrefillSmem = 1024 + (2 + 2 * kStages) * kTileBytes + 16 * 8 + 16 * 4 + kMaxKeyTiles * 5 + 64;
+
+}  // namespace
+
+bool prefill_tc_supported(const PoolView& pv, int Hq)
+{
+    if (pv.dtype != FPKV_BF16 && pv.dtype != FPKV_F16) return false;
+    if (pv.P != kPage || pv.D != kHeadDim) return false;
+    if (Hq % pv.H) return false;
+    if ((long long)2 * pv.H * pv.n_pages * pv.P >= (1ll << 31)) return false;
+    return encoder() != nullptr;
+}
+
+int launch_prefill_tc(const PoolView& pv, int layer, void* out, float* lse, const void* q, long long q_stride_h,
+                      long long q_stride_t, const int64_t* batch_idx, const int32_t* extent, int L, int Hq,
+                      float sm_scale, int32_t* status, cudaStream_t stream)
+{
+    if (L == 0) return FPKV_OK;
+    const CUtensorMapDataType dt = pv.dtype == FPKV_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
+    CUtensorMap kv_map, q_map;
+    {   // one layer's K and V planes: (64 elements, token rows, head_dim / 64)
+        const cuuint64_t dims[3] = {64, (cuuint64_t)2 * pv.H * pv.n_pages * pv.P, (cuuint64_t)(pv.D / 64)};
+        const cuuint64_t strides[2] = {(cuuint64_t)pv.D * 2, 128};
+        const cuuint32_t box[3] = {64, (cuuint32_t)kPage, (cuuint32_t)(pv.D / 64)};
+        const cuuint32_t es[3] = {1, 1, 1};
+        if (encoder()(&kv_map, dt, 3, pv.plane(layer, 0, 0), dims, strides, box, es, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                      CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                      CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
+            return FPKV_ELAUNCH;
+    }
+    {   // queries: (64 elements, L tokens, head_dim / 64, Hq heads); rows past L read as zeros
+        const cuuint64_t dims[4] = {64, (cuuint64_t)L, (cuuint64_t)(pv.D / 64), (cuuint64_t)Hq};
+        const cuuint64_t strides[3] = {(cuuint64_t)q_stride_t * 2, 128, (cuuint64_t)q_stride_h * 2};
+        const cuuint32_t box[4] = {64, (cuuint32_t)kTileM, (cuuint32_t)(pv.D / 64), 1};
+        const cuuint32_t es[4] = {1, 1, 1, 1};
+        if (encoder()(&q_map, dt, 4, const_cast<void*>(q), dims, strides, box, es, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                      CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                      CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
+            return FPKV_ELAUNCH;
+    }
+    PrefillParams prm;
+    prm.page_table = pv.page_table; prm.p2l = pv.p2l; prm.batch_idx = batch_idx; prm.extent = extent;
+    prm.out = out; prm.lse = lse; prm.status = status;
+    prm.L = L; prm.Hq = Hq; prm.Hkv = pv.H; prm.n_pages = pv.n_pages; prm.max_batch = pv.max_batch;
+    prm.rows_per_plane = pv.n_pages * pv.P;
+    prm.scale_log2 = sm_scale * kLog2e;
+    prm.is_bf16 = pv.dtype == FPKV_BF16;
+    dim3 grid((L + kTileM - 1) / kTileM, Hq);
+    if (pv.dtype == FPKV_BF16) {
+        auto kern = prefill_tc_kernel<__nv_bfloat16>;
+        if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, kPrefillSmem) != cudaSuccess) return FPKV_ELAUNCH;
+        kern<<<grid, kPrefillThreads, kPrefillSmem, stream>>>(q_map, kv_map, prm);
+    } else {
+        auto kern = prefill_tc_kernel<__half>;
+        if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, kPrefillSmem) != cudaSuccess) return FPKV_ELAUNCH;
+        kern<<<grid, kPrefillThreads, kPrefillSmem, stream>>>(q_map, kv_map, prm);
+    }
+    return cudaGetLastError() == cudaSuccess ? FPKV_OK : FPKV_ELAUNCH;
+}
+
+}  // namespace fpkv

@@ -22,7 +22,7 @@ STATUS_BAD_SLOT, STATUS_BAD_POS, STATUS_BAD_PAGE, STATUS_TIMEOUT = 1, 2, 4, 8
 
 # every symbol include/fpkv.h declares
 EXPORTS = ("fpkv_version", "fpkv_strerror", "fpkv_append_decode", "fpkv_append_packed", "fpkv_gather",
-           "fpkv_decode_workspace_bytes", "fpkv_decode_attn", "fpkv_decode_attn_static")
+           "fpkv_decode_workspace_bytes", "fpkv_decode_attn", "fpkv_decode_attn_static", "fpkv_prefill_attn")
 
 
 class FpkvPool(ctypes.Structure):
@@ -63,6 +63,8 @@ def _load():
     lib.fpkv_decode_attn.restype = ctypes.c_int
     lib.fpkv_decode_attn.argtypes = [pool, i32, vp, vp, vp, i64, i64, vp, vp, i32, i32, i32, f32, vp,
                                      ctypes.c_size_t, i32, vp, vp]
+    lib.fpkv_prefill_attn.restype = ctypes.c_int
+    lib.fpkv_prefill_attn.argtypes = [pool, i32, vp, vp, vp, i64, i64, vp, vp, i32, i32, f32, vp, vp]
     lib.fpkv_decode_attn_static.restype = ctypes.c_int
     lib.fpkv_decode_attn_static.argtypes = [pool, i32, vp, vp, vp, i64, i64, vp, vp, i32, i32, i32, f32, vp, vp]
     return lib

@@ -55,10 +55,22 @@ class PrefillMask:
     doc_id: Tensor      # (L,) int32 slot of each token, 0 for pads
     img_id: Tensor      # (L,) int32 running image number, 0 outside image spans
     BLOCK_SIZE: int = 128
+    _extent: Tensor | None = None     # filled on first use, shared by all layers of the step
 
     @property
     def L(self):
         return int(self.doc_id.shape[0])
+
+    def extent(self, input_pos: Tensor) -> Tensor:
+        """Visible-prefix length of every packed token (int32, (L,)): the
+        whole mask in one number per row.  A query sees keys u <= pos of its
+        own sequence, plus every key of its own image span; a span is a
+        contiguous run that contains the query, so the union is the prefix
+        [0, extent) with extent = pos + 1 outside spans and the span's end
+        inside one.  Pads (slot 0) get 0."""
+        if self._extent is None:
+            self._extent = prefill_extents(self.doc_id, self.img_id, input_pos.reshape(-1))
+        return self._extent
 
 
 def image_span_ids(input_ids: Tensor, soi_id: int, eoi_id: int) -> Tensor:
@@ -72,3 +84,17 @@ def image_span_ids(input_ids: Tensor, soi_id: int, eoi_id: int) -> Tensor:
     n_eoi = torch.cumsum(ids == eoi_id, dim=0)
     inside = (n_soi - n_eoi) > 0
     return (n_soi * inside).to(torch.int32)
+
+
+def prefill_extents(doc_id: Tensor, img_id: Tensor, input_pos: Tensor) -> Tensor:
+    """extent[t] for a packed row (see ``PrefillMask.extent``).  Index
+    arithmetic on the tensors' device, no host synchronisation: the end of
+    token t's image span is the last packed index that carries the same image
+    number, found with one scatter-max over the row."""
+    L = doc_id.shape[0]
+    idx = torch.arange(L, device=doc_id.device, dtype=torch.int64)
+    img = img_id.to(torch.int64)
+    last = torch.zeros(L + 1, dtype=torch.int64, device=doc_id.device).scatter_reduce_(0, img, idx, "amax")
+    pos = input_pos.to(torch.int64)
+    ext = torch.where(img > 0, pos + (last[img] - idx) + 1, pos + 1)
+    return torch.where(doc_id > 0, ext, torch.zeros_like(ext)).to(torch.int32)

@@ -303,6 +303,32 @@ class PagedKVCache(KVCacheBase):
             "fpkv_decode_attn")
         return out, lse
 
+    def prefill_attention(self, layer_id: int, q: Tensor, batch_idx: Tensor, input_pos: Tensor, mask: PrefillMask,
+                          sm_scale: float | None = None):
+        """Attention of a packed prefill row (or of a chunk of one) against the
+        pages: q (1,Hq,L,D), batch_idx / input_pos (1,L) as given to
+        ``insert_kv``, ``mask`` from ``create_prefill_blockmask``.  Call it
+        after ``insert_kv`` of the same tokens.  Returns out (1,Hq,L,D) in q's
+        dtype and lse (1,Hq,L) fp32; pad rows give 0 / -inf."""
+        _, Hq, L, D = q.shape
+        assert q.shape[0] == 1 and D == self.head_dim and Hq % self.n_heads == 0 and q.dtype == self.dtype
+        assert batch_idx.shape[-1] == L and input_pos.shape[-1] == L and mask.L == L
+        self._require_cuda(q, batch_idx, input_pos)
+        bi = batch_idx.reshape(-1)
+        if bi.dtype != torch.int64:
+            bi = bi.to(torch.int64)
+        bi = bi if bi.is_contiguous() else bi.contiguous()
+        ext = mask.extent(input_pos)
+        q = self._rows16(q)
+        out = torch.empty((1, Hq, L, D), dtype=q.dtype, device=q.device)
+        lse = torch.empty((1, Hq, L), dtype=torch.float32, device=q.device)
+        scale = (1.0 / math.sqrt(D)) if sm_scale is None else float(sm_scale)
+        _lib.check(_lib.lib.fpkv_prefill_attn(
+            ctypes.byref(self._pool), layer_id, out.data_ptr(), lse.data_ptr(), q.data_ptr(), q.stride(1),
+            q.stride(2), bi.data_ptr(), ext.data_ptr(), L, Hq, scale, self._status_ptr(), _stream(self._dev)),
+            "fpkv_prefill_attn")
+        return out, lse
+
     def decode_attention_noalloc(self, layer_id: int, q: Tensor, batch_idx: Tensor, input_pos: Tensor,
                                  out: Tensor, lse: Tensor, sm_scale: float | None = None):
         """``decode_attention`` for code that must not allocate on the device:
@@ -390,9 +416,13 @@ def paged_attention(q: Tensor, kv_cache: PagedKVCache, layer_id: int, batch_idx:
 
     Decode: q (B,Hq,1,D), batch_idx (B,), input_pos (B,) or (B,1); ``mask`` may
     be the step's DecodeStepMask (its tensors are used when given).
+    Prefill: q (1,Hq,L,D), batch_idx and input_pos (1,L), ``mask`` the
+    PrefillMask of the packed row; keys are read from the pages, so call it
+    after ``insert_kv``.
     """
     if batch_idx.ndim == 1:
         if isinstance(mask, DecodeStepMask):
             batch_idx, input_pos = mask.batch_idx, mask.input_pos
         return kv_cache.decode_attention(layer_id, q, batch_idx, input_pos, sm_scale)
-    raise NotImplementedError("prefill attention entry is not wired yet")
+    assert isinstance(mask, PrefillMask), "prefill needs the mask from create_prefill_blockmask"
+    return kv_cache.prefill_attention(layer_id, q, batch_idx, input_pos, mask, sm_scale)

@@ -180,6 +180,40 @@ FPKV_API int fpkv_decode_attn(const fpkv_pool* pool, int32_t layer,
                      int32_t* status, void* stream);
 
 /*
+ * Paged prefill / chunked-prefill attention over a packed row of L query
+ * tokens.  Replaces create_prefill_blockmask + compiled_flex_attn_prefill
+ * (paged_attention.py:343-362, attention.py:18,75-96, called at
+ * model.py:156-162); unlike the reference, which attends over the fresh k, v,
+ * keys and values are read from the pool through the page table, so it also
+ * serves a chunk of a prompt whose earlier tokens are already cached.
+ *
+ * The reference's mask -- query t sees key u of the same sequence iff u <= t
+ * or both lie in the same image span -- always selects a prefix of the
+ * sequence, because a span is a contiguous run containing t.  The caller
+ * passes that prefix length per token:
+ *   extent[t] = input_pos[t] + 1              for a token outside image spans,
+ *   extent[t] = (position of the span's end)  for a token inside one,
+ *   extent[t] = 0                             for a pad token (batch_idx 0).
+ * Keys 0 .. extent[t]-1 of slot batch_idx[t] must already be in the pool.
+ * Every aligned group of 128 packed tokens may hold tokens of one slot only
+ * (plus pads), which the reference's packing guarantees
+ * (paged_inference.py:634-672); other rows raise FPKV_STATUS_BAD_SLOT.
+ *
+ * q    device (1, n_q_heads, L, head_dim), element strides q_stride_h / _t
+ * out  device (1, n_q_heads, L, head_dim) contiguous, dtype of q
+ * lse  device (1, n_q_heads, L) fp32 natural log; rows without a visible key
+ *      give out = 0, lse = -inf.
+ * Shapes: 16-bit pool, page_size 128, head_dim 128 (tcgen05 tensor-core
+ * kernel); anything else returns FPKV_ESHAPE.  Needs no workspace.
+ */
+FPKV_API int fpkv_prefill_attn(const fpkv_pool* pool, int32_t layer,
+                               void* out, float* lse,
+                               const void* q, int64_t q_stride_h, int64_t q_stride_t,
+                               const int64_t* batch_idx, const int32_t* extent,
+                               int32_t L, int32_t n_q_heads, float sm_scale,
+                               int32_t* status, void* stream);
+
+/*
  * fpkv_decode_attn without the workspace argument, for callers that cannot
  * allocate device memory.  It has no counterpart in the reference.
  *

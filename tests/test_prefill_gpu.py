@@ -1,0 +1,108 @@
+"""GPU: paged prefill attention (tcgen05 kernel) through the C ABI against the
+golden vectors recorded from the reference and against the CPU oracle."""
+
+import numpy as np
+import pytest
+import torch
+
+from fpkv import workloads as wl
+from fpkv.paged_attention import PagedKVCache, paged_attention
+from oracle import paged_kv_oracle as orc
+from helpers import assert_attention_close, golden
+from test_oracle_golden import PREFILL_CASES
+
+pytestmark = pytest.mark.gpu
+T = wl.image_text_tokens
+
+
+def run_product(case, n_pages, max_batch, dtype=torch.bfloat16):
+    c = PagedKVCache(n_pages, case.P, max_batch, case.Hkv, case.D, 1, dtype, "cuda")
+    slots = []
+    for toks in case.seq_tokens:
+        s = c.allocate(); slots.append(s); c.reserve(s, None, len(toks))
+    bidx = case.batch_idx_for(slots).cuda()
+    ipos = case.input_pos.cuda()
+    q, k, v = case.q.to(dtype).cuda(), case.k.to(dtype).cuda(), case.v.to(dtype).cuda()
+    mask = c.create_prefill_blockmask(bidx, case.input_ids.cuda(), wl.IMG_CLS_ID, wl.END_OF_IMG_ID)
+    c.insert_kv(0, k, v, input_pos=ipos, batch_idx=bidx)
+    out, lse = paged_attention(q, c, 0, bidx, ipos, mask)
+    return c, slots, bidx, ipos, mask, out, lse
+
+
+def oracle_prefill(case, slots, dtype=torch.bfloat16):
+    bidx = case.batch_idx_for(slots)
+    img = orc.image_span_ids(case.input_ids, wl.IMG_CLS_ID, wl.END_OF_IMG_ID)
+    q, k, v = (x.to(dtype).float() for x in (case.q, case.k, case.v))
+    return orc.prefill_attention(q, k, v, bidx, img)
+
+
+def compare_live_rows(case, out, lse, ref_out, ref_lse, what):
+    live = case.seq_index.view(-1) > 0
+    assert_attention_close(out[0][:, live], lse[0][:, live], torch.as_tensor(ref_out)[0][:, live],
+                           torch.as_tensor(ref_lse)[0][:, live], what)
+    # pad rows are never consumed; the kernel writes zeros / -inf there
+    if (~live).any():
+        assert out[0][:, ~live].abs().max().item() == 0 and torch.isneginf(lse[0][:, ~live]).all()
+
+
+def test_prefill_against_reference_golden():
+    make, n_pages, mb = PREFILL_CASES["prefill_img_d128"]
+    case = make()
+    g = golden("prefill_img_d128")
+    c, slots, bidx, ipos, mask, out, lse = run_product(case, n_pages, mb)
+    assert slots == g["slots"].tolist()
+    assert out.dtype == torch.bfloat16 and tuple(out.shape) == tuple(case.q.shape) and tuple(lse.shape) == (1, 4, case.L)
+    compare_live_rows(case, out, lse, g["out"], g["lse"], "golden d128")
+    c.check_status()
+
+
+@pytest.mark.parametrize("name,seqs,scale", [
+    ("text_only", [T(0, 0, 300), T(0, 0, 77)], 1.0),
+    ("image_then_text", [T(0, 1024, 63)] * 2, 1.0),                       # the config-3 sequence layout
+    ("config3_scaling", [T(0, 1024, 63)], 128 ** -0.5),
+    ("mixed", [T(3, 100, 20), T(0, 0, 50), T(5, 200, 30) + T(2, 37, 9), T(0, 128, 0), T(1, 129, 1)], 1.0),
+    ("short", [T(0, 0, 1), T(0, 2, 0), T(0, 0, 127), T(0, 0, 128), T(0, 0, 129)], 1.0),
+])
+def test_prefill_against_oracle(name, seqs, scale):
+    case = wl.make_prefill_case(777, seqs, Hq=16, Hkv=8, D=128, P=128, dtype=torch.bfloat16, value_scale=scale)
+    n_pages = sum((len(s) + 127) // 128 for s in seqs) + 2
+    c, slots, bidx, ipos, mask, out, lse = run_product(case, n_pages, len(seqs) + 2)
+    ref_out, ref_lse = oracle_prefill(case, slots)
+    compare_live_rows(case, out, lse, ref_out, ref_lse, name)
+    c.check_status()
+
+
+def test_chunked_prefill_equals_whole_prompt():
+    """Queries of a prompt processed 512 rows at a time against the pages (all K/V appended first, as the
+    bidirectional image span needs) give the rows of the unchunked result; so does a reordered packing."""
+    seqs = [T(0, 1024, 63), T(4, 300, 200)]
+    case = wl.make_prefill_case(4321, seqs, Hq=16, Hkv=8, D=128, P=128, dtype=torch.bfloat16)
+    c, slots, bidx, ipos, mask, out, lse = run_product(case, 24, 4)
+    ext = mask.extent(ipos)
+    q = case.q.cuda()
+    for off, toks, slot in zip(case.offsets, case.seq_tokens, slots):
+        Ls = len(toks)
+        for c0 in range(0, Ls, 512):
+            c1 = min(Ls, c0 + 512)
+            from fpkv.attention import PrefillMask
+            chunk_mask = PrefillMask(mask.doc_id[off + c0:off + c1], mask.img_id[off + c0:off + c1])
+            chunk_mask._extent = ext[off + c0:off + c1].contiguous()       # extents are properties of the tokens
+            o2, l2 = c.prefill_attention(0, q[:, :, off + c0:off + c1], bidx[:, off + c0:off + c1],
+                                         ipos[:, off + c0:off + c1], chunk_mask)
+            assert torch.equal(o2, out[:, :, off + c0:off + c1]) and torch.equal(l2, lse[:, :, off + c0:off + c1])
+    c.check_status()
+
+
+def test_fp16_and_unmapped_rows():
+    case = wl.make_prefill_case(99, [T(0, 40, 100), T(0, 0, 200)], Hq=8, Hkv=8, D=128, dtype=torch.float16)
+    c, slots, bidx, ipos, mask, out, lse = run_product(case, 8, 4, dtype=torch.float16)
+    ref_out, ref_lse = oracle_prefill(case, slots, dtype=torch.float16)
+    compare_live_rows(case, out, lse, ref_out, ref_lse, "fp16")
+    c.check_status()
+    # a slot whose pages were erased has nothing visible: zeros and -inf, no fault
+    c.erase(slots[1])
+    out2, lse2 = paged_attention(case.q.half().cuda(), c, 0, bidx, ipos, mask)
+    off = case.offsets[1]
+    assert out2[0, :, off:off + 200].abs().max().item() == 0 and torch.isneginf(lse2[0, :, off:off + 200]).all()
+    assert torch.equal(out2[0, :, :140], out[0, :, :140])
+    c.check_status()
