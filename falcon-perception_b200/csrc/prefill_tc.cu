@@ -18,15 +18,18 @@
 // been appended before its queries run), so the same kernel serves a whole
 // prompt, a chunk of one, or a step that mixes both.
 //
-// One CTA = one 128-row query tile of one query head.  Warps 0-3 (128 threads,
-// thread i owns query row i = TMEM lane i) do the online softmax; warp 4 is the
-// TMA producer; warp 5 issues the MMAs:
+// One CTA = one 128-row query tile of a PAIR of query heads that share a stored
+// head (a single head when the GQA ratio is odd): the K/V tile staged in shared
+// memory feeds both heads, which halves the L2 traffic per FLOP (a one-head
+// CTA was measured L2-bound at 25 % of tensor peak).  Warps 0-3 and 4-7 are the
+// two heads' softmax groups (thread i owns query row i = TMEM lane i); warp 8
+// is the TMA producer; warp 9 issues the MMAs:
 //     S = Q K^T    128x128x128, A = Q (shared, K-major), B = K tile (shared, K-major) -> TMEM
-//     O += P V     128x128x128, A = P (shared, K-major), B = V tile (shared, MN-major) -> TMEM
-// S is double-buffered in TMEM so that the scores of tile j+1 are computed
-// while the softmax of tile j runs.  The running maximum is only raised when a
-// tile exceeds it by more than 2^8 (probabilities stay below 256, exact in
-// fp32 and harmless in bf16), so O in TMEM is rarely rescaled.
+//     O += P V     128x128x128, A = P (TMEM, written in place over S), B = V tile (shared, MN-major) -> TMEM
+// The heads alternate on the tensor pipe: while one head's softmax runs, the
+// other head's P.V and next Q.K^T execute.  The running maximum is only raised
+// when a tile exceeds it by more than 2^8 (probabilities stay below 256, exact
+// in fp32 and harmless in bf16), so O in TMEM is rarely rescaled.
 // Every wait is a bounded mbarrier wait; on expiry the CTA raises
 // FPKV_STATUS_TIMEOUT, every role leaves its loop, TMEM is freed and the
 // kernel returns.
@@ -41,11 +44,12 @@ constexpr int kTileM = 128, kTileN = 128, kHeadDim = 128, kPage = 128;
 constexpr int kTileBytes = 128 * 128 * 2;              // any 128 x 128 16-bit tile
 constexpr int kHalfBytes = kTileBytes / 2;             // 64 columns (128 bytes) x 128 rows
 constexpr int kStages = 2;
-constexpr int kSoftmaxWarps = 4, kLoadWarp = 4, kMmaWarp = 5;
-constexpr int kPrefillThreads = 6 * 32;
+constexpr int kSoftmaxWarps = 4;                       // per head; two groups (warps 0-3, 4-7) for a head pair
+constexpr int kLoadWarp = 8, kMmaWarp = 9;
+constexpr int kPrefillThreads = 10 * 32;
 constexpr int kMaxKeyTiles = 512;                      // 65 536 keys per sequence
 constexpr uint32_t kSpin = 1u << 22;
-constexpr uint32_t kTmemCols = 512;                    // S0 [0,128) S1 [128,256) O [256,384)
+constexpr uint32_t kTmemCols = 512;                    // S/P head 0, S/P head 1, O head 0, O head 1: 128 columns each
 constexpr float kRescaleThreshold = 8.f;
 
 __device__ __forceinline__ uint32_t s32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
@@ -111,6 +115,12 @@ __device__ __forceinline__ void umma(uint32_t tmem_d, uint64_t adesc, uint64_t b
                  "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
                  ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate) : "memory");
 }
+// A operand from tensor memory (128 lanes x 8 columns of packed 16-bit pairs per K = 16 step), B from shared memory.
+__device__ __forceinline__ void umma_ts(uint32_t tmem_d, uint32_t tmem_a, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
+    asm volatile("{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+                 "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}"
+                 ::"r"(tmem_d), "r"(tmem_a), "l"(bdesc), "r"(idesc), "r"(accumulate) : "memory");
+}
 __device__ __forceinline__ void umma_commit(uint32_t bar) {
     asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
 }
@@ -152,6 +162,7 @@ struct PrefillParams {
     int rows_per_plane;         // n_pages * page_size
     float scale_log2;
     int is_bf16;
+    int heads_per_cta;          // 2: both query heads of a GQA pair share the staged K/V tiles; 1 otherwise
 };
 
 template <typename T>
@@ -161,38 +172,40 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_consta
 {
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-    uint8_t* q_s = smem;                                   // 32 KiB
-    uint8_t* k_s = q_s + kTileBytes;                       // kStages x 32 KiB
+    uint8_t* q_s = smem;                                   // 2 x 32 KiB: the query tile of each head of the pair
+    uint8_t* k_s = q_s + 2 * kTileBytes;                   // kStages x 32 KiB
     uint8_t* v_s = k_s + kStages * kTileBytes;             // kStages x 32 KiB
-    uint8_t* p_s = v_s + kStages * kTileBytes;             // 32 KiB
-    uint64_t* bars = reinterpret_cast<uint64_t*>(p_s + kTileBytes);
+    uint64_t* bars = reinterpret_cast<uint64_t*>(v_s + kStages * kTileBytes);
     int* ints = reinterpret_cast<int*>(bars + 16);
-    volatile int* abort_flag = ints;                       // [0] abort, [1] TMEM base, [2] tile slot, [3] key tiles
+    volatile int* abort_flag = ints;                       // [0] abort, [1] TMEM base
     int* tmem_slot = ints + 1;
-    int* tile_slot = ints + 2;
-    int* n_key_tiles = ints + 3;
     int* warp_red = ints + 4;                              // [8] per-warp reductions of the prologue
     int* page_row = ints + 16;                             // [kMaxKeyTiles] pool row of key tile j (page 0 when unmapped)
     unsigned char* page_ok = reinterpret_cast<unsigned char*>(page_row + kMaxKeyTiles);   // [kMaxKeyTiles]
 
     const uint32_t q_full = s32(bars + 0);
-    const uint32_t k_full0 = s32(bars + 1), v_full0 = s32(bars + 3), kv_empty0 = s32(bars + 5);
-    const uint32_t s_full0 = s32(bars + 7), s_free0 = s32(bars + 9);
-    const uint32_t p_full = s32(bars + 11), o_done = s32(bars + 12);
+    const uint32_t k_full0 = s32(bars + 1), v_full0 = s32(bars + 3), k_empty0 = s32(bars + 5), v_empty0 = s32(bars + 7);
+    const uint32_t s_full0 = s32(bars + 9);                // [2] one per head of the pair
+    const uint32_t p_full0 = s32(bars + 11);               // [2]
+    const uint32_t all_done = s32(bars + 13);
 
     const int tid = threadIdx.x, warp = tid / 32, lane = tid % 32;
     const int t0 = blockIdx.x * kTileM;                    // first packed token of the query tile
-    const int hq = blockIdx.y;
-    const int hkv = hq / (prm.Hq / prm.Hkv);
+    const int heads = prm.heads_per_cta;                   // 1 or 2 query heads of one stored head
+    const int hq0 = blockIdx.y * heads;
+    const int hkv = hq0 / (prm.Hq / prm.Hkv);
+    const int group = warp / kSoftmaxWarps;                // softmax group = which head of the pair (warps 0-3, 4-7)
+    const bool is_softmax = warp < 2 * kSoftmaxWarps;
 
     // ---- prologue ----------------------------------------------------------
     if (tid == 0) {
         bar_init(q_full, 1);
         for (int s = 0; s < kStages; ++s) {
-            bar_init(k_full0 + 8 * s, 1); bar_init(v_full0 + 8 * s, 1); bar_init(kv_empty0 + 8 * s, 1);
-            bar_init(s_full0 + 8 * s, 1); bar_init(s_free0 + 8 * s, kSoftmaxWarps);
+            bar_init(k_full0 + 8 * s, 1); bar_init(v_full0 + 8 * s, 1);
+            bar_init(k_empty0 + 8 * s, 1); bar_init(v_empty0 + 8 * s, 1);
         }
-        bar_init(p_full, kSoftmaxWarps); bar_init(o_done, 1);
+        for (int g = 0; g < 2; ++g) { bar_init(s_full0 + 8 * g, 1); bar_init(p_full0 + 8 * g, kSoftmaxWarps); }
+        bar_init(all_done, 1);
         *abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
@@ -200,12 +213,14 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_consta
         asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(s32(tmem_slot)), "r"(kTmemCols) : "memory");
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
     }
-    // slot and extent of this thread's row; the tile's slot is the largest one (pads are slot 0)
+    // slot and extent of this thread's row (both softmax groups look at the same 128 rows);
+    // the tile's slot is the largest one (pads are slot 0)
+    const int row = tid % kTileM;
     int my_slot = 0, my_extent = 0;
-    if (tid < kTileM && t0 + tid < prm.L) {
-        const long long s = prm.batch_idx[t0 + tid];
+    if (is_softmax && t0 + row < prm.L) {
+        const long long s = prm.batch_idx[t0 + row];
         if (s < 0 || s >= prm.max_batch) raise_status(prm.status, FPKV_STATUS_BAD_SLOT);
-        else { my_slot = (int)s; my_extent = s > 0 ? prm.extent[t0 + tid] : 0; }
+        else { my_slot = (int)s; my_extent = s > 0 ? prm.extent[t0 + row] : 0; }
         if (my_extent < 0) my_extent = 0;
     }
     {
@@ -244,149 +259,163 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_consta
     }
     __syncthreads();
     const uint32_t tmem = (uint32_t)*tmem_slot;
-    const uint32_t tmem_s0 = tmem, tmem_o = tmem + 256;
+    // tensor memory: S/P of head 0 [0,128), S/P of head 1 [128,256), O of head 0 [256,384), O of head 1 [384,512)
     bool alive = true;
 
     if (warp == kLoadWarp) {
         // ============================== TMA producer ========================
         if (lane == 0 && n_tiles > 0) {
-            bar_expect_tx(q_full, kTileBytes);
-            tma_4d(s32(q_s), &q_map, 0, t0, 0, hq, q_full);
+            bar_expect_tx(q_full, heads * kTileBytes);
+            for (int g = 0; g < heads; ++g) tma_4d(s32(q_s + g * kTileBytes), &q_map, 0, t0, 0, hq0 + g, q_full);
             for (int j = 0; j < n_tiles; ++j) {
                 const int st = j % kStages;
                 const uint32_t ph = (j / kStages) & 1u;
-                if (!bar_wait(kv_empty0 + 8 * st, ph ^ 1u, abort_flag)) { alive = false; break; }
+                if (!bar_wait(k_empty0 + 8 * st, ph ^ 1u, abort_flag)) { alive = false; break; }
                 bar_expect_tx(k_full0 + 8 * st, kTileBytes);
                 tma_3d(s32(k_s + st * kTileBytes), &kv_map, 0, page_row[j], 0, k_full0 + 8 * st);
+                if (!bar_wait(v_empty0 + 8 * st, ph ^ 1u, abort_flag)) { alive = false; break; }
                 bar_expect_tx(v_full0 + 8 * st, kTileBytes);
                 tma_3d(s32(v_s + st * kTileBytes), &kv_map, 0, page_row[j] + prm.Hkv * prm.rows_per_plane, 0, v_full0 + 8 * st);
             }
         }
     } else if (warp == kMmaWarp) {
         // ============================== MMA issuer ==========================
+        // The two heads of the pair alternate on the tensor pipe: while one head's softmax runs, the
+        // other head's P.V and next Q.K^T execute, and both use the one staged K / V tile.
         if (lane == 0 && n_tiles > 0) {
             const uint32_t idesc_qk = umma_idesc(prm.is_bf16 != 0, false);
             const uint32_t idesc_pv = umma_idesc(prm.is_bf16 != 0, true);
-            auto issue_qk = [&](int j) -> bool {           // S[j % 2] = Q K_j^T
-                const int st = j % kStages;
-                if (!bar_wait(k_full0 + 8 * st, (j / kStages) & 1u, abort_flag)) return false;
-                if (j >= 2 && !bar_wait(s_free0 + 8 * (j & 1), ((j - 2) >> 1) & 1u, abort_flag)) return false;
-                tc_fence_after();
-                const uint32_t a0 = s32(q_s), b0 = s32(k_s + st * kTileBytes);
+            auto issue_qk = [&](int g, int j) {            // S_g = Q_g K_j^T (K tile already waited for)
+                const uint32_t a0 = s32(q_s + g * kTileBytes), b0 = s32(k_s + (j % kStages) * kTileBytes);
 #pragma unroll
                 for (int k = 0; k < kHeadDim / 16; ++k) {  // 16 contraction elements = 32 bytes per step
                     const uint32_t off = (k >> 2) * kHalfBytes + (k & 3) * 32;
-                    umma(tmem_s0 + (j & 1) * kTileN, umma_desc(a0 + off, 0, 1024), umma_desc(b0 + off, 0, 1024),
-                         idesc_qk, k > 0);
+                    umma(tmem + g * kTileN, umma_desc(a0 + off, 0, 1024), umma_desc(b0 + off, 0, 1024), idesc_qk, k > 0);
                 }
-                umma_commit(s_full0 + 8 * (j & 1));
-                return true;
+                umma_commit(s_full0 + 8 * g);
             };
-            alive = bar_wait(q_full, 0, abort_flag);
-            if (alive) alive = issue_qk(0);
-            for (int j = 0; j < n_tiles && alive; ++j) {
-                if (j + 1 < n_tiles) { if (!issue_qk(j + 1)) { alive = false; break; } }
-                const int st = j % kStages;
-                if (!bar_wait(p_full, j & 1u, abort_flag)) { alive = false; break; }
-                if (!bar_wait(v_full0 + 8 * st, (j / kStages) & 1u, abort_flag)) { alive = false; break; }
-                tc_fence_after();
-                const uint32_t a0 = s32(p_s), b0 = s32(v_s + st * kTileBytes);
+            auto issue_pv = [&](int g, int j) {            // O_g += P_g V_j, P read from tensor memory
+                const uint32_t b0 = s32(v_s + (j % kStages) * kTileBytes);
 #pragma unroll
-                for (int k = 0; k < kTileN / 16; ++k) {    // 16 keys per step
-                    const uint32_t a_off = (k >> 2) * kHalfBytes + (k & 3) * 32;      // P is K-major over keys
-                    const uint32_t b_off = k * 16 * 128;                             // V: 16 key rows of 128 bytes
-                    umma(tmem_o, umma_desc(a0 + a_off, 0, 1024), umma_desc(b0 + b_off, kHalfBytes, 1024),
-                         idesc_pv, (j > 0 || k > 0));
-                }
-                umma_commit(o_done);
-                umma_commit(kv_empty0 + 8 * st);
+                for (int k = 0; k < kTileN / 16; ++k)      // 16 keys per step: 8 packed columns of P, 16 rows of V
+                    umma_ts(tmem + 256 + g * kTileN, tmem + g * kTileN + k * 8,
+                            umma_desc(b0 + k * 16 * 128, kHalfBytes, 1024), idesc_pv, (j > 0 || k > 0));
+            };
+            alive = bar_wait(q_full, 0, abort_flag) && bar_wait(k_full0, 0, abort_flag);
+            if (alive) {
+                tc_fence_after();
+                for (int g = 0; g < heads; ++g) issue_qk(g, 0);
+                umma_commit(k_empty0);
             }
+            for (int j = 0; j < n_tiles && alive; ++j) {
+                const int st = j % kStages, sn = (j + 1) % kStages;
+                const bool more = j + 1 < n_tiles;
+                for (int g = 0; g < heads && alive; ++g) {
+                    if (!bar_wait(p_full0 + 8 * g, j & 1u, abort_flag)) { alive = false; break; }
+                    if (g == 0 && !bar_wait(v_full0 + 8 * st, (j / kStages) & 1u, abort_flag)) { alive = false; break; }
+                    tc_fence_after();
+                    issue_pv(g, j);
+                    if (g == heads - 1) umma_commit(v_empty0 + 8 * st);
+                    if (more) {
+                        if (g == 0 && !bar_wait(k_full0 + 8 * sn, ((j + 1) / kStages) & 1u, abort_flag)) { alive = false; break; }
+                        tc_fence_after();
+                        issue_qk(g, j + 1);
+                        if (g == heads - 1) umma_commit(k_empty0 + 8 * sn);
+                    }
+                }
+            }
+            if (alive) umma_commit(all_done);
         }
-    } else {
+    } else if (group < heads) {
         // ============================== softmax warps =======================
-        const int row = tid;                               // TMEM lane = query row of the tile
-        const uint32_t lane_base = (uint32_t)(warp * 32) << 16;
+        const uint32_t lane_base = (uint32_t)((warp % 4) * 32) << 16;    // a warp reaches the TMEM lanes of its quarter
+        const uint32_t ts = tmem + group * kTileN + lane_base;          // S, then P, of this head
+        const uint32_t to = tmem + 256 + group * kTileN + lane_base;    // O of this head
+        const int hq = hq0 + group;
         float m_ref = -INFINITY, l = 0.f;
         uint32_t v[32];
         for (int j = 0; j < n_tiles && alive; ++j) {
-            if (!bar_wait(s_full0 + 8 * (j & 1), (j >> 1) & 1u, abort_flag)) { alive = false; break; }
+            // s_full also tells that P.V of tile j-1 is complete: O is stable and the P columns are free
+            if (!bar_wait(s_full0 + 8 * group, j & 1u, abort_flag)) { alive = false; break; }
             tc_fence_after();
-            const uint32_t ts = tmem_s0 + (j & 1) * kTileN + lane_base;
             const int valid_cols = page_ok[j] ? min(kTileN, my_extent - j * kTileN) : 0;   // <= 0: nothing visible
             // pass 1: row maximum of the visible scores
             float mx = -INFINITY;
 #pragma unroll 1
             for (int c4 = 0; c4 < 4; ++c4) {
                 tmem_ld32(ts + c4 * 32, v);
+                if (valid_cols >= kTileN) {
 #pragma unroll
-                for (int c = 0; c < 32; ++c)
-                    if (c4 * 32 + c < valid_cols) mx = fmaxf(mx, __uint_as_float(v[c]) * prm.scale_log2);
+                    for (int c = 0; c < 32; ++c) mx = fmaxf(mx, __uint_as_float(v[c]));
+                } else {
+#pragma unroll
+                    for (int c = 0; c < 32; ++c) if (c4 * 32 + c < valid_cols) mx = fmaxf(mx, __uint_as_float(v[c]));
+                }
             }
+            mx *= prm.scale_log2;                          // scale > 0: max commutes with it
             // raise the reference maximum only when this tile is far above it
             const bool raise = mx > m_ref + kRescaleThreshold || (m_ref == -INFINITY && mx > -INFINITY);
-            const bool warp_raise = __any_sync(0xffffffffu, raise);
-            if (j > 0) {                                   // O of tile j-1 complete; P buffer free again
-                if (!bar_wait(o_done, (j - 1) & 1u, abort_flag)) { alive = false; break; }
-                tc_fence_after();
-            }
-            if (warp_raise) {
+            if (__any_sync(0xffffffffu, raise)) {          // tensor-memory access is a whole-warp operation
                 const float m_new = raise ? mx : m_ref;
                 const float alpha = (m_ref == -INFINITY) ? 0.f : exp2f(m_ref - m_new);
                 if (j > 0) {                               // rescale this row of O in tensor memory
 #pragma unroll 1
                     for (int c4 = 0; c4 < 4; ++c4) {
-                        tmem_ld32(tmem_o + lane_base + c4 * 32, v);
+                        tmem_ld32(to + c4 * 32, v);
 #pragma unroll
                         for (int c = 0; c < 32; ++c) v[c] = __float_as_uint(__uint_as_float(v[c]) * alpha);
-                        tmem_st32(tmem_o + lane_base + c4 * 32, v);
+                        tmem_st32(to + c4 * 32, v);
                     }
                 }
                 l *= alpha;
                 m_ref = m_new;
             }
-            // pass 2: probabilities -> bf16 -> P tile in shared memory (K-major, 128-byte swizzle)
+            // pass 2: probabilities, packed two per 32-bit column, written over the scores of this row.
+            // Columns [0,64) of the region become P; the scores still to be read sit at or after the
+            // column being written (2 score columns make 1 packed column), so nothing is lost.
             float rsum = 0.f;
-            const float m_use = (m_ref == -INFINITY) ? 0.f : m_ref;
+            const float neg_m = (m_ref == -INFINITY) ? 0.f : -m_ref;
 #pragma unroll 1
-            for (int c4 = 0; c4 < 4; ++c4) {
-                tmem_ld32(ts + c4 * 32, v);
-                uint32_t packed[16];
+            for (int half = 0; half < 2; ++half) {         // 64 scores -> 32 packed columns per round
+                uint32_t pk[32];
 #pragma unroll
-                for (int c = 0; c < 32; c += 2) {
-                    const float p0 = (c4 * 32 + c < valid_cols) ? exp2f(__uint_as_float(v[c]) * prm.scale_log2 - m_use) : 0.f;
-                    const float p1 = (c4 * 32 + c + 1 < valid_cols) ? exp2f(__uint_as_float(v[c + 1]) * prm.scale_log2 - m_use) : 0.f;
-                    rsum += p0 + p1;
-                    if (prm.is_bf16) { __nv_bfloat162 b = __floats2bfloat162_rn(p0, p1); packed[c / 2] = *reinterpret_cast<uint32_t*>(&b); }
-                    else { __half2 b = __floats2half2_rn(p0, p1); packed[c / 2] = *reinterpret_cast<uint32_t*>(&b); }
-                }
-                // 32 columns = 4 chunks of 16 bytes; chunk index within the 128-byte row is XORed with row % 8
-                uint8_t* prow = p_s + (c4 >> 1) * kHalfBytes + row * 128;
+                for (int sub = 0; sub < 2; ++sub) {
+                    const int c4 = half * 2 + sub;
+                    tmem_ld32(ts + c4 * 32, v);
 #pragma unroll
-                for (int q4 = 0; q4 < 4; ++q4) {
-                    const int chunk = (c4 & 1) * 4 + q4;
-                    *reinterpret_cast<uint4*>(prow + ((chunk ^ (row & 7)) << 4)) =
-                        make_uint4(packed[q4 * 4], packed[q4 * 4 + 1], packed[q4 * 4 + 2], packed[q4 * 4 + 3]);
+                    for (int c = 0; c < 32; c += 2) {
+                        float p0 = exp2f(fmaf(__uint_as_float(v[c]), prm.scale_log2, neg_m));
+                        float p1 = exp2f(fmaf(__uint_as_float(v[c + 1]), prm.scale_log2, neg_m));
+                        if (valid_cols < kTileN) {
+                            if (c4 * 32 + c >= valid_cols) p0 = 0.f;
+                            if (c4 * 32 + c + 1 >= valid_cols) p1 = 0.f;
+                        }
+                        rsum += p0 + p1;
+                        uint32_t w;
+                        if (prm.is_bf16) { __nv_bfloat162 b = __floats2bfloat162_rn(p0, p1); w = *reinterpret_cast<uint32_t*>(&b); }
+                        else { __half2 b = __floats2half2_rn(p0, p1); w = *reinterpret_cast<uint32_t*>(&b); }
+                        pk[sub * 16 + c / 2] = w;
+                    }
                 }
+                tmem_st32(ts + half * 32, pk);
             }
             l += rsum;
-            // hand S[j % 2] back and P over: generic-proxy writes must be visible to the tensor core
-            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
             tc_fence_before();
             __syncwarp();
-            if (lane == 0) { bar_arrive(s_free0 + 8 * (j & 1)); bar_arrive(p_full); }
+            if (lane == 0) bar_arrive(p_full0 + 8 * group);
         }
         // ---- epilogue: O / l -> out, lse --------------------------------------
         T* out = reinterpret_cast<T*>(prm.out);
         const int tok = t0 + row;
         if (n_tiles > 0 && alive) {
-            if (!bar_wait(o_done, (n_tiles - 1) & 1u, abort_flag)) alive = false;
+            if (!bar_wait(all_done, 0, abort_flag)) alive = false;
             tc_fence_after();
         }
         if (alive) {
             const float inv = l > 0.f ? 1.f / l : 0.f;
 #pragma unroll 1
             for (int c4 = 0; c4 < 4; ++c4) {
-                if (n_tiles > 0) tmem_ld32(tmem_o + lane_base + c4 * 32, v);
+                if (n_tiles > 0) tmem_ld32(to + c4 * 32, v);
                 if (tok < prm.L) {
                     T* dst = out + ((size_t)hq * prm.L + tok) * kHeadDim + c4 * 32;
 #pragma unroll
@@ -439,7 +468,7 @@ EncodeFn encoder() {
     return fn;
 }
 
-constexpr int kPrefillSmem = 1024 + (2 + 2 * kStages) * kTileBytes + 16 * 8 + 16 * 4 + kMaxKeyTiles * 5 + 64;
+constexpr int kPrefillSmem = 1024 + (2 + 2 * kStages) * kTileBytes + 16 * 8 + 16 * 4 + kMaxKeyTiles * 5 + 64;   // Q x2, K and V x kStages
 
 }  // namespace
 
@@ -486,7 +515,8 @@ int launch_prefill_tc(const PoolView& pv, int layer, void* out, float* lse, cons
     prm.rows_per_plane = pv.n_pages * pv.P;
     prm.scale_log2 = sm_scale * kLog2e;
     prm.is_bf16 = pv.dtype == FPKV_BF16;
-    dim3 grid((L + kTileM - 1) / kTileM, Hq);
+    prm.heads_per_cta = ((Hq / pv.H) % 2 == 0) ? 2 : 1;
+    dim3 grid((L + kTileM - 1) / kTileM, Hq / prm.heads_per_cta);
     if (pv.dtype == FPKV_BF16) {
         auto kern = prefill_tc_kernel<__nv_bfloat16>;
         if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, kPrefillSmem) != cudaSuccess) return FPKV_ELAUNCH;
