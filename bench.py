@@ -427,6 +427,73 @@ def run_reference(args):
     print(json.dumps(line), flush=True)
 
 
+def run_prefill(args):
+    """Secondary workload (config 3's prefill part): 8 sequences of 1024 image-patch tokens + 64 text
+    tokens, packed with 128-alignment (9216 rows), bf16, 16 q heads / 8 kv heads, head_dim 128.  One step =
+    packed append of the row's K/V into pages + paged prefill attention under the image-prefix mask.
+    Tensor-core bound: the metric is TFLOP/s over 4 * Hq * D * (allowed query-key pairs)."""
+    from fpkv import workloads as wl
+    from fpkv.paged_attention import PagedKVCache, paged_attention
+    assert torch.cuda.is_available(), "bench.py needs a CUDA device; there is no CPU path for the product"
+    device = torch.device("cuda", int(os.environ.get("LOCAL_RANK", "0")))
+    torch.cuda.set_device(device)
+    K, W = args.steps, args.warmup
+    case = wl.config3_prefill_case()
+    cache = PagedKVCache(256, P, 16, HKV, D, 1, torch.bfloat16, device)
+    slots = []
+    for toks in case.seq_tokens:
+        s = cache.allocate(); slots.append(s); cache.reserve(s, None, len(toks))
+    bidx, ipos = case.batch_idx_for(slots).to(device), case.input_pos.to(device)
+    q, k, v = case.q.to(device), case.k.to(device), case.v.to(device)
+    mask = cache.create_prefill_blockmask(bidx, case.input_ids.to(device), wl.IMG_CLS_ID, wl.END_OF_IMG_ID)
+    ext = mask.extent(ipos)
+    pairs = int(ext.to(torch.int64).sum().item())          # every row sees a prefix of extent[t] keys
+    flops = 4.0 * HQ * D * pairs
+    stream = torch.cuda.current_stream(device)
+
+    def step():
+        cache.insert_kv(0, k, v, input_pos=ipos, batch_idx=bidx)
+        return paged_attention(q, cache, 0, bidx, ipos, mask)
+    for _ in range(W):
+        step()
+    torch.cuda.synchronize(device)
+    sampler = ClockSampler(device.index); sampler.start()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record(stream)
+    for _ in range(K):
+        step()
+    e1.record(stream)
+    torch.cuda.synchronize(device)
+    ms_step = e0.elapsed_time(e1) / K
+    a0, a1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    a0.record(stream)
+    for _ in range(K):
+        paged_attention(q, cache, 0, bidx, ipos, mask)
+    a1.record(stream)
+    torch.cuda.synchronize(device)
+    ms_attn = a0.elapsed_time(a1) / K
+    clocks = sampler.stop()
+    cache.check_status()
+    try:
+        with open(os.path.join(ROOT, "MEASURED_PEAKS.json")) as f:
+            peak, src = float(json.load(f)["bf16_tflops"]), "measured (burst)"
+    except Exception:
+        peak, src = 1590.0, "fallback"
+    tf = flops / (ms_attn * 1e-3) / 1e12
+    print(json.dumps({
+        "metric": "paged_prefill_attn_tflops", "value": flops / (ms_step * 1e-3) / 1e12, "unit": "TFLOP/s",
+        "n_gpus": 1, "steps": K, "warmup": W, "ms_per_step": ms_step, "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+        "config": {"workload": "config 3 (prefill part): 8 x (1024 image + 64 text tokens) packed to 9216 rows, "
+                               "16 q heads / 8 kv heads, head_dim 128, page 128, image-prefix mask; "
+                               "packed append + paged prefill attention", "allowed_pairs": pairs, "seed": 3003},
+        "gpu_launches": 2 * K,
+        "roofline": {"bound": "tensor", "kernel": "prefill_tc_kernel, timed alone", "achieved": tf, "peak": peak,
+                     "unit": "TFLOP/s", "frac": tf / peak, "peak_source": src, "traffic": None,
+                     "flops_per_launch": flops, "ms_per_launch": ms_attn},
+        "clocks": clocks}), flush=True)
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -440,10 +507,14 @@ def main():
     ap.add_argument("--len-hi", type=int, default=LEN_HI)
     ap.add_argument("--kernels-only", action="store_true",
                     help="run only the device-resident loop (no host-buffer loop, no CPU baseline): for profilers")
+    ap.add_argument("--workload", default="decode", choices=["decode", "prefill"],
+                    help="decode = config 2 (the headline metric); prefill = config 3's prefill part (tensor-bound)")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3)
     if args.impl == "reference":
         run_reference(args)
+    elif args.workload == "prefill":
+        run_prefill(args)
     else:
         run_fpkv(args)
 

@@ -138,6 +138,27 @@ __device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t (&r)[32]) {
                  : "r"(taddr) : "memory");
     asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
 }
+__device__ __forceinline__ void tmem_st32_nowait(uint32_t taddr, const uint32_t (&r)[32]) {
+    asm volatile("tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], "
+                 "{%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,"
+                 "%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31,%32};"
+                 ::"r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]),
+                   "r"(r[8]), "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15]),
+                   "r"(r[16]), "r"(r[17]), "r"(r[18]), "r"(r[19]), "r"(r[20]), "r"(r[21]), "r"(r[22]), "r"(r[23]),
+                   "r"(r[24]), "r"(r[25]), "r"(r[26]), "r"(r[27]), "r"(r[28]), "r"(r[29]), "r"(r[30]), "r"(r[31])
+                 : "memory");
+}
+__device__ __forceinline__ void tmem_ld32_nowait(uint32_t taddr, uint32_t (&r)[32]) {
+    asm volatile("tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+                 "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,"
+                 "%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+                   "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]),
+                   "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),
+                   "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+                 : "r"(taddr) : "memory");
+}
+__device__ __forceinline__ void tmem_wait_ld() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
 __device__ __forceinline__ void tmem_st32(uint32_t taddr, const uint32_t (&r)[32]) {
     asm volatile("tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], "
                  "{%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,"
@@ -149,6 +170,28 @@ __device__ __forceinline__ void tmem_st32(uint32_t taddr, const uint32_t (&r)[32
                  : "memory");
     asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
 }
+
+__device__ __forceinline__ float max3f(float a, float b, float c) {
+    float d;
+    asm("max.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(a), "f"(b), "f"(c));
+    return d;
+}
+__device__ __forceinline__ float ex2(float x) {
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+}
+
+#ifdef FPKV_PROFILE
+// Development aid: time stamps of one CTA's MMA thread, [iteration][event].
+__device__ unsigned long long g_prefill_times[20][8];
+__device__ __forceinline__ unsigned long long gtime_ns() {
+    unsigned long long t; asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t)); return t;
+}
+#define PF_STAMP(it, ev) do { if (blockIdx.x == 3 && blockIdx.y == 2 && (it) < 20) g_prefill_times[it][ev] = gtime_ns(); } while (0)
+#else
+#define PF_STAMP(it, ev) do { } while (0)
+#endif
 
 struct PrefillParams {
     const int64_t* page_table;
@@ -301,7 +344,9 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_consta
                     umma_ts(tmem + 256 + g * kTileN, tmem + g * kTileN + k * 8,
                             umma_desc(b0 + k * 16 * 128, kHalfBytes, 1024), idesc_pv, (j > 0 || k > 0));
             };
+            PF_STAMP(19, 0);
             alive = bar_wait(q_full, 0, abort_flag) && bar_wait(k_full0, 0, abort_flag);
+            PF_STAMP(19, 1);
             if (alive) {
                 tc_fence_after();
                 for (int g = 0; g < heads; ++g) issue_qk(g, 0);
@@ -311,13 +356,17 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_consta
                 const int st = j % kStages, sn = (j + 1) % kStages;
                 const bool more = j + 1 < n_tiles;
                 for (int g = 0; g < heads && alive; ++g) {
+                    PF_STAMP(j, g * 4 + 0);
                     if (!bar_wait(p_full0 + 8 * g, j & 1u, abort_flag)) { alive = false; break; }
+                    PF_STAMP(j, g * 4 + 1);
                     if (g == 0 && !bar_wait(v_full0 + 8 * st, (j / kStages) & 1u, abort_flag)) { alive = false; break; }
+                    PF_STAMP(j, g * 4 + 2);
                     tc_fence_after();
                     issue_pv(g, j);
                     if (g == heads - 1) umma_commit(v_empty0 + 8 * st);
                     if (more) {
                         if (g == 0 && !bar_wait(k_full0 + 8 * sn, ((j + 1) / kStages) & 1u, abort_flag)) { alive = false; break; }
+                        PF_STAMP(j, g * 4 + 3);
                         tc_fence_after();
                         issue_qk(g, j + 1);
                         if (g == heads - 1) umma_commit(k_empty0 + 8 * sn);
@@ -339,18 +388,37 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_consta
             if (!bar_wait(s_full0 + 8 * group, j & 1u, abort_flag)) { alive = false; break; }
             tc_fence_after();
             const int valid_cols = page_ok[j] ? min(kTileN, my_extent - j * kTileN) : 0;   // <= 0: nothing visible
-            // pass 1: row maximum of the visible scores
-            float mx = -INFINITY;
-#pragma unroll 1
-            for (int c4 = 0; c4 < 4; ++c4) {
-                tmem_ld32(ts + c4 * 32, v);
-                if (valid_cols >= kTileN) {
+#ifdef FPKV_EXP_SKIP_SOFTMAX                               // timing experiment only: tensor + copy pipeline alone
+            tc_fence_before(); __syncwarp();
+            if (lane == 0) bar_arrive(p_full0 + 8 * group);
+            continue;
+#endif
+            // the whole score row of this thread: four loads in flight, one wait
+            uint32_t sv[4][32];
 #pragma unroll
-                    for (int c = 0; c < 32; ++c) mx = fmaxf(mx, __uint_as_float(v[c]));
-                } else {
+            for (int c4 = 0; c4 < 4; ++c4) tmem_ld32_nowait(ts + c4 * 32, sv[c4]);
+            tmem_wait_ld();
+            // Most tiles are fully visible to every row of the warp; they take a path without a
+            // per-element mask (one FFMA, one EX2, one add and half a pack per score).
+            const bool full = __all_sync(0xffffffffu, valid_cols >= kTileN);
+            float mx;
+            if (full) {
+                float m4[4];
 #pragma unroll
-                    for (int c = 0; c < 32; ++c) if (c4 * 32 + c < valid_cols) mx = fmaxf(mx, __uint_as_float(v[c]));
+                for (int c4 = 0; c4 < 4; ++c4) {
+                    m4[c4] = max3f(__uint_as_float(sv[c4][0]), __uint_as_float(sv[c4][1]), __uint_as_float(sv[c4][2]));
+#pragma unroll
+                    for (int c = 3; c + 1 < 32; c += 2)
+                        m4[c4] = max3f(m4[c4], __uint_as_float(sv[c4][c]), __uint_as_float(sv[c4][c + 1]));
+                    m4[c4] = fmaxf(m4[c4], __uint_as_float(sv[c4][31]));
                 }
+                mx = fmaxf(fmaxf(m4[0], m4[1]), fmaxf(m4[2], m4[3]));
+            } else {
+                mx = -INFINITY;
+#pragma unroll
+                for (int c4 = 0; c4 < 4; ++c4)
+#pragma unroll
+                    for (int c = 0; c < 32; ++c) if (c4 * 32 + c < valid_cols) mx = fmaxf(mx, __uint_as_float(sv[c4][c]));
             }
             mx *= prm.scale_log2;                          // scale > 0: max commutes with it
             // raise the reference maximum only when this tile is far above it
@@ -370,35 +438,36 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_consta
                 l *= alpha;
                 m_ref = m_new;
             }
-            // pass 2: probabilities, packed two per 32-bit column, written over the scores of this row.
-            // Columns [0,64) of the region become P; the scores still to be read sit at or after the
-            // column being written (2 score columns make 1 packed column), so nothing is lost.
-            float rsum = 0.f;
+            // probabilities, packed two per 32-bit column, written over the scores of this row: columns
+            // [0,64) of the region become P (the scores are all in registers by now).
+            float r4[4] = {0.f, 0.f, 0.f, 0.f};
             const float neg_m = (m_ref == -INFINITY) ? 0.f : -m_ref;
-#pragma unroll 1
-            for (int half = 0; half < 2; ++half) {         // 64 scores -> 32 packed columns per round
+#pragma unroll
+            for (int half = 0; half < 2; ++half) {         // 64 scores -> 32 packed columns per store
                 uint32_t pk[32];
 #pragma unroll
                 for (int sub = 0; sub < 2; ++sub) {
                     const int c4 = half * 2 + sub;
-                    tmem_ld32(ts + c4 * 32, v);
 #pragma unroll
                     for (int c = 0; c < 32; c += 2) {
-                        float p0 = exp2f(fmaf(__uint_as_float(v[c]), prm.scale_log2, neg_m));
-                        float p1 = exp2f(fmaf(__uint_as_float(v[c + 1]), prm.scale_log2, neg_m));
-                        if (valid_cols < kTileN) {
+                        float p0 = ex2(fmaf(__uint_as_float(sv[c4][c]), prm.scale_log2, neg_m));
+                        float p1 = ex2(fmaf(__uint_as_float(sv[c4][c + 1]), prm.scale_log2, neg_m));
+                        if (!full) {
                             if (c4 * 32 + c >= valid_cols) p0 = 0.f;
                             if (c4 * 32 + c + 1 >= valid_cols) p1 = 0.f;
                         }
-                        rsum += p0 + p1;
+                        r4[(c >> 1) & 1] += p0;
+                        r4[2 + ((c >> 1) & 1)] += p1;
                         uint32_t w;
                         if (prm.is_bf16) { __nv_bfloat162 b = __floats2bfloat162_rn(p0, p1); w = *reinterpret_cast<uint32_t*>(&b); }
                         else { __half2 b = __floats2half2_rn(p0, p1); w = *reinterpret_cast<uint32_t*>(&b); }
                         pk[sub * 16 + c / 2] = w;
                     }
                 }
-                tmem_st32(ts + half * 32, pk);
+                tmem_st32_nowait(ts + half * 32, pk);
             }
+            asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
+            const float rsum = (r4[0] + r4[1]) + (r4[2] + r4[3]);
             l += rsum;
             tc_fence_before();
             __syncwarp();
@@ -471,6 +540,12 @@ EncodeFn encoder() {
 constexpr int kPrefillSmem = 1024 + (2 + 2 * kStages) * kTileBytes + 16 * 8 + 16 * 4 + kMaxKeyTiles * 5 + 64;   // Q x2, K and V x kStages
 
 }  // namespace
+
+#ifdef FPKV_PROFILE
+extern "C" __attribute__((visibility("default"))) int fpkv_debug_prefill_times(unsigned long long* host_out) {
+    return (int)cudaMemcpyFromSymbol(host_out, g_prefill_times, sizeof(unsigned long long) * 20 * 8);
+}
+#endif
 
 bool prefill_tc_supported(const PoolView& pv, int Hq)
 {
