@@ -174,7 +174,7 @@ int fpkv_decode_attn(const fpkv_pool* pool, int32_t layer, void* out, float* lse
 
 int fpkv_prefill_attn(const fpkv_pool* pool, int32_t layer, void* out, float* lse, const void* q,
                       int64_t q_stride_h, int64_t q_stride_t, const int64_t* batch_idx, const int32_t* extent,
-                      int32_t L, int32_t n_q_heads, float sm_scale, int32_t* status, void* stream)
+                      int32_t L, int32_t n_q_heads, float sm_scale, int32_t flags, int32_t* status, void* stream)
 {
     PoolView pv;
     int rc = make_view(pool, layer, &pv);
@@ -185,10 +185,15 @@ int fpkv_prefill_attn(const fpkv_pool* pool, int32_t layer, void* out, float* ls
     if (out == nullptr || lse == nullptr || batch_idx == nullptr || extent == nullptr) return FPKV_EINVAL;
     if ((rc = check_rows(q, q_stride_h, q_stride_t, pv.esize))) return rc;
     if (!aligned16(out)) return FPKV_EALIGN;
-    if (!prefill_tc_supported(pv, n_q_heads)) return FPKV_ESHAPE;
+    const int which = flags & 3;
+    const bool tc_ok = prefill_tc_supported(pv, n_q_heads);
+    if (which == FPKV_PREFILL_TC && !tc_ok) return FPKV_ESHAPE;
     if ((rc = check_arch())) return rc;
-    return launch_prefill_tc(pv, layer, out, lse, q, q_stride_h, q_stride_t, batch_idx, extent, L, n_q_heads,
-                             sm_scale, status, static_cast<cudaStream_t>(stream));
+    if (which == FPKV_PREFILL_TC || (which == FPKV_PREFILL_AUTO && tc_ok))
+        return launch_prefill_tc(pv, layer, out, lse, q, q_stride_h, q_stride_t, batch_idx, extent, L, n_q_heads,
+                                 sm_scale, status, static_cast<cudaStream_t>(stream));
+    return launch_prefill_portable(pv, layer, out, lse, q, q_stride_h, q_stride_t, batch_idx, extent, L, n_q_heads,
+                                   sm_scale, status, static_cast<cudaStream_t>(stream));
 }
 
 }  // extern "C"

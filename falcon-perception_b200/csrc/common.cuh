@@ -71,6 +71,9 @@ int launch_decode_tma(const PoolView& pv, int layer, void* out, float* lse, cons
                       const void* pos, int pos_type, int B, int Hq, float sm_scale,
                       void* workspace, int32_t* status, cudaStream_t stream, bool after_append);
 
+int launch_prefill_portable(const PoolView& pv, int layer, void* out, float* lse, const void* q, long long q_stride_h,
+                            long long q_stride_t, const int64_t* batch_idx, const int32_t* extent, int L, int Hq,
+                            float sm_scale, int32_t* status, cudaStream_t stream);
 bool prefill_tc_supported(const PoolView& pv, int Hq);
 int launch_prefill_tc(const PoolView& pv, int layer, void* out, float* lse, const void* q, long long q_stride_h,
                       long long q_stride_t, const int64_t* batch_idx, const int32_t* extent, int L, int Hq,

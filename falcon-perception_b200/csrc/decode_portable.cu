@@ -11,6 +11,11 @@
 // memory and the CTA writes one partial (m, l, acc[head_dim]) per split; a
 // second kernel merges the splits.
 //
+// The same kernel serves packed prefill rows for shapes the tensor-core prefill
+// kernel does not take: a row is then a packed token, its number of visible
+// keys comes from the caller's extent array instead of input_pos + 1, and with
+// one split per row the CTA writes the normalised result itself.
+//
 // Visible key set of row b (slot s = batch_idx[b], p = input_pos[b]): logical
 // positions 0..p whose page id PT[s, j / P] is mapped and maps back
 // (P2L[s, page] >= 0) -- the reference's decode mask after conversion to
@@ -31,14 +36,19 @@ __host__ __device__ inline int portable_splits(int B, int Hq) {
     return s;
 }
 
-template <typename T, int D, typename PosT>
+// Where row (b, hq) of the result goes: element strides of out and lse over rows and heads.
+struct OutLayout { long long out_row, out_head, lse_row, lse_head; };
+
+template <typename T, int D, typename PosT, bool DIRECT>
 __global__ void __launch_bounds__(kPortableWarps * 32)
 decode_portable_kernel(const char* __restrict__ pool_layer, size_t plane_bytes, int H,
                        const int64_t* __restrict__ page_table, const int64_t* __restrict__ p2l,
                        int n_pages, int max_batch, int P,
                        const T* __restrict__ q, long long q_stride_b, long long q_stride_h,
                        const int64_t* __restrict__ batch_idx, const PosT* __restrict__ pos,
-                       int Hq, float scale_log2, float* __restrict__ ws, int32_t* status)
+                       const int32_t* __restrict__ extent,
+                       int Hq, float scale_log2, float* __restrict__ ws, T* __restrict__ out, float* __restrict__ lse,
+                       OutLayout lay, int32_t* status)
 {
     constexpr int E = D / 32;                     // elements per lane
     const int row = blockIdx.x;                   // b * Hq + hq
@@ -52,15 +62,16 @@ decode_portable_kernel(const char* __restrict__ pool_layer, size_t plane_bytes, 
     __shared__ float sm_acc[kPortableWarps][D];
 
     const long long slot = batch_idx[b];
-    const long long p = (long long)pos[b];
+    // visible keys: 0..pos for a decode row, 0..extent-1 for a packed prefill token (0 for pads)
+    const long long want = extent != nullptr ? (slot > 0 ? (long long)extent[b] : 0) : (long long)pos[b] + 1;
     int n_pg = 0;
     long long n_keys = 0;
     if (slot < 0 || slot >= max_batch) {
         if (threadIdx.x == 0 && split == 0) raise_status(status, FPKV_STATUS_BAD_SLOT);
-    } else if (p < 0 || p / P >= n_pages) {
+    } else if (want < (extent != nullptr ? 0 : 1) || (want + P - 1) / P > n_pages) {
         if (threadIdx.x == 0 && split == 0) raise_status(status, FPKV_STATUS_BAD_POS);
     } else {
-        n_keys = p + 1;
+        n_keys = want;
         n_pg = (int)((n_keys + P - 1) / P);
     }
     const int pg0 = (int)((long long)n_pg * split / S);
@@ -109,20 +120,22 @@ decode_portable_kernel(const char* __restrict__ pool_layer, size_t plane_bytes, 
     float M = -INFINITY;
 #pragma unroll
     for (int w = 0; w < kPortableWarps; ++w) M = fmaxf(M, sm_m[w]);
-    float* dst = ws + ((size_t)row * S + split) * (D + 2);
+    float L = 0.f;
+#pragma unroll
+    for (int w = 0; w < kPortableWarps; ++w)
+        if (sm_m[w] != -INFINITY) L += sm_l[w] * exp2f(sm_m[w] - M);
+    float* dst = DIRECT ? nullptr : ws + ((size_t)row * S + split) * (D + 2);
     for (int d = threadIdx.x; d < D; d += blockDim.x) {
         float o = 0.f;
 #pragma unroll
         for (int w = 0; w < kPortableWarps; ++w)
             if (sm_m[w] != -INFINITY) o += sm_acc[w][d] * exp2f(sm_m[w] - M);
-        dst[2 + d] = o;
+        if (DIRECT) out[b * lay.out_row + hq * lay.out_head + d] = ElemTraits<T>::from_float(L > 0.f ? o / L : 0.f);
+        else dst[2 + d] = o;
     }
     if (threadIdx.x == 0) {
-        float L = 0.f;
-#pragma unroll
-        for (int w = 0; w < kPortableWarps; ++w)
-            if (sm_m[w] != -INFINITY) L += sm_l[w] * exp2f(sm_m[w] - M);
-        dst[0] = M; dst[1] = L;
+        if (DIRECT) lse[b * lay.lse_row + hq * lay.lse_head] = L > 0.f ? (M + log2f(L)) * kLn2 : -INFINITY;
+        else { dst[0] = M; dst[1] = L; }
     }
 }
 
@@ -159,10 +172,10 @@ static int launch_typed(const PoolView& pv, int layer, void* out, float* lse, co
 {
     const int S = portable_splits(B, Hq);
     dim3 grid(B * Hq, S);
-    decode_portable_kernel<T, D, PosT><<<grid, kPortableWarps * 32, 0, stream>>>(
+    decode_portable_kernel<T, D, PosT, false><<<grid, kPortableWarps * 32, 0, stream>>>(
         pv.plane(layer, 0, 0), pv.plane_bytes(), pv.H, pv.page_table, pv.p2l, pv.n_pages, pv.max_batch, pv.P,
-        (const T*)q, q_stride_b, q_stride_h, batch_idx, (const PosT*)pos, Hq, sm_scale * kLog2e,
-        (float*)workspace, status);
+        (const T*)q, q_stride_b, q_stride_h, batch_idx, (const PosT*)pos, nullptr, Hq, sm_scale * kLog2e,
+        (float*)workspace, nullptr, nullptr, OutLayout{0, 0, 0, 0}, status);
     if (cudaGetLastError() != cudaSuccess) return FPKV_ELAUNCH;
     decode_portable_merge_kernel<T, D><<<B * Hq, D, 0, stream>>>((const float*)workspace, S, (T*)out, lse);
     return cudaGetLastError() == cudaSuccess ? FPKV_OK : FPKV_ELAUNCH;
@@ -186,6 +199,43 @@ int launch_decode_portable(const PoolView& pv, int layer, void* out, float* lse,
 #define FPKV_DISPATCH(T)                                                                              \
     return pv.D == 64 ? launch_pos<T, 64>(pv, layer, out, lse, q, qsb, qsh, bi, pos, pos_type, B, Hq, sc, ws, st, s) \
                       : launch_pos<T, 128>(pv, layer, out, lse, q, qsb, qsh, bi, pos, pos_type, B, Hq, sc, ws, st, s)
+    switch (pv.dtype) {
+        case FPKV_F32:  FPKV_DISPATCH(float);
+        case FPKV_BF16: FPKV_DISPATCH(__nv_bfloat16);
+        case FPKV_F16:  FPKV_DISPATCH(__half);
+    }
+#undef FPKV_DISPATCH
+    return FPKV_EDTYPE;
+}
+
+// Packed prefill rows through the same kernel: one CTA per (token, query head), one split, direct output
+// to out (Hq, L, D) / lse (Hq, L).
+template <typename T, int D>
+static int launch_prefill_typed(const PoolView& pv, int layer, void* out, float* lse, const void* q, long long qsh,
+                                long long qst, const int64_t* bi, const int32_t* extent, int L, int Hq, float sc,
+                                int32_t* st, cudaStream_t s)
+{
+    const OutLayout lay{(long long)D, (long long)L * D, 1, (long long)L};
+    for (int t0 = 0; t0 < L; t0 += 32768) {            // grid.x = rows * heads stays far below its limit
+        const int n = L - t0 < 32768 ? L - t0 : 32768;
+        dim3 grid(n * Hq, 1);
+        decode_portable_kernel<T, D, int32_t, true><<<grid, kPortableWarps * 32, 0, s>>>(
+            pv.plane(layer, 0, 0), pv.plane_bytes(), pv.H, pv.page_table, pv.p2l, pv.n_pages, pv.max_batch, pv.P,
+            (const T*)q + (long long)t0 * qst, qst, qsh, bi + t0, nullptr, extent + t0, Hq, sc * kLog2e, nullptr,
+            (T*)out + (long long)t0 * D, lse + t0, lay, st);
+        if (cudaGetLastError() != cudaSuccess) return FPKV_ELAUNCH;
+    }
+    return FPKV_OK;
+}
+
+int launch_prefill_portable(const PoolView& pv, int layer, void* out, float* lse, const void* q, long long qsh,
+                            long long qst, const int64_t* bi, const int32_t* extent, int L, int Hq, float sc,
+                            int32_t* st, cudaStream_t s)
+{
+    if (L == 0) return FPKV_OK;
+#define FPKV_DISPATCH(T)                                                                                   \
+    return pv.D == 64 ? launch_prefill_typed<T, 64>(pv, layer, out, lse, q, qsh, qst, bi, extent, L, Hq, sc, st, s) \
+                      : launch_prefill_typed<T, 128>(pv, layer, out, lse, q, qsh, qst, bi, extent, L, Hq, sc, st, s)
     switch (pv.dtype) {
         case FPKV_F32:  FPKV_DISPATCH(float);
         case FPKV_BF16: FPKV_DISPATCH(__nv_bfloat16);

@@ -16,6 +16,7 @@ FPKV_F32, FPKV_BF16, FPKV_F16 = 0, 1, 2
 FPKV_I32, FPKV_I64 = 0, 1
 DECODE_AUTO, DECODE_PORTABLE, DECODE_TMA = 0, 1, 2
 DECODE_AFTER_APPEND = 4
+PREFILL_AUTO, PREFILL_PORTABLE, PREFILL_TC = 0, 1, 2
 STATIC_SCRATCH_BYTES = 4 << 20
 ESTATIC = -8
 STATUS_BAD_SLOT, STATUS_BAD_POS, STATUS_BAD_PAGE, STATUS_TIMEOUT = 1, 2, 4, 8
@@ -64,7 +65,7 @@ def _load():
     lib.fpkv_decode_attn.argtypes = [pool, i32, vp, vp, vp, i64, i64, vp, vp, i32, i32, i32, f32, vp,
                                      ctypes.c_size_t, i32, vp, vp]
     lib.fpkv_prefill_attn.restype = ctypes.c_int
-    lib.fpkv_prefill_attn.argtypes = [pool, i32, vp, vp, vp, i64, i64, vp, vp, i32, i32, f32, vp, vp]
+    lib.fpkv_prefill_attn.argtypes = [pool, i32, vp, vp, vp, i64, i64, vp, vp, i32, i32, f32, i32, vp, vp]
     lib.fpkv_decode_attn_static.restype = ctypes.c_int
     lib.fpkv_decode_attn_static.argtypes = [pool, i32, vp, vp, vp, i64, i64, vp, vp, i32, i32, i32, f32, vp, vp]
     return lib

@@ -86,6 +86,7 @@ class PagedKVCache(KVCacheBase):
         self._status = torch.zeros(1, dtype=torch.int32, device=device)
         self._workspace = None
         self.decode_kernel = _lib.DECODE_AUTO       # DECODE_PORTABLE / DECODE_TMA force one kernel
+        self.prefill_kernel = _lib.PREFILL_AUTO     # PREFILL_PORTABLE / PREFILL_TC force one kernel
 
     # ------------------------------------------------------------------ helpers
     def _require_cuda(self, *tensors):
@@ -325,7 +326,8 @@ class PagedKVCache(KVCacheBase):
         scale = (1.0 / math.sqrt(D)) if sm_scale is None else float(sm_scale)
         _lib.check(_lib.lib.fpkv_prefill_attn(
             ctypes.byref(self._pool), layer_id, out.data_ptr(), lse.data_ptr(), q.data_ptr(), q.stride(1),
-            q.stride(2), bi.data_ptr(), ext.data_ptr(), L, Hq, scale, self._status_ptr(), _stream(self._dev)),
+            q.stride(2), bi.data_ptr(), ext.data_ptr(), L, Hq, scale, int(self.prefill_kernel), self._status_ptr(),
+            _stream(self._dev)),
             "fpkv_prefill_attn")
         return out, lse
 

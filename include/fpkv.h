@@ -203,14 +203,20 @@ FPKV_API int fpkv_decode_attn(const fpkv_pool* pool, int32_t layer,
  * out  device (1, n_q_heads, L, head_dim) contiguous, dtype of q
  * lse  device (1, n_q_heads, L) fp32 natural log; rows without a visible key
  *      give out = 0, lse = -inf.
- * Shapes: 16-bit pool, page_size 128, head_dim 128 (tcgen05 tensor-core
- * kernel); anything else returns FPKV_ESHAPE.  Needs no workspace.
+ * flags: FPKV_PREFILL_AUTO runs the tcgen05 tensor-core kernel for 16-bit
+ * pools with page_size 128 and head_dim 128 and a portable CUDA-core kernel
+ * (any pool dtype, head_dim 64/128, any page size; not tuned) otherwise;
+ * FPKV_PREFILL_PORTABLE / FPKV_PREFILL_TC force one (the latter returns
+ * FPKV_ESHAPE outside its range).  Needs no workspace.
  */
+#define FPKV_PREFILL_AUTO     0
+#define FPKV_PREFILL_PORTABLE 1
+#define FPKV_PREFILL_TC       2
 FPKV_API int fpkv_prefill_attn(const fpkv_pool* pool, int32_t layer,
                                void* out, float* lse,
                                const void* q, int64_t q_stride_h, int64_t q_stride_t,
                                const int64_t* batch_idx, const int32_t* extent,
-                               int32_t L, int32_t n_q_heads, float sm_scale,
+                               int32_t L, int32_t n_q_heads, float sm_scale, int32_t flags,
                                int32_t* status, void* stream);
 
 /*

@@ -5,7 +5,7 @@ import numpy as np
 import pytest
 import torch
 
-from fpkv import workloads as wl
+from fpkv import _lib, workloads as wl
 from fpkv.paged_attention import PagedKVCache, paged_attention
 from oracle import paged_kv_oracle as orc
 from helpers import assert_attention_close, golden
@@ -15,8 +15,9 @@ pytestmark = pytest.mark.gpu
 T = wl.image_text_tokens
 
 
-def run_product(case, n_pages, max_batch, dtype=torch.bfloat16):
+def run_product(case, n_pages, max_batch, dtype=torch.bfloat16, kernel=0):
     c = PagedKVCache(n_pages, case.P, max_batch, case.Hkv, case.D, 1, dtype, "cuda")
+    c.prefill_kernel = kernel
     slots = []
     for toks in case.seq_tokens:
         s = c.allocate(); slots.append(s); c.reserve(s, None, len(toks))
@@ -45,14 +46,27 @@ def compare_live_rows(case, out, lse, ref_out, ref_lse, what):
         assert out[0][:, ~live].abs().max().item() == 0 and torch.isneginf(lse[0][:, ~live]).all()
 
 
-def test_prefill_against_reference_golden():
-    make, n_pages, mb = PREFILL_CASES["prefill_img_d128"]
+@pytest.mark.parametrize("name,kernel", [("prefill_img_d128", _lib.PREFILL_TC), ("prefill_img_d128", _lib.PREFILL_PORTABLE),
+                                         ("prefill_mixed_d64", _lib.PREFILL_AUTO)])
+def test_prefill_against_reference_golden(name, kernel):
+    """Both kernels against the reference's own output; head_dim 64 is served by the portable one."""
+    make, n_pages, mb = PREFILL_CASES[name]
     case = make()
-    g = golden("prefill_img_d128")
-    c, slots, bidx, ipos, mask, out, lse = run_product(case, n_pages, mb)
+    g = golden(name)
+    c, slots, bidx, ipos, mask, out, lse = run_product(case, n_pages, mb, kernel=kernel)
     assert slots == g["slots"].tolist()
     assert out.dtype == torch.bfloat16 and tuple(out.shape) == tuple(case.q.shape) and tuple(lse.shape) == (1, 4, case.L)
-    compare_live_rows(case, out, lse, g["out"], g["lse"], "golden d128")
+    compare_live_rows(case, out, lse, g["out"], g["lse"], name)
+    c.check_status()
+
+
+def test_prefill_fp32_pool_portable():
+    case = wl.make_prefill_case(5, [T(2, 70, 30), T(0, 0, 140)], Hq=8, Hkv=4, D=64, P=16, align=128, dtype=torch.float32)
+    c, slots, bidx, ipos, mask, out, lse = run_product(case, 40, 4, dtype=torch.float32)
+    ref_out, ref_lse = oracle_prefill(case, slots, dtype=torch.float32)
+    live = case.seq_index.view(-1) > 0
+    assert (out[0][:, live].cpu() - ref_out[0][:, live]).abs().max().item() < 1e-4
+    assert (lse[0][:, live].cpu() - ref_lse[0][:, live]).abs().max().item() < 1e-4
     c.check_status()
 
 
