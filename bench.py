@@ -408,6 +408,8 @@ def run_reference(args):
     world = int(os.environ.get("WORLD_SIZE", "1"))
     if rank != 0:
         return
+    # torchrun pins OMP_NUM_THREADS to 1; this arm is meant to use the host cores it can get
+    torch.set_num_threads(max(1, len(os.sched_getaffinity(0))))
     r = time_cpu_path(steps=args.steps, warmup=min(args.warmup, 2), budget_s=120.0)
     line = {
         "impl": "reference", "metric": "paged_decode_attn_kv_gbps", "value": r["gbps"], "unit": "GB/s",

@@ -647,12 +647,19 @@ decode_tma_kernel(const __grid_constant__ CUtensorMap tmap, const Params prm)
 #ifdef FPKV_PROFILE
 __device__ unsigned long long g_fin_times[1024][3];
 #endif
+constexpr int kFinishGroups = 4;                   // thread groups that split a segment's units among them
+
 template <typename T, int D, int NREP>
-__global__ void __launch_bounds__(NREP * D >= 256 ? 256 : NREP * D)
+__global__ void __launch_bounds__(kFinishGroups * NREP * D / 4)
 decode_tma_finish_kernel(const Params prm, int G)
 {
+    constexpr int kVec = NREP * D / 4;                 // threads per group: one float4 of one output row each
+    __shared__ float4 s_acc[kFinishGroups][kVec];
+    __shared__ float2 s_ml[kFinishGroups][NREP];
     const int b = blockIdx.x / prm.Hkv, h = blockIdx.x % prm.Hkv;
     const int Hq = prm.Hkv * NREP;
+    const int grp = threadIdx.x / kVec, v4 = threadIdx.x % kVec;
+    const int r = v4 / (D / 4), d4 = (v4 % (D / 4)) * 4;
     T* out = reinterpret_cast<T*>(prm.out);
     asm volatile("griddepcontrol.wait;" ::: "memory");
 #ifdef FPKV_PROFILE
@@ -668,33 +675,57 @@ decode_tma_finish_kernel(const Params prm, int G)
     const bool maybe_empty = (info.z & 2) != 0;        // only tiny batches have units without tiles
     const int Ttot = info.w;
     auto empty_unit = [&](int u) -> bool {             // the main kernel's unit schedule, by arithmetic
-        int at = 0, lo = Ttot, len = 0;
+        int at = 0, len = 0;
         const int p = u / G, j = u - p * G;
 #pragma unroll
         for (int pp = 0; pp < kPhases; ++pp) {
             const int step = (pp == kPhases - 1) ? Ttot - at : (Ttot - at + 1) / 2;
-            if (pp == p) { lo = at; len = step; }
+            if (pp == p) len = step;
             at += step;
         }
         return (int)((long long)len * j / G) == (int)((long long)len * (j + 1) / G);
     };
-    for (int e = threadIdx.x; e < NREP * D; e += blockDim.x) {
-        const int r = e / D, d = e - r * D;
-        float M = -INFINITY, Lsum = 0.f, acc = 0.f;
-#pragma unroll 8
-        for (int c = u_first; c <= u_last; ++c) {
-            if (maybe_empty && empty_unit(c)) continue;                        // an empty unit wrote nothing
-            const float* src = prm.ws + (((size_t)c * 2 + (c == u_first ? first_slot : 0)) * NREP + r) * (D + 2);
-            const float mc = __ldcg(src), lc = __ldcg(src + 1), x = __ldcg(src + 2 + d);
-            const float Mn = fmaxf(M, mc);
-            const float a = (Mn == -INFINITY) ? 0.f : exp2f(M - Mn), w = (mc == -INFINITY) ? 0.f : exp2f(mc - Mn);
-            Lsum = Lsum * a + lc * w;
-            acc = acc * a + x * w;
-            M = Mn;
+    // group g takes units u_first + g, u_first + g + kFinishGroups, ...: all loads of a thread are independent
+    float M = -INFINITY, Lsum = 0.f;
+    float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll 4
+    for (int c = u_first + grp; c <= u_last; c += kFinishGroups) {
+        if (maybe_empty && empty_unit(c)) continue;                            // an empty unit wrote nothing
+        const float* src = prm.ws + (((size_t)c * 2 + (c == u_first ? first_slot : 0)) * NREP + r) * (D + 2);
+        const float2 ml = __ldcg(reinterpret_cast<const float2*>(src));
+        const float2 x01 = __ldcg(reinterpret_cast<const float2*>(src + 2 + d4));   // rows are 8-byte aligned
+        const float2 x23 = __ldcg(reinterpret_cast<const float2*>(src + 4 + d4));
+        const float Mn = fmaxf(M, ml.x);
+        const float a = (Mn == -INFINITY) ? 0.f : exp2f(M - Mn), w = (ml.x == -INFINITY) ? 0.f : exp2f(ml.x - Mn);
+        Lsum = Lsum * a + ml.y * w;
+        acc.x = acc.x * a + x01.x * w; acc.y = acc.y * a + x01.y * w;
+        acc.z = acc.z * a + x23.x * w; acc.w = acc.w * a + x23.y * w;
+        M = Mn;
+    }
+    s_acc[grp][v4] = acc;
+    if (d4 == 0) s_ml[grp][r] = make_float2(M, Lsum);
+    __syncthreads();
+    if (grp == 0) {
+        float Mt = -INFINITY;
+#pragma unroll
+        for (int g = 0; g < kFinishGroups; ++g) Mt = fmaxf(Mt, s_ml[g][r].x);
+        float Lt = 0.f;
+        float4 o = make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+        for (int g = 0; g < kFinishGroups; ++g) {
+            const float2 ml = s_ml[g][r];
+            if (ml.x == -INFINITY) continue;
+            const float w = exp2f(ml.x - Mt);
+            const float4 x = s_acc[g][v4];
+            Lt += ml.y * w;
+            o.x += x.x * w; o.y += x.y * w; o.z += x.z * w; o.w += x.w * w;
         }
+        const float inv = Lt > 0.f ? 1.f / Lt : 0.f;
         const int hq = h * NREP + r;
-        out[((size_t)b * Hq + hq) * D + d] = ElemTraits<T>::from_float(Lsum > 0.f ? acc / Lsum : 0.f);
-        if (d == 0) prm.lse[(size_t)b * Hq + hq] = Lsum > 0.f ? (M + log2f(Lsum)) * kLn2 : -INFINITY;
+        T* dst = out + ((size_t)b * Hq + hq) * D + d4;
+        dst[0] = ElemTraits<T>::from_float(o.x * inv); dst[1] = ElemTraits<T>::from_float(o.y * inv);
+        dst[2] = ElemTraits<T>::from_float(o.z * inv); dst[3] = ElemTraits<T>::from_float(o.w * inv);
+        if (d4 == 0) prm.lse[(size_t)b * Hq + hq] = Lt > 0.f ? (Mt + log2f(Lt)) * kLn2 : -INFINITY;
     }
 #ifdef FPKV_PROFILE
     if (threadIdx.x == 0) g_fin_times[blockIdx.x % 1024][2] = gtime();
@@ -753,7 +784,7 @@ int launch_one(const CUtensorMap& map, Params prm, int G, cudaStream_t stream)
     }
     // the finish kernel may become resident while the main grid runs; it waits for it on the device
     cudaLaunchConfig_t cfg = {};
-    cfg.gridDim = dim3(prm.B * prm.Hkv); cfg.blockDim = dim3(NREP * D >= 256 ? 256 : NREP * D); cfg.dynamicSmemBytes = 0; cfg.stream = stream;
+    cfg.gridDim = dim3(prm.B * prm.Hkv); cfg.blockDim = dim3(kFinishGroups * NREP * D / 4); cfg.dynamicSmemBytes = 0; cfg.stream = stream;
     cfg.attrs = attr; cfg.numAttrs = 1;
     return cudaLaunchKernelEx(&cfg, decode_tma_finish_kernel<T, D, NREP>, prm, G) == cudaSuccess ? FPKV_OK
                                                                                                   : FPKV_ELAUNCH;
