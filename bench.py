@@ -496,6 +496,104 @@ def run_prefill(args):
         "clocks": clocks}), flush=True)
 
 
+def run_stack(args):
+    """Secondary workload (config 5): decode steps of a 28-layer random-init dense GQA decoder stack (hidden 2048,
+    16 q heads / 8 kv heads, head_dim 128, gated squared-ReLU FFN of 6144, bf16) over 64 sequences per GPU with
+    context uniform in [2048, 8192]; every layer does append + paged attention through fpkv, the projections and
+    the FFN are torch GEMMs (library code, not part of the path under test).  The whole step is replayed from a
+    CUDA graph.  Metric: decode tokens/s of the whole job (512 sequences at 8 GPUs, 64 per GPU: weak scaling)."""
+    import torch.distributed as dist
+    import torch.nn.functional as F
+    from fpkv import workloads as wl
+    from fpkv.paged_attention import PagedKVCache
+    world = int(os.environ.get("WORLD_SIZE", "1")); rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    assert torch.cuda.is_available(), "bench.py needs a CUDA device; there is no CPU path for the product"
+    torch.cuda.set_device(local); device = torch.device("cuda", local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=device)
+    NL, HID, FFN, B = 28, 2048, 6144, BATCH
+    K, W = min(args.steps, 256), args.warmup
+    case = wl.config2_case(B=B, n_pages=4352, len_lo=2048, len_hi=8192, seed=5005 + rank)
+    cache = PagedKVCache(4352, P, B + 1, HKV, D, NL, torch.bfloat16, device)      # 61 GB of pool per GPU
+    cache.free_pages = list(case.free_pages)
+    slots = []
+    for L in case.lens:
+        s = cache.allocate(); slots.append(s); cache.reserve(s, None, L + 1 + WINDOW)
+    cache.kv_cache.normal_(0, D ** -0.5)
+    g = torch.Generator(device=device).manual_seed(5005 + rank)
+    w = lambda *shape: (torch.randn(shape, device=device, generator=g) * 0.02).to(torch.bfloat16)
+    layers = [dict(qkv=w(HID, (HQ + 2 * HKV) * D), wo=w(HQ * D, HID), up=w(HID, 2 * FFN), down=w(FFN, HID))
+              for _ in range(NL)]
+    bidx = torch.tensor(slots, dtype=torch.int64, device=device)
+    pos = torch.tensor(case.lens, dtype=torch.int32, device=device)
+    x0 = torch.randn((B, HID), device=device, generator=g).to(torch.bfloat16)
+    attn_out = torch.empty((B, HQ, 1, D), dtype=torch.bfloat16, device=device)
+    lse = torch.empty((B, HQ, 1), dtype=torch.float32, device=device)
+
+    def step(x, attention_only=False):
+        for li, lw in enumerate(layers):
+            if attention_only:
+                qkv = x_qkv
+            else:
+                qkv = F.rms_norm(x, (HID,)) @ lw["qkv"]
+            q = qkv[:, :HQ * D].view(B, 1, HQ, D).permute(0, 2, 1, 3)
+            k = qkv[:, HQ * D:(HQ + HKV) * D].view(B, 1, HKV, D).permute(0, 2, 1, 3)
+            v = qkv[:, (HQ + HKV) * D:].view(B, 1, HKV, D).permute(0, 2, 1, 3)
+            cache.decode_step(li, q, k, v, bidx, pos, out=attn_out, lse=lse)
+            if attention_only:
+                continue
+            x = x + attn_out.view(B, HQ * D) @ lw["wo"]
+            gu = F.rms_norm(x, (HID,)) @ lw["up"]
+            x = x + (F.relu(gu[:, :FFN]).square() * gu[:, FFN:]) @ lw["down"]
+        return x
+    x_qkv = (torch.randn((B, (HQ + 2 * HKV) * D), device=device, generator=g) * D ** -0.5).to(torch.bfloat16)
+
+    def timed(attention_only):
+        side = torch.cuda.Stream(device)
+        side.wait_stream(torch.cuda.current_stream(device))
+        with torch.cuda.stream(side):
+            step(x0, attention_only)
+        side.synchronize()
+        gr = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(gr, stream=side):
+            y = step(x0, attention_only)
+        for _ in range(W):
+            gr.replay()
+        torch.cuda.synchronize(device)
+        if world > 1:
+            dist.barrier()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for i in range(K):
+            pos.add_(1 if (i % WINDOW) != WINDOW - 1 else -(WINDOW - 1))     # positions advance and wrap (device op)
+            gr.replay()
+        e1.record()
+        torch.cuda.synchronize(device)
+        pos.copy_(torch.tensor(case.lens, dtype=torch.int32))
+        return e0.elapsed_time(e1) / K
+    ms_full = timed(False)
+    ms_attn = timed(True)
+    cache.check_status()
+    kv_bytes = float(NL * sum((L + WINDOW // 2) * 2 * HKV * D * 2 for L in case.lens))
+    (ms_full, ms_attn), (tokens, kvb) = reduce_over_ranks([ms_full, ms_attn], [float(B), kv_bytes], device, world)
+    if rank == 0:
+        print(json.dumps({
+            "metric": "stack_decode_tokens_per_s", "value": tokens / (ms_full * 1e-3), "unit": "tokens/s",
+            "n_gpus": world, "steps": K, "warmup": W, "ms_per_step": ms_full, "higher_is_better": True,
+            "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+            "config": {"workload": "config 5: 28-layer random-init dense GQA decoder stack, hidden 2048, 16 q / 8 kv "
+                                   "heads, head_dim 128, FFN 6144, 64 sequences per GPU, context uniform [2048,8192]; "
+                                   "append + paged attention per layer through fpkv, projections/FFN torch GEMMs, "
+                                   "CUDA-graph replay", "seed": 5005},
+            "attention_only": {"tokens_per_s": tokens / (ms_attn * 1e-3), "ms_per_step": ms_attn,
+                               "kv_gbps": kvb / (ms_attn * 1e-3) / 1e9,
+                               "pct_of_nominal_hbm_8000": 100.0 * kvb / world / (ms_attn * 1e-3) / 1e9 / 8000.0},
+            "gpu_launches": 3 * NL * K}), flush=True)
+    if world > 1:
+        dist.destroy_process_group()
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -509,14 +607,17 @@ def main():
     ap.add_argument("--len-hi", type=int, default=LEN_HI)
     ap.add_argument("--kernels-only", action="store_true",
                     help="run only the device-resident loop (no host-buffer loop, no CPU baseline): for profilers")
-    ap.add_argument("--workload", default="decode", choices=["decode", "prefill"],
-                    help="decode = config 2 (the headline metric); prefill = config 3's prefill part (tensor-bound)")
+    ap.add_argument("--workload", default="decode", choices=["decode", "prefill", "stack"],
+                    help="decode = config 2 (the headline metric); prefill = config 3's prefill part (tensor-bound); "
+                         "stack = config 5's 28-layer decoder stack (decode tokens/s)")
     args = ap.parse_args()
     args.warmup = max(args.warmup, 3)
     if args.impl == "reference":
         run_reference(args)
     elif args.workload == "prefill":
         run_prefill(args)
+    elif args.workload == "stack":
+        run_stack(args)
     else:
         run_fpkv(args)
 
