@@ -120,10 +120,16 @@ class ClockSampler:
                 "reasons": [n for n, b in self.REASONS if self.bits & b], "samples": len(v)}
 
 
-def rank_seed(rank):
-    """Every rank owns its own pool and its own batch of sequences: shard r of the job is the seeded
-    config-2 draw with seed 2002 + r (rank 0 alone is the single-GPU workload)."""
-    return 2002 + rank
+def rank_case(rank, batch=BATCH, n_pages=N_PAGES, len_lo=LEN_LO, len_hi=LEN_HI, seed=2002):
+    """The shard of the job that rank ``rank`` owns.  Weak scaling: every rank gets the same amount of work
+    -- the seeded context lengths of the single-GPU workload -- in its own pool, with its own page
+    permutation (so the page tables differ from rank to rank); rank 0 alone is the single-GPU workload."""
+    import numpy as np
+    from fpkv import workloads as wl
+    case = wl.config2_case(B=batch, n_pages=n_pages, len_lo=len_lo, len_hi=len_hi, seed=seed)
+    if rank:
+        case.free_pages = (np.random.default_rng(seed + 7919 * rank).permutation(n_pages - 1) + 1).tolist()
+    return case
 
 
 def reduce_over_ranks(times_ms, work, device, world):
@@ -142,7 +148,7 @@ def build_gpu_workload(rank, device, n_steps, n_pages=N_PAGES, batch=BATCH, len_
     """Cache with 64 seeded sequences whose context pages hold random values."""
     from fpkv import workloads as wl
     from fpkv.paged_attention import PagedKVCache
-    case = wl.config2_case(B=batch, n_pages=n_pages, len_lo=len_lo, len_hi=len_hi, seed=rank_seed(rank))
+    case = rank_case(rank, batch, n_pages, len_lo, len_hi)
     cache = PagedKVCache(n_pages, P, batch + 1, HKV, D, 1, torch.bfloat16, device)
     cache.free_pages = list(case.free_pages)
     slots = []
@@ -514,7 +520,7 @@ def run_stack(args):
         dist.init_process_group("nccl", device_id=device)
     NL, HID, FFN, B = 28, 2048, 6144, BATCH
     K, W = min(args.steps, 256), args.warmup
-    case = wl.config2_case(B=B, n_pages=4352, len_lo=2048, len_hi=8192, seed=5005 + rank)
+    case = rank_case(rank, B, 4352, 2048, 8192, seed=5005)
     cache = PagedKVCache(4352, P, B + 1, HKV, D, NL, torch.bfloat16, device)      # 61 GB of pool per GPU
     cache.free_pages = list(case.free_pages)
     slots = []

@@ -1,6 +1,6 @@
 """CPU, world_size 2 over gloo: the multi-GPU plan has no data-path collective;
-each rank owns a shard of the job (its own seeded batch, its own pool and free
-lists) and the report is MAX-of-times / SUM-of-work over ranks."""
+each rank owns a shard of the job (the same seeded amount of work in its own
+pool with its own page permutation and free lists) and the report is MAX-of-times / SUM-of-work over ranks."""
 
 import os
 import socket
@@ -20,10 +20,9 @@ def _worker(rank, world, port, out):
     os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), RANK=str(rank), WORLD_SIZE=str(world))
     dist.init_process_group("gloo", rank=rank, world_size=world)
     import bench
-    from fpkv import workloads as wl
     from fpkv.paged_attention import PagedKVCache
     # the rank's shard: its own draw, its own (CPU, bookkeeping-only) cache and allocator state
-    case = wl.config2_case(B=8, n_pages=512, len_lo=100, len_hi=900, seed=bench.rank_seed(rank))
+    case = bench.rank_case(rank, batch=8, n_pages=512, len_lo=100, len_hi=900)
     cache = PagedKVCache(512, 128, 9, 8, 128, 1, torch.bfloat16, "cpu")
     cache.free_pages = list(case.free_pages)
     slots = []
@@ -55,11 +54,10 @@ def test_two_rank_shards_and_report():
     assert res["ms"] == 2.0                             # MAX over ranks
     assert res["tokens"] == 16.0                        # SUM over ranks
     assert abs(res["total_bytes"] - (r0["bytes"] + r1["bytes"])) < 1e-6
-    assert r0["lens"] != r1["lens"]                     # different shards of the job ...
+    assert r0["lens"] == r1["lens"]                     # weak scaling: the same work on every rank ...
+    assert r0["pages"] != r1["pages"]                   # ... in its own pool with its own page permutation
     import bench
-    from fpkv import workloads as wl
-    assert r0["lens"] == wl.config2_case(B=8, n_pages=512, len_lo=100, len_hi=900,
-                                         seed=bench.rank_seed(0)).lens   # ... each reproducible from its rank
+    assert r0["lens"] == bench.rank_case(0, batch=8, n_pages=512, len_lo=100, len_hi=900).lens
     # every rank allocates from its own pool: page ids overlap freely between ranks, never within one
     for r in (r0, r1):
         flat = [p for seq in r["pages"] for p in seq]
