@@ -47,6 +47,16 @@ int check_rows(const void* p, long long s0, long long s1, int esize) {
     return FPKV_OK;
 }
 
+// The optional epilogue descriptor of the attention entry points.
+int make_epilogue(const fpkv_epilogue* e, int n_q_heads, Epilogue* out) {
+    out->sinks = nullptr; out->sinks_dtype = FPKV_F32; out->token_major = 0;
+    if (e == nullptr) return FPKV_OK;
+    if (e->sinks != nullptr && esize_of(e->sinks_dtype) == 0) return FPKV_EDTYPE;
+    (void)n_q_heads;
+    out->sinks = e->sinks; out->sinks_dtype = e->sinks_dtype; out->token_major = e->token_major != 0;
+    return FPKV_OK;
+}
+
 int check_arch() {
     int dev = 0, major = 0;
     if (cudaGetDevice(&dev) != cudaSuccess) return FPKV_EARCH;
@@ -142,11 +152,14 @@ int fpkv_decode_workspace_bytes(const fpkv_pool* pool, int32_t B, int32_t n_q_he
 int fpkv_decode_attn(const fpkv_pool* pool, int32_t layer, void* out, float* lse, const void* q,
                      int64_t q_stride_b, int64_t q_stride_h, const int64_t* batch_idx, const void* input_pos,
                      int32_t pos_type, int32_t B, int32_t n_q_heads, float sm_scale, void* workspace,
-                     size_t workspace_bytes, int32_t flags, int32_t* status, void* stream)
+                     size_t workspace_bytes, int32_t flags, const fpkv_epilogue* epilogue, int32_t* status,
+                     void* stream)
 {
     PoolView pv;
     int rc = make_view(pool, layer, &pv);
     if (rc) return rc;
+    Epilogue epi;
+    if ((rc = make_epilogue(epilogue, n_q_heads, &epi))) return rc;
     if (B < 0 || n_q_heads <= 0 || (pos_type != FPKV_I32 && pos_type != FPKV_I64)) return FPKV_EINVAL;
     if (n_q_heads % pv.H) return FPKV_ESHAPE;
     if (B == 0) return FPKV_OK;
@@ -165,20 +178,23 @@ int fpkv_decode_attn(const fpkv_pool* pool, int32_t layer, void* out, float* lse
     if ((rc = check_arch())) return rc;
     cudaStream_t s = static_cast<cudaStream_t>(stream);
     return use_tma ? launch_decode_tma(pv, layer, out, lse, q, q_stride_b, q_stride_h, batch_idx, input_pos,
-                                       pos_type, B, n_q_heads, sm_scale, workspace, status, s,
+                                       pos_type, B, n_q_heads, sm_scale, workspace, epi, status, s,
                                        (flags & FPKV_DECODE_AFTER_APPEND) != 0)
                    : launch_decode_portable(pv, layer, out, lse, q, q_stride_b, q_stride_h, batch_idx,
                                             input_pos, pos_type, B, n_q_heads, sm_scale,
-                                            static_cast<char*>(workspace) + kCounterBytes, status, s);
+                                            static_cast<char*>(workspace) + kCounterBytes, epi, status, s);
 }
 
 int fpkv_prefill_attn(const fpkv_pool* pool, int32_t layer, void* out, float* lse, const void* q,
                       int64_t q_stride_h, int64_t q_stride_t, const int64_t* batch_idx, const int32_t* extent,
-                      int32_t L, int32_t n_q_heads, float sm_scale, int32_t flags, int32_t* status, void* stream)
+                      int32_t L, int32_t n_q_heads, float sm_scale, int32_t flags, const fpkv_epilogue* epilogue,
+                      int32_t* status, void* stream)
 {
     PoolView pv;
     int rc = make_view(pool, layer, &pv);
     if (rc) return rc;
+    Epilogue epi;
+    if ((rc = make_epilogue(epilogue, n_q_heads, &epi))) return rc;
     if (L < 0 || n_q_heads <= 0) return FPKV_EINVAL;
     if (n_q_heads % pv.H) return FPKV_ESHAPE;
     if (L == 0) return FPKV_OK;
@@ -191,9 +207,9 @@ int fpkv_prefill_attn(const fpkv_pool* pool, int32_t layer, void* out, float* ls
     if ((rc = check_arch())) return rc;
     if (which == FPKV_PREFILL_TC || (which == FPKV_PREFILL_AUTO && tc_ok))
         return launch_prefill_tc(pv, layer, out, lse, q, q_stride_h, q_stride_t, batch_idx, extent, L, n_q_heads,
-                                 sm_scale, status, static_cast<cudaStream_t>(stream));
+                                 sm_scale, epi, status, static_cast<cudaStream_t>(stream));
     return launch_prefill_portable(pv, layer, out, lse, q, q_stride_h, q_stride_t, batch_idx, extent, L, n_q_heads,
-                                   sm_scale, status, static_cast<cudaStream_t>(stream));
+                                   sm_scale, epi, status, static_cast<cudaStream_t>(stream));
 }
 
 }  // extern "C"

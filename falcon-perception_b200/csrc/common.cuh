@@ -49,6 +49,29 @@ template <> struct ElemTraits<__half> {
     static __device__ __forceinline__ __half from_float(float x) { return __float2half_rn(x); }
 };
 
+// Optional epilogue of the attention kernels: the sink gate of the reference's _post_attention
+// (falcon_perception/model.py:122-128), out * sigmoid(lse - sinks[head]), and for prefill the
+// (L, heads * head_dim) output layout its output projection reads.  The gate is applied to the
+// already rounded output and rounded again, as the reference's two-step computation does.
+struct Epilogue {
+    const void* sinks;      // device (n_q_heads) or nullptr: no gate
+    int sinks_dtype;        // fpkv_dtype
+    int token_major;        // prefill only: out as (1, L, n_q_heads, head_dim)
+};
+__device__ __forceinline__ float sink_gate(const Epilogue& e, int hq, float lse_natural) {
+    if (e.sinks == nullptr) return 1.f;
+    float sk;
+    if (e.sinks_dtype == FPKV_F32) sk = reinterpret_cast<const float*>(e.sinks)[hq];
+    else if (e.sinks_dtype == FPKV_BF16) sk = __bfloat162float(reinterpret_cast<const __nv_bfloat16*>(e.sinks)[hq]);
+    else sk = __half2float(reinterpret_cast<const __half*>(e.sinks)[hq]);
+    return 1.f / (1.f + __expf(sk - lse_natural));          // lse = -inf -> 0
+}
+template <typename T>
+__device__ __forceinline__ T gated_out(float o, float gate, bool on) {
+    const T r = ElemTraits<T>::from_float(o);
+    return on ? ElemTraits<T>::from_float(ElemTraits<T>::to_float(r) * gate) : r;
+}
+
 // ---- launchers implemented in the .cu files (host side, internal) ----------
 int launch_append(const PoolView& pv, int layer, const int64_t* batch_idx, const void* pos, int pos_type,
                   const void* k, long long k_stride_tok, long long k_stride_h,
@@ -62,21 +85,21 @@ size_t decode_portable_workspace_bytes(int B, int Hq, int D);
 int launch_decode_portable(const PoolView& pv, int layer, void* out, float* lse, const void* q,
                            long long q_stride_b, long long q_stride_h, const int64_t* batch_idx,
                            const void* pos, int pos_type, int B, int Hq, float sm_scale,
-                           void* workspace, int32_t* status, cudaStream_t stream);
+                           void* workspace, const Epilogue& epi, int32_t* status, cudaStream_t stream);
 
 bool decode_tma_supported(const PoolView& pv, int Hq);
 size_t decode_tma_workspace_bytes(int Hq, int Hkv, int D);
 int launch_decode_tma(const PoolView& pv, int layer, void* out, float* lse, const void* q,
                       long long q_stride_b, long long q_stride_h, const int64_t* batch_idx,
                       const void* pos, int pos_type, int B, int Hq, float sm_scale,
-                      void* workspace, int32_t* status, cudaStream_t stream, bool after_append);
+                      void* workspace, const Epilogue& epi, int32_t* status, cudaStream_t stream, bool after_append);
 
 int launch_prefill_portable(const PoolView& pv, int layer, void* out, float* lse, const void* q, long long q_stride_h,
                             long long q_stride_t, const int64_t* batch_idx, const int32_t* extent, int L, int Hq,
-                            float sm_scale, int32_t* status, cudaStream_t stream);
+                            float sm_scale, const Epilogue& epi, int32_t* status, cudaStream_t stream);
 bool prefill_tc_supported(const PoolView& pv, int Hq);
 int launch_prefill_tc(const PoolView& pv, int layer, void* out, float* lse, const void* q, long long q_stride_h,
                       long long q_stride_t, const int64_t* batch_idx, const int32_t* extent, int L, int Hq,
-                      float sm_scale, int32_t* status, cudaStream_t stream);
+                      float sm_scale, const Epilogue& epi, int32_t* status, cudaStream_t stream);
 
 }  // namespace fpkv

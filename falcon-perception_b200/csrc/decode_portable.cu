@@ -48,7 +48,7 @@ decode_portable_kernel(const char* __restrict__ pool_layer, size_t plane_bytes, 
                        const int64_t* __restrict__ batch_idx, const PosT* __restrict__ pos,
                        const int32_t* __restrict__ extent,
                        int Hq, float scale_log2, float* __restrict__ ws, T* __restrict__ out, float* __restrict__ lse,
-                       OutLayout lay, int32_t* status)
+                       OutLayout lay, Epilogue epi, int32_t* status)
 {
     constexpr int E = D / 32;                     // elements per lane
     const int row = blockIdx.x;                   // b * Hq + hq
@@ -125,16 +125,18 @@ decode_portable_kernel(const char* __restrict__ pool_layer, size_t plane_bytes, 
     for (int w = 0; w < kPortableWarps; ++w)
         if (sm_m[w] != -INFINITY) L += sm_l[w] * exp2f(sm_m[w] - M);
     float* dst = DIRECT ? nullptr : ws + ((size_t)row * S + split) * (D + 2);
+    const float lse_nat = L > 0.f ? (M + log2f(L)) * kLn2 : -INFINITY;
+    const float gate = DIRECT ? sink_gate(epi, hq, lse_nat) : 1.f;
     for (int d = threadIdx.x; d < D; d += blockDim.x) {
         float o = 0.f;
 #pragma unroll
         for (int w = 0; w < kPortableWarps; ++w)
             if (sm_m[w] != -INFINITY) o += sm_acc[w][d] * exp2f(sm_m[w] - M);
-        if (DIRECT) out[b * lay.out_row + hq * lay.out_head + d] = ElemTraits<T>::from_float(L > 0.f ? o / L : 0.f);
+        if (DIRECT) out[b * lay.out_row + hq * lay.out_head + d] = gated_out<T>(L > 0.f ? o / L : 0.f, gate, epi.sinks != nullptr);
         else dst[2 + d] = o;
     }
     if (threadIdx.x == 0) {
-        if (DIRECT) lse[b * lay.lse_row + hq * lay.lse_head] = L > 0.f ? (M + log2f(L)) * kLn2 : -INFINITY;
+        if (DIRECT) lse[b * lay.lse_row + hq * lay.lse_head] = lse_nat;
         else { dst[0] = M; dst[1] = L; }
     }
 }
@@ -142,7 +144,8 @@ decode_portable_kernel(const char* __restrict__ pool_layer, size_t plane_bytes, 
 // Merge S partials of each (b, hq) row: out = sum_s acc_s 2^(m_s - M) / L.
 template <typename T, int D>
 __global__ void __launch_bounds__(D)
-decode_portable_merge_kernel(const float* __restrict__ ws, int S, T* __restrict__ out, float* __restrict__ lse)
+decode_portable_merge_kernel(const float* __restrict__ ws, int S, T* __restrict__ out, float* __restrict__ lse,
+                             int Hq, Epilogue epi)
 {
     const int row = blockIdx.x, d = threadIdx.x;
     const float* src = ws + (size_t)row * S * (D + 2);
@@ -156,8 +159,9 @@ decode_portable_merge_kernel(const float* __restrict__ ws, int S, T* __restrict_
         L += src[s * (D + 2) + 1] * w;
         o += src[s * (D + 2) + 2 + d] * w;
     }
-    out[(size_t)row * D + d] = ElemTraits<T>::from_float(L > 0.f ? o / L : 0.f);
-    if (d == 0) lse[row] = L > 0.f ? (M + log2f(L)) * kLn2 : -INFINITY;
+    const float lse_nat = L > 0.f ? (M + log2f(L)) * kLn2 : -INFINITY;
+    out[(size_t)row * D + d] = gated_out<T>(L > 0.f ? o / L : 0.f, sink_gate(epi, row % Hq, lse_nat), epi.sinks != nullptr);
+    if (d == 0) lse[row] = lse_nat;
 }
 
 size_t decode_portable_workspace_bytes(int B, int Hq, int D) {
@@ -168,37 +172,37 @@ template <typename T, int D, typename PosT>
 static int launch_typed(const PoolView& pv, int layer, void* out, float* lse, const void* q,
                         long long q_stride_b, long long q_stride_h, const int64_t* batch_idx,
                         const void* pos, int B, int Hq, float sm_scale, void* workspace,
-                        int32_t* status, cudaStream_t stream)
+                        const Epilogue& epi, int32_t* status, cudaStream_t stream)
 {
     const int S = portable_splits(B, Hq);
     dim3 grid(B * Hq, S);
     decode_portable_kernel<T, D, PosT, false><<<grid, kPortableWarps * 32, 0, stream>>>(
         pv.plane(layer, 0, 0), pv.plane_bytes(), pv.H, pv.page_table, pv.p2l, pv.n_pages, pv.max_batch, pv.P,
         (const T*)q, q_stride_b, q_stride_h, batch_idx, (const PosT*)pos, nullptr, Hq, sm_scale * kLog2e,
-        (float*)workspace, nullptr, nullptr, OutLayout{0, 0, 0, 0}, status);
+        (float*)workspace, nullptr, nullptr, OutLayout{0, 0, 0, 0}, Epilogue{nullptr, 0, 0}, status);
     if (cudaGetLastError() != cudaSuccess) return FPKV_ELAUNCH;
-    decode_portable_merge_kernel<T, D><<<B * Hq, D, 0, stream>>>((const float*)workspace, S, (T*)out, lse);
+    decode_portable_merge_kernel<T, D><<<B * Hq, D, 0, stream>>>((const float*)workspace, S, (T*)out, lse, Hq, epi);
     return cudaGetLastError() == cudaSuccess ? FPKV_OK : FPKV_ELAUNCH;
 }
 
 template <typename T, int D>
 static int launch_pos(const PoolView& pv, int layer, void* out, float* lse, const void* q, long long qsb,
                       long long qsh, const int64_t* bi, const void* pos, int pos_type, int B, int Hq,
-                      float sc, void* ws, int32_t* st, cudaStream_t s)
+                      float sc, void* ws, const Epilogue& epi, int32_t* st, cudaStream_t s)
 {
     return pos_type == FPKV_I32
-        ? launch_typed<T, D, int32_t>(pv, layer, out, lse, q, qsb, qsh, bi, pos, B, Hq, sc, ws, st, s)
-        : launch_typed<T, D, int64_t>(pv, layer, out, lse, q, qsb, qsh, bi, pos, B, Hq, sc, ws, st, s);
+        ? launch_typed<T, D, int32_t>(pv, layer, out, lse, q, qsb, qsh, bi, pos, B, Hq, sc, ws, epi, st, s)
+        : launch_typed<T, D, int64_t>(pv, layer, out, lse, q, qsb, qsh, bi, pos, B, Hq, sc, ws, epi, st, s);
 }
 
 int launch_decode_portable(const PoolView& pv, int layer, void* out, float* lse, const void* q,
                            long long qsb, long long qsh, const int64_t* bi, const void* pos, int pos_type,
-                           int B, int Hq, float sc, void* ws, int32_t* st, cudaStream_t s)
+                           int B, int Hq, float sc, void* ws, const Epilogue& epi, int32_t* st, cudaStream_t s)
 {
     if (B == 0) return FPKV_OK;
 #define FPKV_DISPATCH(T)                                                                              \
-    return pv.D == 64 ? launch_pos<T, 64>(pv, layer, out, lse, q, qsb, qsh, bi, pos, pos_type, B, Hq, sc, ws, st, s) \
-                      : launch_pos<T, 128>(pv, layer, out, lse, q, qsb, qsh, bi, pos, pos_type, B, Hq, sc, ws, st, s)
+    return pv.D == 64 ? launch_pos<T, 64>(pv, layer, out, lse, q, qsb, qsh, bi, pos, pos_type, B, Hq, sc, ws, epi, st, s) \
+                      : launch_pos<T, 128>(pv, layer, out, lse, q, qsb, qsh, bi, pos, pos_type, B, Hq, sc, ws, epi, st, s)
     switch (pv.dtype) {
         case FPKV_F32:  FPKV_DISPATCH(float);
         case FPKV_BF16: FPKV_DISPATCH(__nv_bfloat16);
@@ -213,16 +217,17 @@ int launch_decode_portable(const PoolView& pv, int layer, void* out, float* lse,
 template <typename T, int D>
 static int launch_prefill_typed(const PoolView& pv, int layer, void* out, float* lse, const void* q, long long qsh,
                                 long long qst, const int64_t* bi, const int32_t* extent, int L, int Hq, float sc,
-                                int32_t* st, cudaStream_t s)
+                                const Epilogue& epi, int32_t* st, cudaStream_t s)
 {
-    const OutLayout lay{(long long)D, (long long)L * D, 1, (long long)L};
+    const OutLayout lay = epi.token_major ? OutLayout{(long long)Hq * D, (long long)D, 1, (long long)L}
+                                          : OutLayout{(long long)D, (long long)L * D, 1, (long long)L};
     for (int t0 = 0; t0 < L; t0 += 32768) {            // grid.x = rows * heads stays far below its limit
         const int n = L - t0 < 32768 ? L - t0 : 32768;
         dim3 grid(n * Hq, 1);
         decode_portable_kernel<T, D, int32_t, true><<<grid, kPortableWarps * 32, 0, s>>>(
             pv.plane(layer, 0, 0), pv.plane_bytes(), pv.H, pv.page_table, pv.p2l, pv.n_pages, pv.max_batch, pv.P,
             (const T*)q + (long long)t0 * qst, qst, qsh, bi + t0, nullptr, extent + t0, Hq, sc * kLog2e, nullptr,
-            (T*)out + (long long)t0 * D, lse + t0, lay, st);
+            (T*)out + (long long)t0 * lay.out_row, lse + t0, lay, epi, st);
         if (cudaGetLastError() != cudaSuccess) return FPKV_ELAUNCH;
     }
     return FPKV_OK;
@@ -230,12 +235,12 @@ static int launch_prefill_typed(const PoolView& pv, int layer, void* out, float*
 
 int launch_prefill_portable(const PoolView& pv, int layer, void* out, float* lse, const void* q, long long qsh,
                             long long qst, const int64_t* bi, const int32_t* extent, int L, int Hq, float sc,
-                            int32_t* st, cudaStream_t s)
+                            const Epilogue& epi, int32_t* st, cudaStream_t s)
 {
     if (L == 0) return FPKV_OK;
 #define FPKV_DISPATCH(T)                                                                                   \
-    return pv.D == 64 ? launch_prefill_typed<T, 64>(pv, layer, out, lse, q, qsh, qst, bi, extent, L, Hq, sc, st, s) \
-                      : launch_prefill_typed<T, 128>(pv, layer, out, lse, q, qsh, qst, bi, extent, L, Hq, sc, st, s)
+    return pv.D == 64 ? launch_prefill_typed<T, 64>(pv, layer, out, lse, q, qsh, qst, bi, extent, L, Hq, sc, epi, st, s) \
+                      : launch_prefill_typed<T, 128>(pv, layer, out, lse, q, qsh, qst, bi, extent, L, Hq, sc, epi, st, s)
     switch (pv.dtype) {
         case FPKV_F32:  FPKV_DISPATCH(float);
         case FPKV_BF16: FPKV_DISPATCH(__nv_bfloat16);

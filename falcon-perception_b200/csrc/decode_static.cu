@@ -63,5 +63,5 @@ extern "C" int fpkv_decode_attn_static(const fpkv_pool* pool, int32_t layer, voi
     if (cudaMemsetAsync(scratch, 0, 1024, static_cast<cudaStream_t>(stream)) != cudaSuccess) return FPKV_ELAUNCH;
     return fpkv_decode_attn(pool, layer, out, lse, q, q_stride_b, q_stride_h, batch_idx, input_pos, pos_type, B,
                             n_q_heads, sm_scale, scratch, (size_t)FPKV_STATIC_SCRATCH_BYTES, FPKV_DECODE_TMA,
-                            status, stream);
+                            nullptr, status, stream);
 }

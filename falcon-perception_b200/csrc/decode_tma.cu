@@ -168,6 +168,7 @@ struct Params {
     int after_append;          // 1: the preceding kernel on the stream is this library's append and writes only the pool
     int rows_per_plane;        // n_pages * P: token rows of one (K|V, head) plane
     float scale_log2;
+    Epilogue epi;
 };
 
 #ifdef FPKV_PROFILE
@@ -624,8 +625,10 @@ decode_tma_kernel(const __grid_constant__ CUtensorMap tmap, const Params prm)
                 }
                 const int hq = h * NREP + r;
                 if (direct) {
-                    out[((size_t)b * Hq + hq) * D + d] = ElemTraits<T>::from_float(Lsum > 0.f ? acc / Lsum : 0.f);
-                    if (d == 0) prm.lse[(size_t)b * Hq + hq] = Lsum > 0.f ? (M + log2f(Lsum)) * kLn2 : -INFINITY;
+                    const float lse_nat = Lsum > 0.f ? (M + log2f(Lsum)) * kLn2 : -INFINITY;
+                    out[((size_t)b * Hq + hq) * D + d] = gated_out<T>(Lsum > 0.f ? acc / Lsum : 0.f,
+                                                                      sink_gate(prm.epi, hq, lse_nat), prm.epi.sinks != nullptr);
+                    if (d == 0) prm.lse[(size_t)b * Hq + hq] = lse_nat;
                 } else {
                     float* dst = prm.ws + (((size_t)u * 2 + ws_slot) * NREP + r) * (D + 2);
                     __stcg(dst + 2 + d, acc);
@@ -722,10 +725,13 @@ decode_tma_finish_kernel(const Params prm, int G)
         }
         const float inv = Lt > 0.f ? 1.f / Lt : 0.f;
         const int hq = h * NREP + r;
+        const float lse_nat = Lt > 0.f ? (Mt + log2f(Lt)) * kLn2 : -INFINITY;
+        const float gate = sink_gate(prm.epi, hq, lse_nat);
+        const bool on = prm.epi.sinks != nullptr;
         T* dst = out + ((size_t)b * Hq + hq) * D + d4;
-        dst[0] = ElemTraits<T>::from_float(o.x * inv); dst[1] = ElemTraits<T>::from_float(o.y * inv);
-        dst[2] = ElemTraits<T>::from_float(o.z * inv); dst[3] = ElemTraits<T>::from_float(o.w * inv);
-        if (d4 == 0) prm.lse[(size_t)b * Hq + hq] = Lt > 0.f ? (Mt + log2f(Lt)) * kLn2 : -INFINITY;
+        dst[0] = gated_out<T>(o.x * inv, gate, on); dst[1] = gated_out<T>(o.y * inv, gate, on);
+        dst[2] = gated_out<T>(o.z * inv, gate, on); dst[3] = gated_out<T>(o.w * inv, gate, on);
+        if (d4 == 0) prm.lse[(size_t)b * Hq + hq] = lse_nat;
     }
 #ifdef FPKV_PROFILE
     if (threadIdx.x == 0) g_fin_times[blockIdx.x % 1024][2] = gtime();
@@ -840,7 +846,7 @@ size_t decode_tma_workspace_bytes(int Hq, int Hkv, int D)
 int launch_decode_tma(const PoolView& pv, int layer, void* out, float* lse, const void* q,
                       long long q_stride_b, long long q_stride_h, const int64_t* batch_idx,
                       const void* pos, int pos_type, int B, int Hq, float sm_scale,
-                      void* workspace, int32_t* status, cudaStream_t stream, bool after_append)
+                      void* workspace, const Epilogue& epi, int32_t* status, cudaStream_t stream, bool after_append)
 {
     if (B == 0) return FPKV_OK;
     const int nrep = Hq / pv.H;
@@ -876,6 +882,7 @@ int launch_decode_tma(const PoolView& pv, int layer, void* out, float* lse, cons
         prm.after_append = (after_append && b0 == 0) ? 1 : 0;
         prm.rows_per_plane = pv.n_pages * pv.P;
         prm.scale_log2 = sm_scale * kLog2e;
+        prm.epi = epi;
         int rc;
         if (pv.dtype == FPKV_BF16)
             rc = pos_type == FPKV_I32 ? launch_shape<__nv_bfloat16, int32_t>(pv.D, nrep, map, prm, G, stream)

@@ -206,6 +206,7 @@ struct PrefillParams {
     float scale_log2;
     int is_bf16;
     int heads_per_cta;          // 2: both query heads of a GQA pair share the staged K/V tiles; 1 otherwise
+    Epilogue epi;
 };
 
 template <typename T>
@@ -482,11 +483,14 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_consta
         }
         if (alive) {
             const float inv = l > 0.f ? 1.f / l : 0.f;
+            const float lse_nat = l > 0.f ? (m_ref + log2f(l)) * kLn2 : -INFINITY;
+            const bool gate_on = prm.epi.sinks != nullptr;
+            const float gate = sink_gate(prm.epi, hq, lse_nat);
 #pragma unroll 1
             for (int c4 = 0; c4 < 4; ++c4) {
                 if (n_tiles > 0) tmem_ld32(to + c4 * 32, v);
                 if (tok < prm.L) {
-                    T* dst = out + ((size_t)hq * prm.L + tok) * kHeadDim + c4 * 32;
+                    T* dst = out + (prm.epi.token_major ? ((size_t)tok * prm.Hq + hq) : ((size_t)hq * prm.L + tok)) * kHeadDim + c4 * 32;
 #pragma unroll
                     for (int c = 0; c < 32; c += 8) {
                         uint32_t w[4];
@@ -494,14 +498,14 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_consta
                         for (int e = 0; e < 4; ++e) {
                             const float a = (n_tiles > 0 && l > 0.f) ? __uint_as_float(v[c + 2 * e]) * inv : 0.f;
                             const float b = (n_tiles > 0 && l > 0.f) ? __uint_as_float(v[c + 2 * e + 1]) * inv : 0.f;
-                            if (prm.is_bf16) { __nv_bfloat162 x = __floats2bfloat162_rn(a, b); w[e] = *reinterpret_cast<uint32_t*>(&x); }
-                            else { __half2 x = __floats2half2_rn(a, b); w[e] = *reinterpret_cast<uint32_t*>(&x); }
+                            const T ra = gated_out<T>(a, gate, gate_on), rb = gated_out<T>(b, gate, gate_on);
+                            w[e] = (uint32_t)*reinterpret_cast<const uint16_t*>(&ra) | ((uint32_t)*reinterpret_cast<const uint16_t*>(&rb) << 16);
                         }
                         *reinterpret_cast<uint4*>(dst + c) = make_uint4(w[0], w[1], w[2], w[3]);
                     }
                 }
             }
-            if (tok < prm.L) prm.lse[(size_t)hq * prm.L + tok] = l > 0.f ? (m_ref + log2f(l)) * kLn2 : -INFINITY;
+            if (tok < prm.L) prm.lse[(size_t)hq * prm.L + tok] = lse_nat;
         }
     }
     if (!alive && lane == 0) {
@@ -558,7 +562,7 @@ bool prefill_tc_supported(const PoolView& pv, int Hq)
 
 int launch_prefill_tc(const PoolView& pv, int layer, void* out, float* lse, const void* q, long long q_stride_h,
                       long long q_stride_t, const int64_t* batch_idx, const int32_t* extent, int L, int Hq,
-                      float sm_scale, int32_t* status, cudaStream_t stream)
+                      float sm_scale, const Epilogue& epi, int32_t* status, cudaStream_t stream)
 {
     if (L == 0) return FPKV_OK;
     const CUtensorMapDataType dt = pv.dtype == FPKV_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
@@ -591,6 +595,7 @@ int launch_prefill_tc(const PoolView& pv, int layer, void* out, float* lse, cons
     prm.scale_log2 = sm_scale * kLog2e;
     prm.is_bf16 = pv.dtype == FPKV_BF16;
     prm.heads_per_cta = ((Hq / pv.H) % 2 == 0) ? 2 : 1;
+    prm.epi = epi;
     dim3 grid((L + kTileM - 1) / kTileM, Hq / prm.heads_per_cta);
     if (pv.dtype == FPKV_BF16) {
         auto kern = prefill_tc_kernel<__nv_bfloat16>;

@@ -35,6 +35,11 @@ class FpkvPool(ctypes.Structure):
                 ("dtype", ctypes.c_int32), ("reserved_", ctypes.c_int32)]
 
 
+class FpkvEpilogue(ctypes.Structure):
+    """struct fpkv_epilogue"""
+    _fields_ = [("sinks", ctypes.c_void_p), ("sinks_dtype", ctypes.c_int32), ("token_major", ctypes.c_int32)]
+
+
 class FpkvError(RuntimeError):
     def __init__(self, code, where):
         self.code = code
@@ -62,10 +67,11 @@ def _load():
     lib.fpkv_decode_workspace_bytes.restype = ctypes.c_int
     lib.fpkv_decode_workspace_bytes.argtypes = [pool, i32, i32, ctypes.POINTER(ctypes.c_size_t)]
     lib.fpkv_decode_attn.restype = ctypes.c_int
+    epi = ctypes.POINTER(FpkvEpilogue)
     lib.fpkv_decode_attn.argtypes = [pool, i32, vp, vp, vp, i64, i64, vp, vp, i32, i32, i32, f32, vp,
-                                     ctypes.c_size_t, i32, vp, vp]
+                                     ctypes.c_size_t, i32, epi, vp, vp]
     lib.fpkv_prefill_attn.restype = ctypes.c_int
-    lib.fpkv_prefill_attn.argtypes = [pool, i32, vp, vp, vp, i64, i64, vp, vp, i32, i32, f32, i32, vp, vp]
+    lib.fpkv_prefill_attn.argtypes = [pool, i32, vp, vp, vp, i64, i64, vp, vp, i32, i32, f32, i32, epi, vp, vp]
     lib.fpkv_decode_attn_static.restype = ctypes.c_int
     lib.fpkv_decode_attn_static.argtypes = [pool, i32, vp, vp, vp, i64, i64, vp, vp, i32, i32, i32, f32, vp, vp]
     return lib

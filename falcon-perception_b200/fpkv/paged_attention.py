@@ -47,6 +47,17 @@ def _pos_type(t: Tensor) -> int:
     raise AssertionError("input_pos must be int32 or int64")
 
 
+def _epilogue(sinks: Tensor | None, token_major: bool = False):
+    """fpkv_epilogue for a call, or None: the sink gate of the reference's
+    ``_post_attention`` (``model.py:122-128``) and the token-major prefill layout."""
+    if sinks is None and not token_major:
+        return None
+    if sinks is not None:
+        assert sinks.is_cuda and sinks.is_contiguous() and sinks.dtype in _DTYPES
+    return _lib.FpkvEpilogue(sinks.data_ptr() if sinks is not None else None,
+                             _DTYPES[sinks.dtype] if sinks is not None else 0, int(token_major))
+
+
 def _stream(device) -> int:
     return torch.cuda.current_stream(device).cuda_stream
 
@@ -257,20 +268,25 @@ class PagedKVCache(KVCacheBase):
         return self._workspace
 
     def decode_step(self, layer_id: int, q: Tensor, k: Tensor, v: Tensor, batch_idx: Tensor, input_pos: Tensor,
-                    sm_scale: float | None = None, out: Tensor | None = None, lse: Tensor | None = None):
+                    sm_scale: float | None = None, out: Tensor | None = None, lse: Tensor | None = None,
+                    sinks: Tensor | None = None):
         """Append k, v (B,H,1,D) and attend with q (B,Hq,1,D) in one go: what
         ``Attention.forward`` does per layer in a decode step (``insert_kv``
         followed by the attention call, ``falcon_perception/model.py:150-162``).
         Same results as the two separate calls; because the attention kernel
         knows that the append is what runs right before it, its set-up overlaps
-        the append instead of waiting for it."""
+        the append instead of waiting for it.  With ``sinks`` (n_q_heads,) the
+        returned out is already ``out * sigmoid(lse - sinks)``, the gate of
+        ``_post_attention`` (``model.py:122-128``); viewed as (B, 1, Hq*D) it is
+        what the output projection takes."""
         B = q.shape[0]
         self.assign(layer_id, batch_idx, input_pos.reshape(B, 1), k, v)
-        return self.decode_attention(layer_id, q, batch_idx, input_pos, sm_scale, out, lse, _after_append=True)
+        return self.decode_attention(layer_id, q, batch_idx, input_pos, sm_scale, out, lse, sinks=sinks,
+                                     _after_append=True)
 
     def decode_attention(self, layer_id: int, q: Tensor, batch_idx: Tensor, input_pos: Tensor,
                          sm_scale: float | None = None, out: Tensor | None = None, lse: Tensor | None = None,
-                         _after_append: bool = False):
+                         sinks: Tensor | None = None, _after_append: bool = False):
         """One query token per row against keys 0..input_pos[b] of slot
         batch_idx[b].  q (B,Hq,1,D) -> out (B,Hq,1,D) in q's dtype, lse (B,Hq,1)
         fp32.  Call after ``insert_kv`` of the same step, as the model does."""
@@ -297,20 +313,25 @@ class PagedKVCache(KVCacheBase):
         ws = self._get_workspace(B, Hq)
         scale = (1.0 / math.sqrt(D)) if sm_scale is None else float(sm_scale)
         flags = int(self.decode_kernel) | (_lib.DECODE_AFTER_APPEND if _after_append else 0)
+        epi = _epilogue(sinks)
         _lib.check(_lib.lib.fpkv_decode_attn(
             ctypes.byref(self._pool), layer_id, out.data_ptr(), lse.data_ptr(), q.data_ptr(), q.stride(0),
             q.stride(1), batch_idx.data_ptr(), input_pos.data_ptr(), _pos_type(input_pos), B, Hq, scale,
-            ws.data_ptr(), ws.numel(), flags, self._status_ptr(), _stream(self._dev)),
+            ws.data_ptr(), ws.numel(), flags, ctypes.byref(epi) if epi is not None else None, self._status_ptr(),
+            _stream(self._dev)),
             "fpkv_decode_attn")
         return out, lse
 
     def prefill_attention(self, layer_id: int, q: Tensor, batch_idx: Tensor, input_pos: Tensor, mask: PrefillMask,
-                          sm_scale: float | None = None):
+                          sm_scale: float | None = None, sinks: Tensor | None = None, token_major: bool = False):
         """Attention of a packed prefill row (or of a chunk of one) against the
         pages: q (1,Hq,L,D), batch_idx / input_pos (1,L) as given to
         ``insert_kv``, ``mask`` from ``create_prefill_blockmask``.  Call it
         after ``insert_kv`` of the same tokens.  Returns out (1,Hq,L,D) in q's
-        dtype and lse (1,Hq,L) fp32; pad rows give 0 / -inf."""
+        dtype and lse (1,Hq,L) fp32; pad rows give 0 / -inf.  ``sinks``
+        (n_q_heads,) applies the gate of ``_post_attention`` to out;
+        ``token_major`` returns out as (1,L,Hq,D), i.e. (1,L,Hq*D) for the
+        output projection, without the reference's permute + copy."""
         _, Hq, L, D = q.shape
         assert q.shape[0] == 1 and D == self.head_dim and Hq % self.n_heads == 0 and q.dtype == self.dtype
         assert batch_idx.shape[-1] == L and input_pos.shape[-1] == L and mask.L == L
@@ -321,13 +342,14 @@ class PagedKVCache(KVCacheBase):
         bi = bi if bi.is_contiguous() else bi.contiguous()
         ext = mask.extent(input_pos)
         q = self._rows16(q)
-        out = torch.empty((1, Hq, L, D), dtype=q.dtype, device=q.device)
+        out = torch.empty((1, L, Hq, D) if token_major else (1, Hq, L, D), dtype=q.dtype, device=q.device)
         lse = torch.empty((1, Hq, L), dtype=torch.float32, device=q.device)
         scale = (1.0 / math.sqrt(D)) if sm_scale is None else float(sm_scale)
+        epi = _epilogue(sinks, token_major)
         _lib.check(_lib.lib.fpkv_prefill_attn(
             ctypes.byref(self._pool), layer_id, out.data_ptr(), lse.data_ptr(), q.data_ptr(), q.stride(1),
-            q.stride(2), bi.data_ptr(), ext.data_ptr(), L, Hq, scale, int(self.prefill_kernel), self._status_ptr(),
-            _stream(self._dev)),
+            q.stride(2), bi.data_ptr(), ext.data_ptr(), L, Hq, scale, int(self.prefill_kernel),
+            ctypes.byref(epi) if epi is not None else None, self._status_ptr(), _stream(self._dev)),
             "fpkv_prefill_attn")
         return out, lse
 

@@ -81,6 +81,24 @@ typedef struct fpkv_pool {
     int32_t reserved_;
 } fpkv_pool;
 
+/*
+ * Optional epilogue of the attention entry points (pass NULL for none): what
+ * the reference does right after attention in Attention._post_attention
+ * (falcon_perception/model.py:122-128), folded into the kernels' output stage.
+ *   sinks        device (n_q_heads) of `sinks_dtype`, or NULL.  When given,
+ *                out is written as round(round(out) * sigmoid(lse - sinks[h])),
+ *                the reference's two-step value; lse is returned ungated.
+ *   token_major  prefill only: write out as (1, L, n_q_heads, head_dim), the
+ *                layout the output projection reads after the reference's
+ *                permute(0, 2, 1, 3).flatten(2), instead of (1, n_q_heads, L,
+ *                head_dim).  (For decode the two layouts are the same memory.)
+ */
+typedef struct fpkv_epilogue {
+    const void* sinks;
+    int32_t sinks_dtype;        /* fpkv_dtype */
+    int32_t token_major;
+} fpkv_epilogue;
+
 /* Library version (major*10000 + minor*100 + patch). */
 FPKV_API int fpkv_version(void);
 
@@ -177,7 +195,7 @@ FPKV_API int fpkv_decode_attn(const fpkv_pool* pool, int32_t layer,
                      const int64_t* batch_idx, const void* input_pos, int32_t pos_type,
                      int32_t B, int32_t n_q_heads, float sm_scale,
                      void* workspace, size_t workspace_bytes, int32_t flags,
-                     int32_t* status, void* stream);
+                     const fpkv_epilogue* epilogue, int32_t* status, void* stream);
 
 /*
  * Paged prefill / chunked-prefill attention over a packed row of L query
@@ -217,7 +235,7 @@ FPKV_API int fpkv_prefill_attn(const fpkv_pool* pool, int32_t layer,
                                const void* q, int64_t q_stride_h, int64_t q_stride_t,
                                const int64_t* batch_idx, const int32_t* extent,
                                int32_t L, int32_t n_q_heads, float sm_scale, int32_t flags,
-                               int32_t* status, void* stream);
+                               const fpkv_epilogue* epilogue, int32_t* status, void* stream);
 
 /*
  * fpkv_decode_attn without the workspace argument, for callers that cannot

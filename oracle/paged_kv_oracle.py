@@ -18,6 +18,7 @@ What it restates (paths are relative to the reference project root):
                                 falcon_perception/model.py:150-162
 * prefill mask                  falcon_perception/attention.py:75-96
                                 falcon_perception/paged_attention.py:343-362
+* sink gate after attention     falcon_perception/model.py:122-128
 
 The attention arithmetic itself lives in a third-party dependency of the
 reference, torch 2.11.0 FlexAttention (torch/nn/attention/flex_attention.py),
@@ -268,3 +269,15 @@ def paged_prefill_attention(cache: OraclePagedKVCache, layer, q, slot, q_pos,
     allowed = (same_img | (u[None, :] <= qp[:, None])) & valid[None, :]
     o, l = _masked_attention(q.float(), K, V, torch.from_numpy(allowed), scale)
     return o.to(q.dtype), l
+
+
+def post_attention_gate(out, lse, sinks):
+    """The sink gate and layout change right after attention
+    (falcon_perception/model.py:122-128): out (B,Hq,S,D) in the model dtype,
+    lse (B,Hq,S) fp32, sinks (Hq,).  scale = sigmoid(lse - sinks[h]); the
+    product is formed in fp32 from the rounded output and rounded back to the
+    output dtype; the result is laid out (B, S, Hq*D) for the output
+    projection.  (The projection itself is a library GEMM and not restated.)"""
+    scale = torch.sigmoid(lse - sinks.float().view(1, -1, 1))
+    gated = (out.float() * scale.unsqueeze(-1)).to(out.dtype)
+    return gated.permute(0, 2, 1, 3).contiguous().flatten(2)

@@ -295,8 +295,28 @@ def prefill_goldens():
         print(name, "L", case.L, "oracle-vs-reference err", g["oracle_err"])
 
 
+# --------------------------------------------------------------------------
+# 4. the sink gate after attention (Attention._post_attention, model.py:122-128)
+# --------------------------------------------------------------------------
+def post_attention_golden():
+    from falcon_perception.model import Attention
+    rng = np.random.default_rng(4101)
+    B, Hq, S, D = 3, 8, 5, 64
+    out = torch.from_numpy(rng.standard_normal((B, Hq, S, D), dtype=np.float32)).bfloat16()
+    lse = torch.from_numpy(rng.standard_normal((B, Hq, S), dtype=np.float32) * 3)
+    lse[0, 1, 2] = float("-inf")                      # a row that saw no key
+    sinks = torch.from_numpy(rng.standard_normal(Hq, dtype=np.float32)).bfloat16()
+    fake = types.SimpleNamespace(sinks=sinks, wo=lambda x: x)       # identity projection: the gate and layout only
+    ref = Attention._post_attention(fake, out, lse)
+    mine = orc.post_attention_gate(out, lse, sinks)
+    assert torch.equal(ref, mine)
+    np.savez_compressed(os.path.join(OUT, "post_attention.npz"), gated=ref.float().numpy())
+    print("post_attention: oracle equals reference bit for bit,", tuple(ref.shape))
+
+
 if __name__ == "__main__":
     torch.manual_seed(0)
+    post_attention_golden()
     allocator_traces()
     decode_goldens()
     prefill_goldens()

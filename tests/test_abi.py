@@ -66,7 +66,7 @@ def test_validation_happens_before_any_launch():
     assert L.fpkv_decode_workspace_bytes(ctypes.byref(p), 4, 4, ctypes.byref(need)) == 0 and need.value > 0
     # decode: workspace too small is caught on the host
     assert L.fpkv_decode_attn(ctypes.byref(p), 0, ptr, ptr, ptr, 256, 64, ptr, ptr, 0, 2, 4, 0.125, ptr, 16, 0,
-                              None, None) == -6
+                              None, None, None) == -6
     if not torch.cuda.is_available():
         # valid arguments but no device: refused, never a silent CPU path
         assert call(p) == -4

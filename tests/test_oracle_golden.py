@@ -142,3 +142,15 @@ def test_prefill_matches_reference(name):
                                              img[off:off + L])
         assert np.abs(po.numpy() - g["out"][0][:, off + c0:off + c1]).max() < 2e-5
         assert np.abs(pl.numpy() - g["lse"][0][:, off + c0:off + c1]).max() < 2e-5
+
+
+def test_sink_gate_matches_reference():
+    """Attention._post_attention with an identity projection, recorded from the reference."""
+    rng = np.random.default_rng(4101)
+    B, Hq, S, D = 3, 8, 5, 64
+    out = torch.from_numpy(rng.standard_normal((B, Hq, S, D), dtype=np.float32)).bfloat16()
+    lse = torch.from_numpy(rng.standard_normal((B, Hq, S), dtype=np.float32) * 3)
+    lse[0, 1, 2] = float("-inf")
+    sinks = torch.from_numpy(rng.standard_normal(Hq, dtype=np.float32)).bfloat16()
+    got = orc.post_attention_gate(out, lse, sinks)
+    assert np.array_equal(got.float().numpy(), golden("post_attention")["gated"])
