@@ -185,6 +185,21 @@ int fpkv_decode_attn(const fpkv_pool* pool, int32_t layer, void* out, float* lse
                                             static_cast<char*>(workspace) + kCounterBytes, epi, status, s);
 }
 
+int fpkv_table_update(const fpkv_pool* pool, const int32_t* ops, int32_t n_ops, int32_t* status, void* stream)
+{
+    // only the tables matter here: any page size or head_dim is fine
+    if (pool == nullptr || pool->page_table == nullptr || pool->physical_to_logical == nullptr) return FPKV_EINVAL;
+    if (pool->n_pages <= 0 || pool->max_batch_size <= 0 || n_ops < 0) return FPKV_EINVAL;
+    if (n_ops == 0) return FPKV_OK;
+    if (ops == nullptr) return FPKV_EINVAL;
+    if (!aligned16(ops)) return FPKV_EALIGN;
+    const int rc = check_arch();
+    if (rc) return rc;
+    return launch_table_update(const_cast<int64_t*>(pool->page_table), const_cast<int64_t*>(pool->physical_to_logical),
+                               pool->n_pages, pool->max_batch_size, ops, n_ops, status,
+                               static_cast<cudaStream_t>(stream));
+}
+
 int fpkv_prefill_attn(const fpkv_pool* pool, int32_t layer, void* out, float* lse, const void* q,
                       int64_t q_stride_h, int64_t q_stride_t, const int64_t* batch_idx, const int32_t* extent,
                       int32_t L, int32_t n_q_heads, float sm_scale, int32_t flags, const fpkv_epilogue* epilogue,

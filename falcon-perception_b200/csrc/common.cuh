@@ -97,6 +97,8 @@ int launch_decode_tma(const PoolView& pv, int layer, void* out, float* lse, cons
 int launch_prefill_portable(const PoolView& pv, int layer, void* out, float* lse, const void* q, long long q_stride_h,
                             long long q_stride_t, const int64_t* batch_idx, const int32_t* extent, int L, int Hq,
                             float sm_scale, const Epilogue& epi, int32_t* status, cudaStream_t stream);
+int launch_table_update(int64_t* page_table, int64_t* p2l, int n_pages, int max_batch, const int32_t* ops,
+                        int n_ops, int32_t* status, cudaStream_t stream);
 bool prefill_tc_supported(const PoolView& pv, int Hq);
 int launch_prefill_tc(const PoolView& pv, int layer, void* out, float* lse, const void* q, long long q_stride_h,
                       long long q_stride_t, const int64_t* batch_idx, const int32_t* extent, int L, int Hq,

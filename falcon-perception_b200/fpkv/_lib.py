@@ -23,7 +23,7 @@ STATUS_BAD_SLOT, STATUS_BAD_POS, STATUS_BAD_PAGE, STATUS_TIMEOUT = 1, 2, 4, 8
 
 # every symbol include/fpkv.h declares
 EXPORTS = ("fpkv_version", "fpkv_strerror", "fpkv_append_decode", "fpkv_append_packed", "fpkv_gather",
-           "fpkv_decode_workspace_bytes", "fpkv_decode_attn", "fpkv_decode_attn_static", "fpkv_prefill_attn")
+           "fpkv_decode_workspace_bytes", "fpkv_decode_attn", "fpkv_decode_attn_static", "fpkv_prefill_attn", "fpkv_table_update")
 
 
 class FpkvPool(ctypes.Structure):
@@ -70,6 +70,8 @@ def _load():
     epi = ctypes.POINTER(FpkvEpilogue)
     lib.fpkv_decode_attn.argtypes = [pool, i32, vp, vp, vp, i64, i64, vp, vp, i32, i32, i32, f32, vp,
                                      ctypes.c_size_t, i32, epi, vp, vp]
+    lib.fpkv_table_update.restype = ctypes.c_int
+    lib.fpkv_table_update.argtypes = [pool, vp, i32, vp, vp]
     lib.fpkv_prefill_attn.restype = ctypes.c_int
     lib.fpkv_prefill_attn.argtypes = [pool, i32, vp, vp, vp, i64, i64, vp, vp, i32, i32, f32, i32, epi, vp, vp]
     lib.fpkv_decode_attn_static.restype = ctypes.c_int

@@ -79,33 +79,80 @@ class PagedKVCache(KVCacheBase):
         self._dev = torch.device(device)
 
         # [slot, logical page] -> physical page; page 0 and slot 0 are reserved (no-op targets)
-        self.page_table = torch.full((max_batch_size, n_pages), -1, dtype=torch.int64, device=device)
-        self.page_table[0, :] = 0
+        self._page_table = torch.full((max_batch_size, n_pages), -1, dtype=torch.int64, device=device)
+        self._page_table[0, :] = 0
         self.page_table_cpu = [[] for _ in range(max_batch_size)]
         self.capacity = [0 for _ in range(max_batch_size)]
         self.free_pages = list(reversed(range(1, n_pages)))
         self.free_batch_idx = list(reversed(range(1, max_batch_size)))
         # [slot, physical page] -> logical page
-        self.physical_to_logical = torch.full((max_batch_size, n_pages), -1, dtype=torch.int64, device=device)
+        self._physical_to_logical = torch.full((max_batch_size, n_pages), -1, dtype=torch.int64, device=device)
+        # On a CUDA cache the table edits of allocate / reserve / erase are queued here and applied by one
+        # kernel launch before the tables are next used (by a kernel of this class or through the attributes).
+        self._pending = []
 
         self.kv_shape = (num_layers, 2, 1, n_heads, n_pages * page_size, head_dim)
         self.kv_cache = torch.zeros(self.kv_shape, dtype=dtype, device=device)
 
-        self._pool = _lib.FpkvPool(self.kv_cache.data_ptr(), self.page_table.data_ptr(),
-                                   self.physical_to_logical.data_ptr(), num_layers, n_heads, n_pages,
+        self._pool = _lib.FpkvPool(self.kv_cache.data_ptr(), self._page_table.data_ptr(),
+                                   self._physical_to_logical.data_ptr(), num_layers, n_heads, n_pages,
                                    page_size, head_dim, max_batch_size, _DTYPES[dtype], 0)
         self._status = torch.zeros(1, dtype=torch.int32, device=device)
         self._workspace = None
         self.decode_kernel = _lib.DECODE_AUTO       # DECODE_PORTABLE / DECODE_TMA force one kernel
         self.prefill_kernel = _lib.PREFILL_AUTO     # PREFILL_PORTABLE / PREFILL_TC force one kernel
 
+    # ------------------------------------------------------------------ tables
+    @property
+    def page_table(self) -> Tensor:
+        """int64 (max_batch_size, n_pages): [slot, logical page] -> physical page."""
+        self._flush_tables()
+        return self._page_table
+
+    @property
+    def physical_to_logical(self) -> Tensor:
+        """int64 (max_batch_size, n_pages): [slot, physical page] -> logical page."""
+        self._flush_tables()
+        return self._physical_to_logical
+
+    def _edit_tables(self, ops):
+        """ops: list of (kind, slot, a, b); kind 0 clears the slot's rows, kind 1 maps logical page a to
+        physical page b.  A CPU cache (bookkeeping only) applies them at once; a CUDA cache queues them."""
+        if self._dev.type == "cuda":
+            self._pending.extend(ops)
+            return
+        for kind, slot, a, b in ops:
+            if kind == 0:
+                self._page_table[slot, :] = -1
+                self._physical_to_logical[slot, :] = -1
+            else:
+                self._page_table[slot, a] = b
+                self._physical_to_logical[slot, b] = a
+
+    def flush_tables(self):
+        """Apply the queued table edits now (one pinned upload, one kernel launch).  Every data-path
+        method and the table attributes do this on their own; call it yourself before a region that must
+        not allocate (CUDA-graph capture, ``decode_attention_noalloc``)."""
+        self._flush_tables()
+
+    def _flush_tables(self):
+        if not self._pending:
+            return
+        ops = torch.tensor(self._pending, dtype=torch.int32).pin_memory().to(self._dev, non_blocking=True)
+        n = len(self._pending)
+        self._pending = []
+        _lib.check(_lib.lib.fpkv_table_update(ctypes.byref(self._pool), ops.data_ptr(), n, self._status_ptr(),
+                                              _stream(self._dev)), "fpkv_table_update")
+
     # ------------------------------------------------------------------ helpers
-    def _require_cuda(self, *tensors):
+    def _require_cuda(self, *tensors, flush: bool = True):
         if self._dev.type != "cuda":
             raise RuntimeError("fpkv moves K/V only with its CUDA kernels; this cache lives on "
                                f"{self._dev} and has no CPU path")
         for t in tensors:
             assert t.is_cuda, "tensor must be on the cache's CUDA device"
+        if flush:
+            self._flush_tables()
 
     def _status_ptr(self):
         return self._status.data_ptr()
@@ -142,8 +189,7 @@ class PagedKVCache(KVCacheBase):
     def allocate(self) -> int:
         slot = self.free_batch_idx.pop()
         self.capacity[slot] = 0
-        self.physical_to_logical[slot, :] = -1
-        self.page_table[slot, :] = -1
+        self._edit_tables([(0, slot, 0, 0)])
         return slot
 
     @property
@@ -168,11 +214,7 @@ class PagedKVCache(KVCacheBase):
         start = self.capacity[batch_idx_int] // self.page_size
         end = start + n_new
         pages = self.free_pages[-n_new:]
-        pages_t = torch.tensor(pages, dtype=torch.int64)
-        if self._dev.type == "cuda":
-            pages_t = pages_t.pin_memory().to(self._dev, non_blocking=True)
-        self.page_table[batch_idx_int, start:end] = pages_t
-        self.physical_to_logical[batch_idx_int, pages_t] = torch.arange(start, end, device=self.device)
+        self._edit_tables([(1, batch_idx_int, start + i, pg) for i, pg in enumerate(pages)])
         self.page_table_cpu[batch_idx_int] += pages
         self.free_pages = self.free_pages[:-n_new]
         self.capacity[batch_idx_int] += n_new * self.page_size
@@ -183,8 +225,7 @@ class PagedKVCache(KVCacheBase):
         self.free_pages.extend(reversed(self.page_table_cpu[batch_idx]))
         self.page_table_cpu[batch_idx] = []
         # cleared on the device too, so padding rows and stale slots read "unmapped"
-        self.page_table[batch_idx, :] = -1
-        self.physical_to_logical[batch_idx, :] = -1
+        self._edit_tables([(0, batch_idx, 0, 0)])
         self.capacity[batch_idx] = 0
 
     # ------------------------------------------------------------------- append
@@ -372,7 +413,8 @@ class PagedKVCache(KVCacheBase):
         assert input_pos.shape == (B,) and input_pos.is_contiguous()
         assert tuple(out.shape) == (B, Hq, 1, D) and out.is_contiguous() and out.dtype == q.dtype
         assert tuple(lse.shape) == (B, Hq, 1) and lse.is_contiguous() and lse.dtype == torch.float32
-        self._require_cuda(q, batch_idx, input_pos, out, lse)
+        self._require_cuda(q, batch_idx, input_pos, out, lse, flush=False)
+        assert not self._pending, "page-table edits are pending: call flush_tables() before the no-allocation region"
         scale = (1.0 / math.sqrt(D)) if sm_scale is None else float(sm_scale)
         _lib.check(_lib.lib.fpkv_decode_attn_static(
             ctypes.byref(self._pool), layer_id, out.data_ptr(), lse.data_ptr(), q.data_ptr(), q.stride(0),

@@ -106,6 +106,22 @@ FPKV_API int fpkv_version(void);
 FPKV_API const char* fpkv_strerror(int code);
 
 /*
+ * Apply a batch of page-table edits on the device, in order, with one launch.
+ * Replaces the per-call device updates of PagedKVCache.allocate, reserve and
+ * erase (paged_attention.py:102-109, 145-158, 166-182), which issue a few
+ * tensor operations and one host-to-device tensor each; the free lists and
+ * capacities stay on the host as there.  This entry point WRITES
+ * pool->page_table and pool->physical_to_logical.
+ * ops: device int32 [n_ops][4], 16-byte aligned, each {kind, slot, a, b}:
+ *   kind 0  clear both table rows of `slot` to -1              (allocate, erase)
+ *   kind 1  page_table[slot, a] = b; physical_to_logical[slot, b] = a   (reserve)
+ * Slot 0 and page 0 are reserved and never edited; edits naming them or ids
+ * out of range are skipped and raise FPKV_STATUS_BAD_SLOT / _BAD_PAGE.
+ */
+FPKV_API int fpkv_table_update(const fpkv_pool* pool, const int32_t* ops, int32_t n_ops,
+                               int32_t* status, void* stream);
+
+/*
  * Decode append: one new K/V row per sequence, written through the page
  * table.  Replaces PagedKVCache.assign (paged_attention.py:184-232):
  *   page = max(page_table[batch_idx[b], input_pos[b] / page_size], 0)

@@ -124,3 +124,32 @@ def test_logical_index_helpers():
     assert ok.tolist() == [True, True, True, False] and logical.tolist()[:3] == [1, 4, 11]
     mod = c.get_mask_mod(lambda b, h, q, kv: kv <= 4, bidx)
     assert mod(torch.zeros(4, dtype=torch.int64), 0, 0, phys).tolist() == [True, True, False, False]
+
+
+@pytest.mark.gpu
+def test_table_edits_are_batched_and_ordered():
+    """allocate / reserve / erase on a CUDA cache queue their table edits; one launch applies a whole batch in
+    order (clear, map, clear again, map again on the same slot) and bad ids are reported, not written."""
+    import ctypes
+    from fpkv import _lib
+    c = PagedKVCache(16, 8, 4, 1, 64, 1, torch.float32, "cuda")
+    a = c.allocate(); c.reserve(a, None, 20)
+    pages_a = list(c.page_table_cpu[a])
+    c.erase(a)
+    b = c.allocate(); assert b == a
+    c.reserve(b, None, 9)
+    assert len(c._pending) == 2 + 3 + 1 + 2                 # nothing has touched the device yet
+    pt = c.page_table                                       # flushes
+    assert not c._pending
+    assert pt[b, :2].tolist() == c.page_table_cpu[b] and (pt[b, 2:] == -1).all()
+    p2l = c.physical_to_logical[b]
+    assert sorted((p2l >= 0).nonzero().view(-1).tolist()) == sorted(c.page_table_cpu[b])
+    assert (pt[0] == 0).all()                               # slot 0 is never edited
+    # edits naming slot 0, page 0 or ids out of range are skipped and flagged
+    bad = torch.tensor([[1, 0, 0, 3], [1, 2, 1, 0], [1, 2, 99, 3], [0, 7, 0, 0]], dtype=torch.int32, device="cuda")
+    before = c._page_table.clone()
+    assert _lib.lib.fpkv_table_update(ctypes.byref(c._pool), bad.data_ptr(), 4, c._status.data_ptr(), None) == 0
+    torch.cuda.synchronize()
+    assert torch.equal(before, c._page_table)
+    with pytest.raises(RuntimeError, match="bad slot, bad page id"):
+        c.check_status()

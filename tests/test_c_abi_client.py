@@ -29,7 +29,7 @@ int main(int argc, char** argv) {
     if (!h) { printf("dlopen failed: %s\n", dlerror()); return 1; }
     const char* names[] = {"fpkv_version", "fpkv_strerror", "fpkv_append_decode", "fpkv_append_packed", "fpkv_gather",
                            "fpkv_decode_workspace_bytes", "fpkv_decode_attn", "fpkv_prefill_attn",
-                           "fpkv_decode_attn_static"};
+                           "fpkv_decode_attn_static", "fpkv_table_update"};
     for (unsigned i = 0; i < sizeof(names) / sizeof(names[0]); ++i)
         if (!dlsym(h, names[i])) { printf("missing %s\n", names[i]); return 2; }
     version_fn version = (version_fn)dlsym(h, "fpkv_version");
