@@ -10,7 +10,7 @@
 //    (row b, stored head h, logical page).
 //  * SMs do not all pull the same bandwidth, so equal static shares leave the
 //    fast ones idle at the end (measured: exits spread over 150..190 us).  The
-//    flat tile range is therefore cut into "units" of decreasing size (eight
+//    flat tile range is therefore cut into "units" of decreasing size (five
 //    phases, each covering half of what is left with gridDim.x units) and the
 //    persistent CTAs, one per SM, claim units in order from an atomic counter.
 //  * A unit can start and end in the middle of a (b, h) segment; such a piece
@@ -56,12 +56,12 @@ constexpr int kConsumerWarps = 8;
 constexpr int kIssueWarp = kConsumerWarps, kScoutWarp = kConsumerWarps + 1;
 constexpr int kThreads = (kConsumerWarps + 2) * 32;
 #ifndef FPKV_PHASES
-#define FPKV_PHASES 6
+#define FPKV_PHASES 5
 #endif
 constexpr int kPhases = FPKV_PHASES;           // unit sizes halve from phase to phase
 constexpr int kDescBlocks = 8;                 // resolved-tile blocks (32 tiles each) between scout and issue warp
 constexpr int kUnitQueue = 8;                  // claimed units in flight between scout and consumers
-constexpr int kClaimAhead = 4;                 // tiles before a unit's start at which the scout claims the unit after it
+constexpr int kClaimAhead = 3;                 // the scout claims the next unit when this few resolved tiles are unissued
 constexpr int kMaxGrid = 256;
 constexpr int kMaxBatchPerLaunch = 512;
 constexpr uint32_t kSpinLimit = 1u << 22;      // try_wait attempts before giving up
@@ -358,14 +358,14 @@ decode_tma_kernel(const __grid_constant__ CUtensorMap tmap, const Params prm)
                 ++blk;
             }
             if (!ok) break;
-            const int unit_start = resolved;           // position of this unit in the CTA's own tile stream
             resolved += r1 - r0;
-            // Claim the next unit only when the issue warp is about to begin this one: the CTA then
-            // holds the unit in progress plus one resolved unit, enough to hide the claim and the two
-            // dependent table reads, and no more.
+            // Claim the next unit as late as the lookups allow: when the issue warp has only a few resolved
+            // tiles left.  A CTA then never sits on work that a faster SM could take (measured: claiming one
+            // unit ahead cost 3 % through the tail), and three tiles of streaming cover the claim and the two
+            // dependent table reads.
             if (lane == 0) {
                 uint32_t spins = 0;
-                while (*issued + kClaimAhead < unit_start && !*abort_flag && ++spins < kSpinLimit) __nanosleep(100);
+                while (resolved - *issued > kClaimAhead && !*abort_flag && ++spins < kSpinLimit) __nanosleep(100);
                 ok = spins < kSpinLimit && !*abort_flag;
                 if (ok) u = G + atomicAdd(prm.counters, 1);
             }
