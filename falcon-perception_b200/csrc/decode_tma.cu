@@ -430,6 +430,9 @@ decode_tma_kernel(const __grid_constant__ CUtensorMap tmap, const Params prm)
 
     // ============================ consumer warps ============================
     // While the first tiles are in flight: tell the finish kernel which units hold each segment.
+    bool has_empty_units = false;                      // a phase shorter than the grid leaves some units without tiles
+#pragma unroll
+    for (int p = 0; p < kPhases; ++p) has_empty_units |= (pb[p + 1] - pb[p]) < G;
     for (int sgi = blockIdx.x + G * tid; sgi < B * Hkv; sgi += G * kConsumerWarps * 32) {
         const int b = sgi / Hkv, h = sgi - b * Hkv;
         const int npg = (cum[b + 1] - cum[b]) / Hkv;
@@ -438,7 +441,7 @@ decode_tma_kernel(const __grid_constant__ CUtensorMap tmap, const Params prm)
             const int seg0 = cum[b] + h * npg;
             info.x = unit_of(ub, NU, seg0);
             info.y = unit_of(ub, NU, seg0 + npg - 1);
-            info.z = ((seg0 <= ub[info.x]) ? 0 : 1) | ((cum[B] < 2 * NU) ? 2 : 0);
+            info.z = ((seg0 <= ub[info.x]) ? 0 : 1) | (has_empty_units ? 2 : 0);
         }
         __stcg(prm.seginfo + sgi, info);
     }

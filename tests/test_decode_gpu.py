@@ -200,3 +200,40 @@ def test_decode_step_equals_separate_calls():
         ref_out, ref_lse = orc.decode_attention(o, 0, qn.float(), obidx, p.cpu())
         assert_attention_close(out_b, lse_b, ref_out, ref_lse, f"step {step}")
     ca.check_status(); cb.check_status()
+
+
+def test_batch_larger_than_one_launch():
+    """More rows than one launch of the TMA kernel takes (512): the call is split into launches that share the
+    workspace; short contexts, so that the oracle stays quick."""
+    case = wl.make_decode_case(909, B=700, Hq=16, Hkv=8, D=128, P=128, n_pages=1500, max_batch_size=702,
+                               len_lo=1, len_hi=200, dtype=torch.bfloat16)
+    c, slots, bidx, pos, k, v, q = product_from_case(case)
+    o, _, obidx, opos, ok, ov, oq = oracle_from_case(case)
+    ref_out, ref_lse = orc.decode_attention(o, 0, oq.float(), obidx, opos)
+    for kern in KERNELS.values():
+        c.decode_kernel = kern
+        out, lse = c.decode_attention(0, q, bidx, pos)
+        assert_attention_close(out, lse, ref_out, ref_lse, f"B=700 kernel {kern}")
+    out2, lse2 = c.decode_step(0, q, k, v, bidx, pos)            # fused path over several launches
+    c.decode_kernel = _lib.DECODE_TMA
+    out3, lse3 = c.decode_attention(0, q, bidx, pos)
+    assert_attention_close(out2, lse2, ref_out, ref_lse, "B=700 fused")
+    assert torch.equal(out3, c.decode_attention(0, q, bidx, pos)[0])
+    c.check_status()
+
+
+@pytest.mark.parametrize("B,hi", [(2, 300), (8, 700), (12, 1400), (24, 1000), (30, 1200), (36, 1100), (44, 1300), (60, 900)])
+def test_work_unit_schedule_across_batch_sizes(B, hi):
+    """Total tile counts from below the number of SMs to many per SM: phases of the unit schedule that are
+    shorter than the grid leave units without tiles, which nobody may read.  The workspace is poisoned, the
+    portable kernel is the cross-check."""
+    case = wl.make_decode_case(1234 + B, B=B, Hq=16, Hkv=8, D=128, P=128, n_pages=B * 12 + 2, max_batch_size=B + 1,
+                               len_lo=hi // 2, len_hi=hi, dtype=torch.bfloat16)
+    c, slots, bidx, pos, k, v, q = product_from_case(case)
+    c.decode_kernel = _lib.DECODE_PORTABLE
+    out_p, lse_p = c.decode_attention(0, q, bidx, pos)
+    c.decode_kernel = _lib.DECODE_TMA
+    c._workspace[16384:].fill_(255)                      # NaN bit patterns in every partial and table of the scratch
+    out_t, lse_t = c.decode_attention(0, q, bidx, pos)
+    assert_attention_close(out_t, lse_t, out_p.float().cpu(), lse_p.cpu(), f"B={B}")
+    c.check_status()
