@@ -120,3 +120,33 @@ def test_fp16_and_unmapped_rows():
     assert out2[0, :, off:off + 200].abs().max().item() == 0 and torch.isneginf(lse2[0, :, off:off + 200]).all()
     assert torch.equal(out2[0, :, :140], out[0, :, :140])
     c.check_status()
+
+
+def test_long_prompts_many_key_tiles():
+    """Thousands of keys per row: 20+ key tiles, query tiles whose rows have very different extents."""
+    seqs = [T(0, 0, 2900), T(50, 2000, 300)]
+    case = wl.make_prefill_case(31, seqs, Hq=4, Hkv=2, D=128, dtype=torch.bfloat16)
+    c, slots, bidx, ipos, mask, out, lse = run_product(case, 48, 4)
+    ref_out, ref_lse = oracle_prefill(case, slots)
+    compare_live_rows(case, out, lse, ref_out, ref_lse, "long prompts")
+    c.check_status()
+
+
+@pytest.mark.parametrize("seed", range(6))
+def test_random_prompt_layouts(seed):
+    """Random mixes of text, images (with a few leading register-like tokens folded into the span) and
+    several images per prompt, both kernels."""
+    rng = np.random.default_rng(500 + seed)
+    seqs = []
+    for _ in range(int(rng.integers(1, 5))):
+        toks = []
+        for _ in range(int(rng.integers(1, 4))):
+            toks += T(int(rng.integers(0, 40)), int(rng.integers(0, 2)) * int(rng.integers(2, 400)), int(rng.integers(0, 150)))
+        seqs.append(toks or T(0, 0, 1))
+    case = wl.make_prefill_case(900 + seed, seqs, Hq=8, Hkv=4, D=128, dtype=torch.bfloat16)
+    n_pages = sum((len(s) + 127) // 128 for s in seqs) + 2
+    for kernel in (_lib.PREFILL_TC, _lib.PREFILL_PORTABLE):
+        c, slots, bidx, ipos, mask, out, lse = run_product(case, n_pages, len(seqs) + 2, kernel=kernel)
+        ref_out, ref_lse = oracle_prefill(case, slots)
+        compare_live_rows(case, out, lse, ref_out, ref_lse, f"random layout {seed}, kernel {kernel}")
+        c.check_status()
