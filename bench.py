@@ -14,8 +14,9 @@ by one.  Inputs are synthetic and seeded; nothing is read from disk or network.
              divided by the device time of K steps, summed over GPUs, with the
              step inputs already resident in HBM.
   e2e        the same through the public Python API with the step's inputs
-             (q, k, v, slots, positions) coming from pinned host memory and
-             out / lse copied back to the host every step.
+             (q, k, v, slots, positions) copied from pinned host memory and
+             out / lse written to pinned host memory every step, the host
+             waiting for each step's result.
   roofline   the decode-attention kernel alone (its two launches) against the
              measured HBM copy bandwidth.
   cpu_baseline / --impl reference
@@ -244,8 +245,9 @@ def run_fpkv(args):
     in_bytes = nq + 2 * nk + B * 4 + B * 8
     in_h = torch.empty((NV, in_bytes), dtype=torch.uint8).pin_memory()
     in_d = torch.empty(in_bytes, dtype=torch.uint8, device=device)
-    res_d = torch.empty(nq + B * HQ * 4, dtype=torch.uint8, device=device)
-    res_h = torch.empty_like(res_d, device="cpu").pin_memory()
+    # The result needs no staging copy: out and lse are pinned host memory that the kernels write directly
+    # (the device can address pinned memory), so the step's result is on the host when the stream is idle.
+    res_h = torch.empty(nq + B * HQ * 4, dtype=torch.uint8).pin_memory()
 
     def views(buf):
         o = 0
@@ -261,12 +263,12 @@ def run_fpkv(args):
         hq.copy_(q_h[j]); hk.copy_(k_h[j]); hv.copy_(v_h[j]); hbi.copy_(bidx_h); hps.copy_(pos_h[0])
         host_pos.append(hps)
     q_s, k_s, v_s, bidx_s, pos_s = views(in_d)
-    out_s = res_d[:nq].view(torch.bfloat16).view(B, HQ, 1, D)
-    lse_s = res_d[nq:].view(torch.float32).view(B, HQ, 1)
+    out_s = res_h[:nq].view(torch.bfloat16).view(B, HQ, 1, D)
+    lse_s = res_h[nq:].view(torch.float32).view(B, HQ, 1)
 
-    # As the reference engine does for decode, the step (copy in, append + attention, copy out) is
-    # captured once per staging buffer in a CUDA graph and replayed; the host writes the step's
-    # positions into pinned memory, replays, and waits for the result.
+    # As the reference engine does for decode, the step (copy in, append + attention writing its result to
+    # host memory) is captured once per staging buffer in a CUDA graph and replayed; the host writes the
+    # step's positions into pinned memory, replays, and waits for the result.
     graphs = []
     if not args.kernels_only:
         side = torch.cuda.Stream(device)
@@ -275,13 +277,11 @@ def run_fpkv(args):
             with torch.cuda.stream(side):              # warm the path on the capture stream first
                 in_d.copy_(in_h[j], non_blocking=True)
                 cache.decode_step(0, q_s, k_s, v_s, bidx_s, pos_s, out=out_s, lse=lse_s)
-                res_h.copy_(res_d, non_blocking=True)
             side.synchronize()
             gr = torch.cuda.CUDAGraph()
             with torch.cuda.graph(gr, stream=side):
                 in_d.copy_(in_h[j], non_blocking=True)
                 cache.decode_step(0, q_s, k_s, v_s, bidx_s, pos_s, out=out_s, lse=lse_s)
-                res_h.copy_(res_d, non_blocking=True)
             graphs.append(gr)
         torch.cuda.synchronize(device)
 
