@@ -30,7 +30,9 @@
 //    resolved tiles into TMA tensor copies, one per K or V tile, into a ring
 //    of shared-memory slots.  A copy lands with the 128-byte swizzle so that
 //    ldmatrix reads are free of bank conflicts, and targets this CTA's own
-//    shared memory only.
+//    shared memory only.  The last, partly filled page of a row is fetched in
+//    groups of 16 token rows (one consumer warp's share) up to the row's length,
+//    and the warps whose rows were not fetched skip the tile.
 //  * Eight consumer warps each own page_size/8 token rows of every tile.  The
 //    GQA group's query heads are the M rows of mma.sync.m16n8k16 (zero padded
 //    to 16), so all query heads of a stored head consume the one staged tile.
@@ -143,7 +145,7 @@ struct Layout {
     static constexpr int kMergeFloats = kConsumerWarps * NREP * (D + 2);
     static constexpr int kBarWords = 80;                                // mbarriers (8 bytes each)
     static constexpr int kSmallInts = kDescBlocks * 33 + kUnitQueue + 16 + 4 + (kPhases + 1) + 3;
-    static constexpr int kBatchInts = (kMaxBatchPerLaunch + 1) + kMaxBatchPerLaunch + (kPhases * kMaxGrid + 1);
+    static constexpr int kBatchInts = (kMaxBatchPerLaunch + 1) + 2 * kMaxBatchPerLaunch + (kPhases * kMaxGrid + 1);
     static constexpr int kFixedBytes = 2 * kMergeFloats * 4 + kBarWords * 8 + (kSmallInts + kBatchInts) * 4 + 64;
     static constexpr int kSlotsFit = (kSmemBudget - 1024 - kFixedBytes) / kTileBytes;
     static constexpr int kSlots = (kSlotsFit > 12 ? 12 : kSlotsFit) & ~1;   // K and V alternate: even
@@ -196,7 +198,8 @@ __device__ __forceinline__ int unit_of(const int* ub, int NU, int t) {     // ub
 // ------------------------------------------------------------------ kernel
 template <typename T, int D, int P, int NREP, typename PosT>
 __global__ void __launch_bounds__(kThreads, 1)
-decode_tma_kernel(const __grid_constant__ CUtensorMap tmap, const Params prm)
+decode_tma_kernel(const __grid_constant__ CUtensorMap tmap, const __grid_constant__ CUtensorMap tmap_rows,
+                  const Params prm)
 {
     using L = Layout<D, P, NREP>;
     constexpr int NS = L::kSlots;
@@ -214,15 +217,16 @@ decode_tma_kernel(const __grid_constant__ CUtensorMap tmap, const Params prm)
     uint64_t* bars = reinterpret_cast<uint64_t*>(merge + 2 * L::kMergeFloats);
     int* ints = reinterpret_cast<int*>(bars + L::kBarWords);
     int* dcount = ints;                               // [kDescBlocks] tiles in the block, -1 = end of work
-    int* drow = dcount + kDescBlocks;                 // [kDescBlocks][32] pool row of the K tile, -1 = unmapped page
+    int* drow = dcount + kDescBlocks;                 // [kDescBlocks][32] pool row of the K tile | (16-row groups to fetch - 1), -1 = unmapped page
     int* uq = drow + kDescBlocks * 32;                // [kUnitQueue] claimed unit ids, -1 = end of work
-    int* slot_valid = uq + kUnitQueue;                // [16] per ring slot
+    int* slot_valid = uq + kUnitQueue;                // [16] per ring slot: row groups present (0 = unmapped page, 8 = whole tile)
     volatile int* abort_flag = slot_valid + 16;       // [4]: abort flag, tiles issued so far
     volatile int* issued = abort_flag + 1;
     int* pb = const_cast<int*>(abort_flag) + 4;       // [kPhases + 1] phase boundaries
     int* cum = pb + kPhases + 1;                      // [B + 1] tiles before row b
     int* slot_of = cum + kMaxBatchPerLaunch + 1;      // [B] slot of row b
-    int* ub = slot_of + kMaxBatchPerLaunch;           // [kPhases * G + 1] first tile of each unit
+    int* nkeys_of = slot_of + kMaxBatchPerLaunch;     // [B] visible keys of row b (position + 1)
+    int* ub = nkeys_of + kMaxBatchPerLaunch;          // [kPhases * G + 1] first tile of each unit
 
     const int tid = threadIdx.x, warp = tid / 32, lane = tid % 32;
     const int B = prm.B, Hkv = prm.Hkv;
@@ -259,6 +263,7 @@ decode_tma_kernel(const __grid_constant__ CUtensorMap tmap, const Params prm)
         else if (p < 0 || p / P >= prm.n_pages) raise_status(prm.status, FPKV_STATUS_BAD_POS);
         else npg = (int)(p / P) + 1;
         slot_of[b] = (npg > 0) ? (int)slot : 0;
+        nkeys_of[b] = (npg > 0) ? (int)p + 1 : 0;
         cum[b + 1] = npg * Hkv;                        // scanned below
     }
     __syncthreads();
@@ -345,7 +350,11 @@ decode_tma_kernel(const __grid_constant__ CUtensorMap tmap, const Params prm)
                     const long long trow = (long long)slot_of[b] * prm.n_pages;
                     const long long pg = prm.page_table[trow + (rel - h * npg)];
                     if (pg >= prm.n_pages) raise_status(prm.status, FPKV_STATUS_BAD_PAGE);
-                    else if (pg >= 0 && prm.p2l[trow + pg] >= 0) row_k = h * prm.rows_per_plane + (int)pg * P;
+                    else if (pg >= 0 && prm.p2l[trow + pg] >= 0) {
+                        // the row's last page is fetched only as far as it is filled, in groups of RW rows
+                        const int n_here = min(P, nkeys_of[b] - (rel - h * npg) * P);
+                        row_k = (h * prm.rows_per_plane + (int)pg * P) | ((n_here + RW - 1) / RW - 1);
+                    }
                 }
                 const uint32_t s = blk % kDescBlocks, ph = (blk / kDescBlocks) & 1u;
                 if (lane == 0) ok = mbar_wait(dempty0 + 8 * s, ph ^ 1u, abort_flag);
@@ -396,16 +405,26 @@ decode_tma_kernel(const __grid_constant__ CUtensorMap tmap, const Params prm)
             const int cnt = dcount[ds];
             if (cnt < 0) break;
             for (int j = 0; j < cnt && ok; ++j) {
-                const int rk = drow[ds * 32 + j];
+                const int desc = drow[ds * 32 + j];
+                const int rk = desc < 0 ? -1 : (desc & ~(P - 1));
+                const int groups = desc < 0 ? 0 : (desc & (P - 1)) + 1;
 #pragma unroll
                 for (int kv = 0; kv < 2; ++kv, ++it) {
                     const uint32_t s = it % NS, ph = (it / NS) & 1u;
                     if (!mbar_wait(empty0 + 8 * s, ph ^ 1u, abort_flag)) { ok = false; break; }
-                    slot_valid[s] = rk >= 0;
-                    if (rk >= 0) {
+                    slot_valid[s] = groups;
+                    const int row = rk + kv * Hkv * prm.rows_per_plane;
+                    const uint32_t dst = smem_u32(ring + s * kTile);
+                    if (groups == kConsumerWarps) {                     // whole page: one copy
                         mbar_arrive_expect_tx(full0 + 8 * s, kTile);
-                        tma_load_3d(smem_u32(ring + s * kTile), &tmap, 0, rk + kv * Hkv * prm.rows_per_plane, 0,
-                                    full0 + 8 * s);
+                        tma_load_3d(dst, &tmap, 0, row, 0, full0 + 8 * s);
+                    } else if (groups > 0) {                            // filled part of a row's last page
+                        mbar_arrive_expect_tx(full0 + 8 * s, groups * RW * D * 2);
+                        for (int g = 0; g < groups; ++g)
+#pragma unroll
+                            for (int half = 0; half < D / 64; ++half)
+                                tma_load_3d(dst + half * (P * 128) + g * (RW * 128), &tmap_rows, 0, row + g * RW, half,
+                                            full0 + 8 * s);
                     } else {
                         mbar_arrive(full0 + 8 * s);
                     }
@@ -507,7 +526,7 @@ decode_tma_kernel(const __grid_constant__ CUtensorMap tmap, const Params prm)
                 // ---------------- S = Q K^T for this warp's RW tokens -------
                 uint32_t s = it % NS, ph = (it / NS) & 1u;
                 if (!mbar_wait(full0 + 8 * s, ph, abort_flag)) { alive = false; break; }
-                const bool valid = slot_valid[s] != 0;
+                const bool valid = warp < slot_valid[s];               // this warp's rows were fetched
                 float sc[NB][4];
 #pragma unroll
                 for (int j = 0; j < NB; ++j) { sc[j][0] = sc[j][1] = sc[j][2] = sc[j][3] = 0.f; }
@@ -775,7 +794,7 @@ size_t partial_bytes(int G, int nrep, int D) {
 }
 
 template <typename T, int D, int P, int NREP, typename PosT>
-int launch_one(const CUtensorMap& map, Params prm, int G, cudaStream_t stream)
+int launch_one(const CUtensorMap& map, const CUtensorMap& map_rows, Params prm, int G, cudaStream_t stream)
 {
     using L = Layout<D, P, NREP>;
     auto kern = decode_tma_kernel<T, D, P, NREP, PosT>;
@@ -789,7 +808,7 @@ int launch_one(const CUtensorMap& map, Params prm, int G, cudaStream_t stream)
         cudaLaunchConfig_t cfg = {};
         cfg.gridDim = dim3(G); cfg.blockDim = dim3(kThreads); cfg.dynamicSmemBytes = L::kSmemBytes; cfg.stream = stream;
         cfg.attrs = attr; cfg.numAttrs = 1;
-        if (cudaLaunchKernelEx(&cfg, kern, map, prm) != cudaSuccess) return FPKV_ELAUNCH;
+        if (cudaLaunchKernelEx(&cfg, kern, map, map_rows, prm) != cudaSuccess) return FPKV_ELAUNCH;
     }
     // the finish kernel may become resident while the main grid runs; it waits for it on the device
     cudaLaunchConfig_t cfg = {};
@@ -800,22 +819,22 @@ int launch_one(const CUtensorMap& map, Params prm, int G, cudaStream_t stream)
 }
 
 template <typename T, int D, int P, typename PosT>
-int launch_nrep(int nrep, const CUtensorMap& map, const Params& prm, int G, cudaStream_t s)
+int launch_nrep(int nrep, const CUtensorMap& map, const CUtensorMap& map_rows, const Params& prm, int G, cudaStream_t s)
 {
     switch (nrep) {
-        case 1: return launch_one<T, D, P, 1, PosT>(map, prm, G, s);
-        case 2: return launch_one<T, D, P, 2, PosT>(map, prm, G, s);
-        case 4: return launch_one<T, D, P, 4, PosT>(map, prm, G, s);
-        case 8: return launch_one<T, D, P, 8, PosT>(map, prm, G, s);
+        case 1: return launch_one<T, D, P, 1, PosT>(map, map_rows, prm, G, s);
+        case 2: return launch_one<T, D, P, 2, PosT>(map, map_rows, prm, G, s);
+        case 4: return launch_one<T, D, P, 4, PosT>(map, map_rows, prm, G, s);
+        case 8: return launch_one<T, D, P, 8, PosT>(map, map_rows, prm, G, s);
     }
     return FPKV_ESHAPE;
 }
 
 template <typename T, typename PosT>
-int launch_shape(int D, int nrep, const CUtensorMap& map, const Params& prm, int G, cudaStream_t s)
+int launch_shape(int D, int nrep, const CUtensorMap& map, const CUtensorMap& map_rows, const Params& prm, int G, cudaStream_t s)
 {
-    return D == 128 ? launch_nrep<T, 128, 128, PosT>(nrep, map, prm, G, s)
-                    : launch_nrep<T, 64, 128, PosT>(nrep, map, prm, G, s);
+    return D == 128 ? launch_nrep<T, 128, 128, PosT>(nrep, map, map_rows, prm, G, s)
+                    : launch_nrep<T, 64, 128, PosT>(nrep, map, map_rows, prm, G, s);
 }
 
 }  // namespace
@@ -865,6 +884,14 @@ int launch_decode_tma(const PoolView& pv, int layer, void* out, float* lse, cons
                     CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
         return FPKV_ELAUNCH;
 
+    // the same tensor with a box of one consumer warp's rows (page_size / 8) of one 64-element column group
+    CUtensorMap map_rows;
+    const cuuint32_t box_rows[3] = {64, (cuuint32_t)(pv.P / kConsumerWarps), 1};
+    if (encode_fn()(&map_rows, dt, 3, pv.plane(layer, 0, 0), dims, strides, box_rows, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+                    CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                    CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
+        return FPKV_ELAUNCH;
+
     const int G = sm_count() < kMaxGrid ? sm_count() : kMaxGrid;
     const size_t esz = 2;
     for (int b0 = 0; b0 < B; b0 += kMaxBatchPerLaunch) {
@@ -888,11 +915,11 @@ int launch_decode_tma(const PoolView& pv, int layer, void* out, float* lse, cons
         prm.epi = epi;
         int rc;
         if (pv.dtype == FPKV_BF16)
-            rc = pos_type == FPKV_I32 ? launch_shape<__nv_bfloat16, int32_t>(pv.D, nrep, map, prm, G, stream)
-                                      : launch_shape<__nv_bfloat16, int64_t>(pv.D, nrep, map, prm, G, stream);
+            rc = pos_type == FPKV_I32 ? launch_shape<__nv_bfloat16, int32_t>(pv.D, nrep, map, map_rows, prm, G, stream)
+                                      : launch_shape<__nv_bfloat16, int64_t>(pv.D, nrep, map, map_rows, prm, G, stream);
         else
-            rc = pos_type == FPKV_I32 ? launch_shape<__half, int32_t>(pv.D, nrep, map, prm, G, stream)
-                                      : launch_shape<__half, int64_t>(pv.D, nrep, map, prm, G, stream);
+            rc = pos_type == FPKV_I32 ? launch_shape<__half, int32_t>(pv.D, nrep, map, map_rows, prm, G, stream)
+                                      : launch_shape<__half, int64_t>(pv.D, nrep, map, map_rows, prm, G, stream);
         if (rc != FPKV_OK) return rc;
     }
     return FPKV_OK;
