@@ -50,7 +50,7 @@ FALLBACK_HBM_GBS = 6650.0
 WINDOW = 64          # positions cycle through L .. L+63
 # dram__bytes_read.sum + dram__bytes_write.sum of one decode_tma_kernel launch on this workload, from the
 # ncu capture summarised in profiles/decode_tma_kernel_config2.md
-NCU_TRAFFIC_BYTES = 1.1868e9
+NCU_TRAFFIC_BYTES = 1.1731e9
 
 
 def step_bytes(lens_before_append):
