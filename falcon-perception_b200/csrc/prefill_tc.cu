@@ -35,6 +35,7 @@
 // kernel returns.
 
 #include <cuda.h>
+#include <type_traits>
 #include "common.cuh"
 
 namespace fpkv {
@@ -45,8 +46,8 @@ constexpr int kTileBytes = 128 * 128 * 2;              // any 128 x 128 16-bit t
 constexpr int kHalfBytes = kTileBytes / 2;             // 64 columns (128 bytes) x 128 rows
 constexpr int kStages = 2;
 constexpr int kSoftmaxWarps = 4;                       // per head; two groups (warps 0-3, 4-7) for a head pair
-constexpr int kLoadWarp = 8, kMmaWarp = 9;
-constexpr int kPrefillThreads = 10 * 32;
+constexpr int kLoadWarp = 8, kMmaWarp = 9;              // warps 9 and 10 issue the MMAs of head 0 and head 1 of the pair
+constexpr int kPrefillThreads = 12 * 32;               // warp 11 idles: registers are granted per four warps anyway
 constexpr int kMaxKeyTiles = 512;                      // 65 536 keys per sequence
 constexpr uint32_t kSpin = 1u << 22;
 constexpr uint32_t kTmemCols = 512;                    // S/P head 0, S/P head 1, O head 0, O head 1: 128 columns each
@@ -110,16 +111,22 @@ __device__ __forceinline__ uint32_t umma_idesc(bool bf16, bool b_mn_major) {
     d |= (uint32_t)(kTileM >> 4) << 24;
     return d;
 }
-__device__ __forceinline__ void umma(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
-    asm volatile("{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
-                 "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
-                 ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate) : "memory");
+// The issuing thread shares its scheduler with softmax warps, so the issue loop is kept to a few
+// instructions per MMA: the descriptors' high words are constants, the low words (start address >> 4)
+// advance by a compile-time step.
+__device__ __forceinline__ void umma(uint32_t tmem_d, uint32_t a_lo, uint32_t a_hi, uint32_t b_lo, uint32_t b_hi,
+                                     uint32_t idesc, uint32_t accumulate) {
+    asm volatile("{\n\t.reg .pred p;\n\t.reg .b64 da, db;\n\tmov.b64 da, {%1, %2};\n\tmov.b64 db, {%3, %4};\n\t"
+                 "setp.ne.b32 p, %6, 0;\n\t"
+                 "tcgen05.mma.cta_group::1.kind::f16 [%0], da, db, %5, p;\n\t}"
+                 ::"r"(tmem_d), "r"(a_lo), "r"(a_hi), "r"(b_lo), "r"(b_hi), "r"(idesc), "r"(accumulate));
 }
 // A operand from tensor memory (128 lanes x 8 columns of packed 16-bit pairs per K = 16 step), B from shared memory.
-__device__ __forceinline__ void umma_ts(uint32_t tmem_d, uint32_t tmem_a, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
-    asm volatile("{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
-                 "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}"
-                 ::"r"(tmem_d), "r"(tmem_a), "l"(bdesc), "r"(idesc), "r"(accumulate) : "memory");
+__device__ __forceinline__ void umma_ts(uint32_t tmem_d, uint32_t tmem_a, uint32_t b_lo, uint32_t b_hi, uint32_t idesc,
+                                        uint32_t accumulate) {
+    asm volatile("{\n\t.reg .pred p;\n\t.reg .b64 db;\n\tmov.b64 db, {%2, %3};\n\tsetp.ne.b32 p, %5, 0;\n\t"
+                 "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], db, %4, p;\n\t}"
+                 ::"r"(tmem_d), "r"(tmem_a), "r"(b_lo), "r"(b_hi), "r"(idesc), "r"(accumulate));
 }
 __device__ __forceinline__ void umma_commit(uint32_t bar) {
     asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
@@ -158,6 +165,12 @@ __device__ __forceinline__ void tmem_ld32_nowait(uint32_t taddr, uint32_t (&r)[3
                    "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
                  : "r"(taddr) : "memory");
 }
+__device__ __forceinline__ void tmem_st16_nowait(uint32_t taddr, const uint32_t (&r)[16]) {
+    asm volatile("tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16};"
+                 ::"r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]),
+                   "r"(r[8]), "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15])
+                 : "memory");
+}
 __device__ __forceinline__ void tmem_wait_ld() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
 __device__ __forceinline__ void tmem_st32(uint32_t taddr, const uint32_t (&r)[32]) {
     asm volatile("tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], "
@@ -176,22 +189,57 @@ __device__ __forceinline__ float max3f(float a, float b, float c) {
     asm("max.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(a), "f"(b), "f"(c));
     return d;
 }
+template <typename T> __device__ __forceinline__ uint32_t pack2(float a, float b);
+template <> __device__ __forceinline__ uint32_t pack2<__nv_bfloat16>(float a, float b) {
+    uint32_t w;
+    asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(w) : "f"(b), "f"(a));      // first source lands in the upper half
+    return w;
+}
+template <> __device__ __forceinline__ uint32_t pack2<__half>(float a, float b) {
+    uint32_t w;
+    asm("cvt.rn.f16x2.f32 %0, %1, %2;" : "=r"(w) : "f"(b), "f"(a));
+    return w;
+}
 __device__ __forceinline__ float ex2(float x) {
     float y;
     asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
     return y;
 }
 
-#ifdef FPKV_PROFILE
-// Development aid: time stamps of one CTA's MMA thread, [iteration][event].
-__device__ unsigned long long g_prefill_times[20][8];
+#if defined(FPKV_CTA_SUMS)
+__device__ unsigned long long g_cta_sums[8];               // all CTAs: [0] entry->loop start, [1] loop, [2] loop end->exit, [3] count, [4] tiles
 __device__ __forceinline__ unsigned long long gtime_ns() {
     unsigned long long t; asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t)); return t;
 }
-#define PF_STAMP(it, ev) do { if (blockIdx.x == 3 && blockIdx.y == 2 && (it) < 20) g_prefill_times[it][ev] = gtime_ns(); } while (0)
-#else
-#define PF_STAMP(it, ev) do { } while (0)
 #endif
+#ifdef FPKV_FINE
+// Development aid: cycle stamps of one CTA for two consecutive key tiles, [tile - 3][slot].
+__device__ long long g_fine[2][64];
+#define FT(j, slot) do { if (((j) == 3 || (j) == 4) && blockIdx.x == 3 && blockIdx.y == 2) g_fine[(j) - 3][slot] = clock64(); } while (0)
+#else
+#define FT(j, slot) do { } while (0)
+#endif
+
+// S = Q K^T: eight K = 16 steps (32 bytes along the 128-byte swizzled rows, second 64-element half 16 KiB on), then
+// the commit that tells the softmax group.
+__device__ __forceinline__ void issue_qk_gemm(uint32_t d, uint32_t a_lo, uint32_t b_lo, uint32_t hi, uint32_t idesc, uint32_t bar) {
+#pragma unroll
+    for (int k = 0; k < kHeadDim / 16; ++k) {
+        const uint32_t off = ((k >> 2) * kHalfBytes + (k & 3) * 32) >> 4;
+        umma(d, a_lo + off, hi, b_lo + off, hi, idesc, k > 0);
+    }
+    umma_commit(bar);
+}
+// O += P V: P from tensor memory (8 packed columns per 16 keys), V rows from shared memory (MN-major, 16 rows = 2 KiB per step).
+// Issued in two halves of four steps (keys 0-63, 64-127) so that the first can run while the softmax group still
+// exponentiates the second half of the tile.
+template <int kHalf>
+__device__ __forceinline__ void issue_pv_gemm(uint32_t d, uint32_t a, uint32_t b_lo, uint32_t hi, uint32_t idesc, uint32_t acc0) {
+#pragma unroll
+    for (int k = kHalf * 4; k < kHalf * 4 + 4; ++k)
+        umma_ts(d, a + k * 8, b_lo + k * ((16 * 128) >> 4), hi, idesc, k > 0 ? 1u : acc0);
+}
+
 
 struct PrefillParams {
     const int64_t* page_table;
@@ -220,7 +268,7 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_consta
     uint8_t* k_s = q_s + 2 * kTileBytes;                   // kStages x 32 KiB
     uint8_t* v_s = k_s + kStages * kTileBytes;             // kStages x 32 KiB
     uint64_t* bars = reinterpret_cast<uint64_t*>(v_s + kStages * kTileBytes);
-    int* ints = reinterpret_cast<int*>(bars + 16);
+    int* ints = reinterpret_cast<int*>(bars + 24);
     volatile int* abort_flag = ints;                       // [0] abort, [1] TMEM base
     int* tmem_slot = ints + 1;
     int* warp_red = ints + 4;                              // [8] per-warp reductions of the prologue
@@ -230,8 +278,10 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_consta
     const uint32_t q_full = s32(bars + 0);
     const uint32_t k_full0 = s32(bars + 1), v_full0 = s32(bars + 3), k_empty0 = s32(bars + 5), v_empty0 = s32(bars + 7);
     const uint32_t s_full0 = s32(bars + 9);                // [2] one per head of the pair
-    const uint32_t p_full0 = s32(bars + 11);               // [2]
-    const uint32_t all_done = s32(bars + 13);
+    const uint32_t p_full0 = s32(bars + 11);               // [2] all 64 packed columns of P written
+    const uint32_t p_half0 = s32(bars + 15);               // [2] the first 32 packed columns (keys 0-63) written
+    const uint32_t turn0 = s32(bars + 17);                 // [2] this head has issued the exponentials of its tile
+    const uint32_t all_done0 = s32(bars + 13);             // [2] one per head
 
     const int tid = threadIdx.x, warp = tid / 32, lane = tid % 32;
     const int t0 = blockIdx.x * kTileM;                    // first packed token of the query tile
@@ -241,15 +291,19 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_consta
     const int group = warp / kSoftmaxWarps;                // softmax group = which head of the pair (warps 0-3, 4-7)
     const bool is_softmax = warp < 2 * kSoftmaxWarps;
 
+#if defined(FPKV_CTA_SUMS)
+    const unsigned long long cta_t0 = gtime_ns();
+    __shared__ unsigned long long cta_marks[2];
+#endif
     // ---- prologue ----------------------------------------------------------
     if (tid == 0) {
         bar_init(q_full, 1);
         for (int s = 0; s < kStages; ++s) {
             bar_init(k_full0 + 8 * s, 1); bar_init(v_full0 + 8 * s, 1);
-            bar_init(k_empty0 + 8 * s, 1); bar_init(v_empty0 + 8 * s, 1);
+            bar_init(k_empty0 + 8 * s, heads); bar_init(v_empty0 + 8 * s, heads);     // one commit per head's MMA warp
         }
-        for (int g = 0; g < 2; ++g) { bar_init(s_full0 + 8 * g, 1); bar_init(p_full0 + 8 * g, kSoftmaxWarps); }
-        bar_init(all_done, 1);
+        for (int g = 0; g < 2; ++g) { bar_init(s_full0 + 8 * g, 1); bar_init(p_full0 + 8 * g, kSoftmaxWarps); bar_init(p_half0 + 8 * g, kSoftmaxWarps); bar_init(turn0 + 8 * g, kSoftmaxWarps); }
+        bar_init(all_done0, 1); bar_init(all_done0 + 8, 1);
         *abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
@@ -322,61 +376,61 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_consta
                 tma_3d(s32(v_s + st * kTileBytes), &kv_map, 0, page_row[j] + prm.Hkv * prm.rows_per_plane, 0, v_full0 + 8 * st);
             }
         }
-    } else if (warp == kMmaWarp) {
-        // ============================== MMA issuer ==========================
-        // The two heads of the pair alternate on the tensor pipe: while one head's softmax runs, the
-        // other head's P.V and next Q.K^T execute, and both use the one staged K / V tile.
+    } else if (warp >= kMmaWarp && warp < kMmaWarp + heads) {
+        // ============================== MMA issuers =========================
+        // One issuing warp per head of the pair.  The tensor pipe takes the MMAs of one thread strictly one
+        // after the other, and whatever else that thread does (barrier waits, commits) is time the pipe
+        // idles for it; with an issuer per head the other head's MMAs fill those gaps, and each head's
+        // chain  S -> softmax -> P.V -> next S  advances on its own.  Both heads read the one staged K / V tile.
+        const int g = warp - kMmaWarp;
         if (lane == 0 && n_tiles > 0) {
             const uint32_t idesc_qk = umma_idesc(prm.is_bf16 != 0, false);
             const uint32_t idesc_pv = umma_idesc(prm.is_bf16 != 0, true);
-            auto issue_qk = [&](int g, int j) {            // S_g = Q_g K_j^T (K tile already waited for)
-                const uint32_t a0 = s32(q_s + g * kTileBytes), b0 = s32(k_s + (j % kStages) * kTileBytes);
-#pragma unroll
-                for (int k = 0; k < kHeadDim / 16; ++k) {  // 16 contraction elements = 32 bytes per step
-                    const uint32_t off = (k >> 2) * kHalfBytes + (k & 3) * 32;
-                    umma(tmem + g * kTileN, umma_desc(a0 + off, 0, 1024), umma_desc(b0 + off, 0, 1024), idesc_qk, k > 0);
-                }
-                umma_commit(s_full0 + 8 * g);
-            };
-            auto issue_pv = [&](int g, int j) {            // O_g += P_g V_j, P read from tensor memory
-                const uint32_t b0 = s32(v_s + (j % kStages) * kTileBytes);
-#pragma unroll
-                for (int k = 0; k < kTileN / 16; ++k)      // 16 keys per step: 8 packed columns of P, 16 rows of V
-                    umma_ts(tmem + 256 + g * kTileN, tmem + g * kTileN + k * 8,
-                            umma_desc(b0 + k * 16 * 128, kHalfBytes, 1024), idesc_pv, (j > 0 || k > 0));
-            };
-            PF_STAMP(19, 0);
+            // descriptor words: low = start address >> 4 (| LBO for MN-major), high = SBO 1024 | version | 128-byte swizzle
+            const uint32_t desc_hi = (uint32_t)(umma_desc(0, 0, 1024) >> 32);
+            const uint32_t q_lo = ((s32(q_s) & 0x3FFFF) >> 4) + g * (kTileBytes >> 4), k_lo = (s32(k_s) & 0x3FFFF) >> 4;
+            const uint32_t v_lo = ((s32(v_s) & 0x3FFFF) >> 4) | (uint32_t)umma_desc(0, kHalfBytes, 1024);
+            const uint32_t t_s = tmem + g * kTileN, t_o = tmem + 256 + g * kTileN;
+            const uint32_t s_full = s_full0 + 8 * g, p_full = p_full0 + 8 * g;
+#if defined(FPKV_CTA_SUMS)
+            if (g == 0) cta_marks[0] = gtime_ns();
+#endif
             alive = bar_wait(q_full, 0, abort_flag) && bar_wait(k_full0, 0, abort_flag);
-            PF_STAMP(19, 1);
             if (alive) {
                 tc_fence_after();
-                for (int g = 0; g < heads; ++g) issue_qk(g, 0);
+                issue_qk_gemm(t_s, q_lo, k_lo, desc_hi, idesc_qk, s_full);
                 umma_commit(k_empty0);
             }
             for (int j = 0; j < n_tiles && alive; ++j) {
                 const int st = j % kStages, sn = (j + 1) % kStages;
-                const bool more = j + 1 < n_tiles;
-                for (int g = 0; g < heads && alive; ++g) {
-                    PF_STAMP(j, g * 4 + 0);
-                    if (!bar_wait(p_full0 + 8 * g, j & 1u, abort_flag)) { alive = false; break; }
-                    PF_STAMP(j, g * 4 + 1);
-                    if (g == 0 && !bar_wait(v_full0 + 8 * st, (j / kStages) & 1u, abort_flag)) { alive = false; break; }
-                    PF_STAMP(j, g * 4 + 2);
-                    tc_fence_after();
-                    issue_pv(g, j);
-                    if (g == heads - 1) umma_commit(v_empty0 + 8 * st);
-                    if (more) {
-                        if (g == 0 && !bar_wait(k_full0 + 8 * sn, ((j + 1) / kStages) & 1u, abort_flag)) { alive = false; break; }
-                        PF_STAMP(j, g * 4 + 3);
-                        tc_fence_after();
-                        issue_qk(g, j + 1);
-                        if (g == heads - 1) umma_commit(k_empty0 + 8 * sn);
-                    }
+                // the operand tiles first: they arrived long ago, and waiting for them here costs nothing
+                // while the softmax group is still busy
+                if (!bar_wait(v_full0 + 8 * st, (j / kStages) & 1u, abort_flag)) { alive = false; break; }
+                if (j + 1 < n_tiles && !bar_wait(k_full0 + 8 * sn, ((j + 1) / kStages) & 1u, abort_flag)) { alive = false; break; }
+                FT(j, g * 8 + 0);
+                if (!bar_wait(p_half0 + 8 * g, j & 1u, abort_flag)) { alive = false; break; }
+                FT(j, g * 8 + 1);
+                tc_fence_after();
+                issue_pv_gemm<0>(t_o, t_s, v_lo + st * (kTileBytes >> 4), desc_hi, idesc_pv, j > 0);
+                FT(j, g * 8 + 2);
+                if (!bar_wait(p_full, j & 1u, abort_flag)) { alive = false; break; }
+                FT(j, g * 8 + 3);
+                tc_fence_after();
+                issue_pv_gemm<1>(t_o, t_s, v_lo + st * (kTileBytes >> 4), desc_hi, idesc_pv, 1u);
+                umma_commit(v_empty0 + 8 * st);
+                FT(j, g * 8 + 4);
+                if (j + 1 < n_tiles) {
+                    issue_qk_gemm(t_s, q_lo, k_lo + sn * (kTileBytes >> 4), desc_hi, idesc_qk, s_full);
+                    umma_commit(k_empty0 + 8 * sn);
                 }
+                FT(j, g * 8 + 5);
             }
-            if (alive) umma_commit(all_done);
+            if (alive) umma_commit(all_done0 + 8 * g);
+#if defined(FPKV_CTA_SUMS)
+            if (g == 0) cta_marks[1] = gtime_ns();
+#endif
         }
-    } else if (group < heads) {
+    } else if (is_softmax && group < heads) {
         // ============================== softmax warps =======================
         const uint32_t lane_base = (uint32_t)((warp % 4) * 32) << 16;    // a warp reaches the TMEM lanes of its quarter
         const uint32_t ts = tmem + group * kTileN + lane_base;          // S, then P, of this head
@@ -388,10 +442,12 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_consta
             // s_full also tells that P.V of tile j-1 is complete: O is stable and the P columns are free
             if (!bar_wait(s_full0 + 8 * group, j & 1u, abort_flag)) { alive = false; break; }
             tc_fence_after();
+#define SFT(slot) do { if ((tid & 127) == 0) FT(j, 16 + group * 16 + (slot)); } while (0)
+            SFT(0);
             const int valid_cols = page_ok[j] ? min(kTileN, my_extent - j * kTileN) : 0;   // <= 0: nothing visible
 #ifdef FPKV_EXP_SKIP_SOFTMAX                               // timing experiment only: tensor + copy pipeline alone
             tc_fence_before(); __syncwarp();
-            if (lane == 0) bar_arrive(p_full0 + 8 * group);
+            if (lane == 0) { bar_arrive(p_half0 + 8 * group); bar_arrive(p_full0 + 8 * group); }
             continue;
 #endif
             // the whole score row of this thread: four loads in flight, one wait
@@ -399,8 +455,8 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_consta
 #pragma unroll
             for (int c4 = 0; c4 < 4; ++c4) tmem_ld32_nowait(ts + c4 * 32, sv[c4]);
             tmem_wait_ld();
-            // Most tiles are fully visible to every row of the warp; they take a path without a
-            // per-element mask (one FFMA, one EX2, one add and half a pack per score).
+            SFT(1);
+            // Most tiles are fully visible to every row of the warp; they take a path without a per-element mask.
             const bool full = __all_sync(0xffffffffu, valid_cols >= kTileN);
             float mx;
             if (full) {
@@ -439,46 +495,73 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_consta
                 l *= alpha;
                 m_ref = m_new;
             }
-            // probabilities, packed two per 32-bit column, written over the scores of this row: columns
-            // [0,64) of the region become P (the scores are all in registers by now).
+            // Probabilities, packed two per 32-bit column, written over the scores of this row (all in registers
+            // by now): columns [0,64) of the region become P.  The exponential unit (16 results per clock per
+            // SM) bounds this phase.  The first 32 packed columns (keys 0-63) are handed to the MMA warp as soon
+            // as they are stored, so that half of P.V runs under the second half's exponentials.
             float r4[4] = {0.f, 0.f, 0.f, 0.f};
             const float neg_m = (m_ref == -INFINITY) ? 0.f : -m_ref;
-#pragma unroll
-            for (int half = 0; half < 2; ++half) {         // 64 scores -> 32 packed columns per store
-                uint32_t pk[32];
-#pragma unroll
-                for (int sub = 0; sub < 2; ++sub) {
-                    const int c4 = half * 2 + sub;
-#pragma unroll
-                    for (int c = 0; c < 32; c += 2) {
-                        float p0 = ex2(fmaf(__uint_as_float(sv[c4][c]), prm.scale_log2, neg_m));
-                        float p1 = ex2(fmaf(__uint_as_float(sv[c4][c + 1]), prm.scale_log2, neg_m));
-                        if (!full) {
-                            if (c4 * 32 + c >= valid_cols) p0 = 0.f;
-                            if (c4 * 32 + c + 1 >= valid_cols) p1 = 0.f;
-                        }
-                        r4[(c >> 1) & 1] += p0;
-                        r4[2 + ((c >> 1) & 1)] += p1;
-                        uint32_t w;
-                        if (prm.is_bf16) { __nv_bfloat162 b = __floats2bfloat162_rn(p0, p1); w = *reinterpret_cast<uint32_t*>(&b); }
-                        else { __half2 b = __floats2half2_rn(p0, p1); w = *reinterpret_cast<uint32_t*>(&b); }
-                        pk[sub * 16 + c / 2] = w;
-                    }
-                }
-                tmem_st32_nowait(ts + half * 32, pk);
+            SFT(2);
+            // The two heads take turns at the exponentials: a head that has the unit to itself finishes in
+            // half the time, and meanwhile the other head's MMAs run.  Left alone, the two heads drift into
+            // step, exponentiate together at half speed each and then queue on the tensor pipe together.
+            // Head 1 starts tile j when head 0 has issued the exponentials of tile j, head 0 starts tile j when
+            // head 1 has issued those of tile j - 1; the turn passes before the stores and barrier traffic that
+            // end a tile, so the unit does not idle through them.
+#ifndef FPKV_EXP_NO_TURNS
+            if (heads == 2) {
+                if (group == 1) { if (!bar_wait(turn0, j & 1u, abort_flag)) { alive = false; break; } }
+                else if (j > 0) { if (!bar_wait(turn0 + 8, (j - 1) & 1u, abort_flag)) { alive = false; break; } }
             }
-            asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
+#endif
+            SFT(3);
+            auto probabilities = [&](auto full_tag) {
+                constexpr bool kFull = decltype(full_tag)::value;
+#pragma unroll
+                for (int half = 0; half < 2; ++half) {     // 64 scores -> 32 packed columns per store
+                    uint32_t pk[32];
+#pragma unroll
+                    for (int sub = 0; sub < 2; ++sub) {
+                        const int c4 = half * 2 + sub;
+#pragma unroll
+                        for (int c = 0; c < 32; c += 2) {
+                            float p0 = ex2(fmaf(__uint_as_float(sv[c4][c]), prm.scale_log2, neg_m));
+                            float p1 = ex2(fmaf(__uint_as_float(sv[c4][c + 1]), prm.scale_log2, neg_m));
+                            if (!kFull) {
+                                if (c4 * 32 + c >= valid_cols) p0 = 0.f;
+                                if (c4 * 32 + c + 1 >= valid_cols) p1 = 0.f;
+                            }
+                            r4[(c >> 1) & 1] += p0;
+                            r4[2 + ((c >> 1) & 1)] += p1;
+                            pk[sub * 16 + c / 2] = pack2<T>(p0, p1);
+                        }
+                    }
+                    SFT(4 + half * 2);
+                    if (half == 1 && heads == 2) { __syncwarp(); if (lane == 0) bar_arrive(turn0 + 8 * group); }
+                    tmem_st32_nowait(ts + half * 32, pk);
+                    asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
+                    if (half == 0) {
+                        tc_fence_before();
+                        __syncwarp();
+                        if (lane == 0) bar_arrive(p_half0 + 8 * group);
+                    }
+                    SFT(5 + half * 2);
+                }
+            };
+            if (full) probabilities(std::true_type{}); else probabilities(std::false_type{});
             const float rsum = (r4[0] + r4[1]) + (r4[2] + r4[3]);
             l += rsum;
             tc_fence_before();
             __syncwarp();
             if (lane == 0) bar_arrive(p_full0 + 8 * group);
+            SFT(8);
+#undef SFT
         }
         // ---- epilogue: O / l -> out, lse --------------------------------------
         T* out = reinterpret_cast<T*>(prm.out);
         const int tok = t0 + row;
         if (n_tiles > 0 && alive) {
-            if (!bar_wait(all_done, 0, abort_flag)) alive = false;
+            if (!bar_wait(all_done0 + 8 * group, 0, abort_flag)) alive = false;
             tc_fence_after();
         }
         if (alive) {
@@ -486,23 +569,37 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_consta
             const float lse_nat = l > 0.f ? (m_ref + log2f(l)) * kLn2 : -INFINITY;
             const bool gate_on = prm.epi.sinks != nullptr;
             const float gate = sink_gate(prm.epi, hq, lse_nat);
+            // Each thread owns one 256-byte output row; storing it straight from registers would touch 32
+            // different lines per warp instruction.  The warp stages its 32 rows in the (now idle) query tile
+            // of its head, 16-byte chunks XOR-swizzled by row so that neither side has bank conflicts, and
+            // writes them out two whole rows per instruction.
+            uint8_t* slab = q_s + group * kTileBytes + (warp % 4) * (32 * 256);
 #pragma unroll 1
             for (int c4 = 0; c4 < 4; ++c4) {
                 if (n_tiles > 0) tmem_ld32(to + c4 * 32, v);
-                if (tok < prm.L) {
-                    T* dst = out + (prm.epi.token_major ? ((size_t)tok * prm.Hq + hq) : ((size_t)hq * prm.L + tok)) * kHeadDim + c4 * 32;
 #pragma unroll
-                    for (int c = 0; c < 32; c += 8) {
-                        uint32_t w[4];
+                for (int c = 0; c < 32; c += 8) {
+                    uint32_t w[4];
 #pragma unroll
-                        for (int e = 0; e < 4; ++e) {
-                            const float a = (n_tiles > 0 && l > 0.f) ? __uint_as_float(v[c + 2 * e]) * inv : 0.f;
-                            const float b = (n_tiles > 0 && l > 0.f) ? __uint_as_float(v[c + 2 * e + 1]) * inv : 0.f;
-                            const T ra = gated_out<T>(a, gate, gate_on), rb = gated_out<T>(b, gate, gate_on);
-                            w[e] = (uint32_t)*reinterpret_cast<const uint16_t*>(&ra) | ((uint32_t)*reinterpret_cast<const uint16_t*>(&rb) << 16);
-                        }
-                        *reinterpret_cast<uint4*>(dst + c) = make_uint4(w[0], w[1], w[2], w[3]);
+                    for (int e = 0; e < 4; ++e) {
+                        const float a = (n_tiles > 0 && l > 0.f) ? __uint_as_float(v[c + 2 * e]) * inv : 0.f;
+                        const float b = (n_tiles > 0 && l > 0.f) ? __uint_as_float(v[c + 2 * e + 1]) * inv : 0.f;
+                        const T ra = gated_out<T>(a, gate, gate_on), rb = gated_out<T>(b, gate, gate_on);
+                        w[e] = (uint32_t)*reinterpret_cast<const uint16_t*>(&ra) | ((uint32_t)*reinterpret_cast<const uint16_t*>(&rb) << 16);
                     }
+                    const int chunk = c4 * 4 + c / 8;
+                    *reinterpret_cast<uint4*>(slab + lane * 256 + ((chunk ^ (lane & 15)) * 16)) = make_uint4(w[0], w[1], w[2], w[3]);
+                }
+            }
+            __syncwarp();
+#pragma unroll 4
+            for (int i = 0; i < 16; ++i) {
+                const int rr = 2 * i + (lane >> 4), chunk = lane & 15;
+                const uint4 val = *reinterpret_cast<const uint4*>(slab + rr * 256 + ((chunk ^ (rr & 15)) * 16));
+                const int tk = t0 + (warp % 4) * 32 + rr;
+                if (tk < prm.L) {
+                    T* dst = out + (prm.epi.token_major ? ((size_t)tk * prm.Hq + hq) : ((size_t)hq * prm.L + tk)) * kHeadDim + chunk * 8;
+                    *reinterpret_cast<uint4*>(dst) = val;
                 }
             }
             if (tok < prm.L) prm.lse[(size_t)hq * prm.L + tok] = lse_nat;
@@ -520,6 +617,13 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_consta
         for (int s = 0; s < kStages; ++s)
             for (uint32_t k = 0; k < (1u << 16) && !bar_try(k_full0 + 8 * s, 0) && !bar_try(k_full0 + 8 * s, 1); ++k) {}
     }
+#if defined(FPKV_CTA_SUMS)
+    if (tid == 0 && n_tiles > 0) {
+        const unsigned long long t3 = gtime_ns();
+        atomicAdd(&g_cta_sums[0], cta_marks[0] - cta_t0); atomicAdd(&g_cta_sums[1], cta_marks[1] - cta_marks[0]);
+        atomicAdd(&g_cta_sums[2], t3 - cta_marks[1]); atomicAdd(&g_cta_sums[3], 1ull); atomicAdd(&g_cta_sums[4], (unsigned long long)n_tiles);
+    }
+#endif
     if (warp == kMmaWarp) {
         tc_fence_after();
         asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(kTmemCols) : "memory");
@@ -541,13 +645,19 @@ EncodeFn encoder() {
     return fn;
 }
 
-constexpr int kPrefillSmem = 1024 + (2 + 2 * kStages) * kTileBytes + 16 * 8 + 16 * 4 + kMaxKeyTiles * 5 + 64;   // Q x2, K and V x kStages
+constexpr int kPrefillSmem = 1024 + (2 + 2 * kStages) * kTileBytes + 24 * 8 + 16 * 4 + kMaxKeyTiles * 5 + 64;   // Q x2, K and V x kStages
 
 }  // namespace
 
-#ifdef FPKV_PROFILE
-extern "C" __attribute__((visibility("default"))) int fpkv_debug_prefill_times(unsigned long long* host_out) {
-    return (int)cudaMemcpyFromSymbol(host_out, g_prefill_times, sizeof(unsigned long long) * 20 * 8);
+#if defined(FPKV_CTA_SUMS)
+extern "C" __attribute__((visibility("default"))) int fpkv_debug_cta_sums(unsigned long long* host_out, int reset) {
+    if (reset) { unsigned long long z[8] = {0}; return (int)cudaMemcpyToSymbol(g_cta_sums, z, sizeof(z)); }
+    return (int)cudaMemcpyFromSymbol(host_out, g_cta_sums, sizeof(unsigned long long) * 8);
+}
+#endif
+#ifdef FPKV_FINE
+extern "C" __attribute__((visibility("default"))) int fpkv_debug_fine(long long* host_out) {
+    return (int)cudaMemcpyFromSymbol(host_out, g_fine, sizeof(long long) * 128);
 }
 #endif
 
