@@ -165,12 +165,6 @@ __device__ __forceinline__ void tmem_ld32_nowait(uint32_t taddr, uint32_t (&r)[3
                    "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
                  : "r"(taddr) : "memory");
 }
-__device__ __forceinline__ void tmem_st16_nowait(uint32_t taddr, const uint32_t (&r)[16]) {
-    asm volatile("tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16};"
-                 ::"r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]),
-                   "r"(r[8]), "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15])
-                 : "memory");
-}
 __device__ __forceinline__ void tmem_wait_ld() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
 __device__ __forceinline__ void tmem_st32(uint32_t taddr, const uint32_t (&r)[32]) {
     asm volatile("tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], "
@@ -274,13 +268,12 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_consta
     int* warp_red = ints + 4;                              // [8] per-warp reductions of the prologue
     int* page_row = ints + 16;                             // [kMaxKeyTiles] pool row of key tile j (page 0 when unmapped)
     unsigned char* page_ok = reinterpret_cast<unsigned char*>(page_row + kMaxKeyTiles);   // [kMaxKeyTiles]
+    float* xch = reinterpret_cast<float*>(page_ok + kMaxKeyTiles);                         // [2][2][128] row max / row sum exchange
 
     const uint32_t q_full = s32(bars + 0);
     const uint32_t k_full0 = s32(bars + 1), v_full0 = s32(bars + 3), k_empty0 = s32(bars + 5), v_empty0 = s32(bars + 7);
     const uint32_t s_full0 = s32(bars + 9);                // [2] one per head of the pair
-    const uint32_t p_full0 = s32(bars + 11);               // [2] all 64 packed columns of P written
-    const uint32_t p_half0 = s32(bars + 15);               // [2] the first 32 packed columns (keys 0-63) written
-    const uint32_t turn0 = s32(bars + 17);                 // [2] this head has issued the exponentials of its tile
+    const uint32_t p_full0 = s32(bars + 11);               // [2] P of the tile written (all eight softmax warps arrive)
     const uint32_t all_done0 = s32(bars + 13);             // [2] one per head
 
     const int tid = threadIdx.x, warp = tid / 32, lane = tid % 32;
@@ -288,7 +281,6 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_consta
     const int heads = prm.heads_per_cta;                   // 1 or 2 query heads of one stored head
     const int hq0 = blockIdx.y * heads;
     const int hkv = hq0 / (prm.Hq / prm.Hkv);
-    const int group = warp / kSoftmaxWarps;                // softmax group = which head of the pair (warps 0-3, 4-7)
     const bool is_softmax = warp < 2 * kSoftmaxWarps;
 
 #if defined(FPKV_CTA_SUMS)
@@ -302,7 +294,7 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_consta
             bar_init(k_full0 + 8 * s, 1); bar_init(v_full0 + 8 * s, 1);
             bar_init(k_empty0 + 8 * s, heads); bar_init(v_empty0 + 8 * s, heads);     // one commit per head's MMA warp
         }
-        for (int g = 0; g < 2; ++g) { bar_init(s_full0 + 8 * g, 1); bar_init(p_full0 + 8 * g, kSoftmaxWarps); bar_init(p_half0 + 8 * g, kSoftmaxWarps); bar_init(turn0 + 8 * g, kSoftmaxWarps); }
+        for (int g = 0; g < 2; ++g) { bar_init(s_full0 + 8 * g, 1); bar_init(p_full0 + 8 * g, 2 * kSoftmaxWarps); }
         bar_init(all_done0, 1); bar_init(all_done0 + 8, 1);
         *abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -407,202 +399,182 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_consta
                 // while the softmax group is still busy
                 if (!bar_wait(v_full0 + 8 * st, (j / kStages) & 1u, abort_flag)) { alive = false; break; }
                 if (j + 1 < n_tiles && !bar_wait(k_full0 + 8 * sn, ((j + 1) / kStages) & 1u, abort_flag)) { alive = false; break; }
-                FT(j, g * 8 + 0);
-                if (!bar_wait(p_half0 + 8 * g, j & 1u, abort_flag)) { alive = false; break; }
-                FT(j, g * 8 + 1);
+                if (!bar_wait(p_full, j & 1u, abort_flag)) { alive = false; break; }
                 tc_fence_after();
                 issue_pv_gemm<0>(t_o, t_s, v_lo + st * (kTileBytes >> 4), desc_hi, idesc_pv, j > 0);
-                FT(j, g * 8 + 2);
-                if (!bar_wait(p_full, j & 1u, abort_flag)) { alive = false; break; }
-                FT(j, g * 8 + 3);
-                tc_fence_after();
                 issue_pv_gemm<1>(t_o, t_s, v_lo + st * (kTileBytes >> 4), desc_hi, idesc_pv, 1u);
                 umma_commit(v_empty0 + 8 * st);
-                FT(j, g * 8 + 4);
                 if (j + 1 < n_tiles) {
                     issue_qk_gemm(t_s, q_lo, k_lo + sn * (kTileBytes >> 4), desc_hi, idesc_qk, s_full);
                     umma_commit(k_empty0 + 8 * sn);
                 }
-                FT(j, g * 8 + 5);
             }
             if (alive) umma_commit(all_done0 + 8 * g);
 #if defined(FPKV_CTA_SUMS)
             if (g == 0) cta_marks[1] = gtime_ns();
 #endif
         }
-    } else if (is_softmax && group < heads) {
+    } else if (is_softmax) {
         // ============================== softmax warps =======================
-        const uint32_t lane_base = (uint32_t)((warp % 4) * 32) << 16;    // a warp reaches the TMEM lanes of its quarter
-        const uint32_t ts = tmem + group * kTileN + lane_base;          // S, then P, of this head
-        const uint32_t to = tmem + 256 + group * kTileN + lane_base;    // O of this head
-        const int hq = hq0 + group;
-        float m_ref = -INFINITY, l = 0.f;
+        // All eight warps work on ONE head's score tile at a time, two threads per query row: warps w and
+        // w + 4 reach the same 32 tensor-memory lanes, warp w / 4 takes key columns [0,64) or [64,128).  The
+        // exponential unit (16 results per clock per SM) bounds this phase; with two warps per scheduler
+        // it stays saturated, and a head's tile is through in half the time a single thread per row needs,
+        // which is what the chain  S -> softmax -> P.V -> next S  of each head waits for.  The heads alternate
+        // (tile j of head 0, tile j of head 1, tile j + 1 of head 0, ...) while the other head's MMAs run.
+        const int quarter = warp % 4, colhalf = warp / 4;
+        const uint32_t lane_base = (uint32_t)(quarter * 32) << 16;
+        float m_ref[2] = {-INFINITY, -INFINITY}, l[2] = {0.f, 0.f};
         uint32_t v[32];
-        for (int j = 0; j < n_tiles && alive; ++j) {
-            // s_full also tells that P.V of tile j-1 is complete: O is stable and the P columns are free
-            if (!bar_wait(s_full0 + 8 * group, j & 1u, abort_flag)) { alive = false; break; }
-            tc_fence_after();
-#define SFT(slot) do { if ((tid & 127) == 0) FT(j, 16 + group * 16 + (slot)); } while (0)
-            SFT(0);
-            const int valid_cols = page_ok[j] ? min(kTileN, my_extent - j * kTileN) : 0;   // <= 0: nothing visible
-#ifdef FPKV_EXP_SKIP_SOFTMAX                               // timing experiment only: tensor + copy pipeline alone
-            tc_fence_before(); __syncwarp();
-            if (lane == 0) { bar_arrive(p_half0 + 8 * group); bar_arrive(p_full0 + 8 * group); }
-            continue;
-#endif
-            // the whole score row of this thread: four loads in flight, one wait
-            uint32_t sv[4][32];
+        uint32_t xslot = 0;                                // exchange buffer parity
+        // (the two warps of a row quarter meet at their own named barrier, 1 + quarter)
+        auto exchange_max = [&](float mine) {              // maximum over the two threads of a row
+            float* buf = xch + (xslot & 1u) * 256;
+            buf[colhalf * 128 + row] = mine;
+            asm volatile("bar.sync %0, 64;" ::"r"(1 + quarter) : "memory");
+            const float other = buf[(1 - colhalf) * 128 + row];
+            ++xslot;
+            return fmaxf(mine, other);
+        };
+        for (int j = 0; j < n_tiles; ++j) {
+            const int valid_row = page_ok[j] ? min(kTileN, my_extent - j * kTileN) : 0;   // visible keys of this row in the tile
+            const int valid_cols = valid_row - colhalf * 64;                               // ... among this thread's 64 columns
+            const bool full = __all_sync(0xffffffffu, valid_cols >= 64);
+            for (int h = 0; h < heads; ++h) {
+                const uint32_t ts = tmem + h * kTileN + lane_base;          // S, then P, of this head
+                const uint32_t to = tmem + 256 + h * kTileN + lane_base + colhalf * 64;   // this thread's half of the O row
+                // s_full also tells that P.V of tile j-1 is complete: O is stable and the P columns are free.
+                // A wait that runs out does not leave the loop: every thread must reach the named barrier below.
+                if (alive && !bar_wait(s_full0 + 8 * h, j & 1u, abort_flag)) alive = false;
+                tc_fence_after();
+                uint32_t sv[2][32];
+                tmem_ld32_nowait(ts + colhalf * 64, sv[0]);
+                tmem_ld32_nowait(ts + colhalf * 64 + 32, sv[1]);
+                tmem_wait_ld();
+                float mx;
+                if (full) {
+                    float m2[2];
 #pragma unroll
-            for (int c4 = 0; c4 < 4; ++c4) tmem_ld32_nowait(ts + c4 * 32, sv[c4]);
-            tmem_wait_ld();
-            SFT(1);
-            // Most tiles are fully visible to every row of the warp; they take a path without a per-element mask.
-            const bool full = __all_sync(0xffffffffu, valid_cols >= kTileN);
-            float mx;
-            if (full) {
-                float m4[4];
+                    for (int c2 = 0; c2 < 2; ++c2) {
+                        m2[c2] = max3f(__uint_as_float(sv[c2][0]), __uint_as_float(sv[c2][1]), __uint_as_float(sv[c2][2]));
 #pragma unroll
-                for (int c4 = 0; c4 < 4; ++c4) {
-                    m4[c4] = max3f(__uint_as_float(sv[c4][0]), __uint_as_float(sv[c4][1]), __uint_as_float(sv[c4][2]));
-#pragma unroll
-                    for (int c = 3; c + 1 < 32; c += 2)
-                        m4[c4] = max3f(m4[c4], __uint_as_float(sv[c4][c]), __uint_as_float(sv[c4][c + 1]));
-                    m4[c4] = fmaxf(m4[c4], __uint_as_float(sv[c4][31]));
-                }
-                mx = fmaxf(fmaxf(m4[0], m4[1]), fmaxf(m4[2], m4[3]));
-            } else {
-                mx = -INFINITY;
-#pragma unroll
-                for (int c4 = 0; c4 < 4; ++c4)
-#pragma unroll
-                    for (int c = 0; c < 32; ++c) if (c4 * 32 + c < valid_cols) mx = fmaxf(mx, __uint_as_float(sv[c4][c]));
-            }
-            mx *= prm.scale_log2;                          // scale > 0: max commutes with it
-            // raise the reference maximum only when this tile is far above it
-            const bool raise = mx > m_ref + kRescaleThreshold || (m_ref == -INFINITY && mx > -INFINITY);
-            if (__any_sync(0xffffffffu, raise)) {          // tensor-memory access is a whole-warp operation
-                const float m_new = raise ? mx : m_ref;
-                const float alpha = (m_ref == -INFINITY) ? 0.f : exp2f(m_ref - m_new);
-                if (j > 0) {                               // rescale this row of O in tensor memory
-#pragma unroll 1
-                    for (int c4 = 0; c4 < 4; ++c4) {
-                        tmem_ld32(to + c4 * 32, v);
-#pragma unroll
-                        for (int c = 0; c < 32; ++c) v[c] = __float_as_uint(__uint_as_float(v[c]) * alpha);
-                        tmem_st32(to + c4 * 32, v);
+                        for (int c = 3; c + 1 < 32; c += 2)
+                            m2[c2] = max3f(m2[c2], __uint_as_float(sv[c2][c]), __uint_as_float(sv[c2][c + 1]));
+                        m2[c2] = fmaxf(m2[c2], __uint_as_float(sv[c2][31]));
                     }
+                    mx = fmaxf(m2[0], m2[1]);
+                } else {
+                    mx = -INFINITY;
+#pragma unroll
+                    for (int c2 = 0; c2 < 2; ++c2)
+#pragma unroll
+                        for (int c = 0; c < 32; ++c) if (c2 * 32 + c < valid_cols) mx = fmaxf(mx, __uint_as_float(sv[c2][c]));
                 }
-                l *= alpha;
-                m_ref = m_new;
-            }
-            // Probabilities, packed two per 32-bit column, written over the scores of this row (all in registers
-            // by now): columns [0,64) of the region become P.  The exponential unit (16 results per clock per
-            // SM) bounds this phase.  The first 32 packed columns (keys 0-63) are handed to the MMA warp as soon
-            // as they are stored, so that half of P.V runs under the second half's exponentials.
-            float r4[4] = {0.f, 0.f, 0.f, 0.f};
-            const float neg_m = (m_ref == -INFINITY) ? 0.f : -m_ref;
-            SFT(2);
-            // The two heads take turns at the exponentials: a head that has the unit to itself finishes in
-            // half the time, and meanwhile the other head's MMAs run.  Left alone, the two heads drift into
-            // step, exponentiate together at half speed each and then queue on the tensor pipe together.
-            // Head 1 starts tile j when head 0 has issued the exponentials of tile j, head 0 starts tile j when
-            // head 1 has issued those of tile j - 1; the turn passes before the stores and barrier traffic that
-            // end a tile, so the unit does not idle through them.
-#ifndef FPKV_EXP_NO_TURNS
-            if (heads == 2) {
-                if (group == 1) { if (!bar_wait(turn0, j & 1u, abort_flag)) { alive = false; break; } }
-                else if (j > 0) { if (!bar_wait(turn0 + 8, (j - 1) & 1u, abort_flag)) { alive = false; break; } }
-            }
-#endif
-            SFT(3);
-            auto probabilities = [&](auto full_tag) {
-                constexpr bool kFull = decltype(full_tag)::value;
+                // after this barrier both threads of the row hold all their scores in registers, so the packed
+                // P columns may overwrite either thread's score columns
+                mx = exchange_max(mx) * prm.scale_log2;    // scale > 0: max commutes with it
+                // raise the reference maximum only when this tile is far above it (both threads of a row decide alike)
+                const bool raise = mx > m_ref[h] + kRescaleThreshold || (m_ref[h] == -INFINITY && mx > -INFINITY);
+                if (__any_sync(0xffffffffu, raise)) {      // tensor-memory access is a whole-warp operation
+                    const float m_new = raise ? mx : m_ref[h];
+                    const float alpha = (m_ref[h] == -INFINITY) ? 0.f : exp2f(m_ref[h] - m_new);
+                    if (j > 0) {                           // rescale this thread's half of the O row in tensor memory
+#pragma unroll 1
+                        for (int c2 = 0; c2 < 2; ++c2) {
+                            tmem_ld32(to + c2 * 32, v);
 #pragma unroll
-                for (int half = 0; half < 2; ++half) {     // 64 scores -> 32 packed columns per store
-                    uint32_t pk[32];
+                            for (int c = 0; c < 32; ++c) v[c] = __float_as_uint(__uint_as_float(v[c]) * alpha);
+                            tmem_st32(to + c2 * 32, v);
+                        }
+                    }
+                    l[h] *= alpha;
+                    m_ref[h] = m_new;
+                }
+                // probabilities, packed two per 32-bit column: this thread's 64 scores become packed columns
+                // [colhalf * 32, colhalf * 32 + 32) of the region
+                float r4[4] = {0.f, 0.f, 0.f, 0.f};
+                const float neg_m = (m_ref[h] == -INFINITY) ? 0.f : -m_ref[h];
+                uint32_t pk[32];
+                auto probabilities = [&](auto full_tag) {
+                    constexpr bool kFull = decltype(full_tag)::value;
 #pragma unroll
-                    for (int sub = 0; sub < 2; ++sub) {
-                        const int c4 = half * 2 + sub;
+                    for (int c2 = 0; c2 < 2; ++c2) {
 #pragma unroll
                         for (int c = 0; c < 32; c += 2) {
-                            float p0 = ex2(fmaf(__uint_as_float(sv[c4][c]), prm.scale_log2, neg_m));
-                            float p1 = ex2(fmaf(__uint_as_float(sv[c4][c + 1]), prm.scale_log2, neg_m));
+                            float p0 = ex2(fmaf(__uint_as_float(sv[c2][c]), prm.scale_log2, neg_m));
+                            float p1 = ex2(fmaf(__uint_as_float(sv[c2][c + 1]), prm.scale_log2, neg_m));
                             if (!kFull) {
-                                if (c4 * 32 + c >= valid_cols) p0 = 0.f;
-                                if (c4 * 32 + c + 1 >= valid_cols) p1 = 0.f;
+                                if (c2 * 32 + c >= valid_cols) p0 = 0.f;
+                                if (c2 * 32 + c + 1 >= valid_cols) p1 = 0.f;
                             }
                             r4[(c >> 1) & 1] += p0;
                             r4[2 + ((c >> 1) & 1)] += p1;
-                            pk[sub * 16 + c / 2] = pack2<T>(p0, p1);
+                            pk[c2 * 16 + c / 2] = pack2<T>(p0, p1);
                         }
                     }
-                    SFT(4 + half * 2);
-                    if (half == 1 && heads == 2) { __syncwarp(); if (lane == 0) bar_arrive(turn0 + 8 * group); }
-                    tmem_st32_nowait(ts + half * 32, pk);
-                    asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
-                    if (half == 0) {
-                        tc_fence_before();
-                        __syncwarp();
-                        if (lane == 0) bar_arrive(p_half0 + 8 * group);
-                    }
-                    SFT(5 + half * 2);
-                }
-            };
-            if (full) probabilities(std::true_type{}); else probabilities(std::false_type{});
-            const float rsum = (r4[0] + r4[1]) + (r4[2] + r4[3]);
-            l += rsum;
-            tc_fence_before();
-            __syncwarp();
-            if (lane == 0) bar_arrive(p_full0 + 8 * group);
-            SFT(8);
-#undef SFT
+                };
+                if (full) probabilities(std::true_type{}); else probabilities(std::false_type{});
+                tmem_st32_nowait(ts + colhalf * 32, pk);
+                l[h] += (r4[0] + r4[1]) + (r4[2] + r4[3]);
+                asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
+                tc_fence_before();
+                __syncwarp();
+                if (lane == 0) bar_arrive(p_full0 + 8 * h);
+            }
         }
         // ---- epilogue: O / l -> out, lse --------------------------------------
+        // Each thread holds 64 of the 128 output values of its row.  Storing them straight from registers
+        // would touch 32 different lines per warp instruction; the two warps of a row quarter stage their 32
+        // rows in the (now idle) query tile of the head, 16-byte chunks XOR-swizzled by row so that neither
+        // side has bank conflicts, and write them out two whole rows per instruction.
         T* out = reinterpret_cast<T*>(prm.out);
-        const int tok = t0 + row;
-        if (n_tiles > 0 && alive) {
-            if (!bar_wait(all_done0 + 8 * group, 0, abort_flag)) alive = false;
-            tc_fence_after();
-        }
-        if (alive) {
-            const float inv = l > 0.f ? 1.f / l : 0.f;
-            const float lse_nat = l > 0.f ? (m_ref + log2f(l)) * kLn2 : -INFINITY;
+        for (int h = 0; h < heads; ++h) {
+            const int hq = hq0 + h;
+            const uint32_t to = tmem + 256 + h * kTileN + lane_base + colhalf * 64;
+            if (n_tiles > 0) {
+                if (alive && !bar_wait(all_done0 + 8 * h, 0, abort_flag)) alive = false;
+                tc_fence_after();
+            }
+            // row sum over both threads of the row
+            float* buf = xch + (xslot & 1u) * 256;
+            buf[colhalf * 128 + row] = l[h];
+            asm volatile("bar.sync %0, 64;" ::"r"(1 + quarter) : "memory");
+            const float lsum = l[h] + buf[(1 - colhalf) * 128 + row];
+            ++xslot;
+            const float inv = lsum > 0.f ? 1.f / lsum : 0.f;
+            const float lse_nat = lsum > 0.f ? (m_ref[h] + log2f(lsum)) * kLn2 : -INFINITY;
             const bool gate_on = prm.epi.sinks != nullptr;
             const float gate = sink_gate(prm.epi, hq, lse_nat);
-            // Each thread owns one 256-byte output row; storing it straight from registers would touch 32
-            // different lines per warp instruction.  The warp stages its 32 rows in the (now idle) query tile
-            // of its head, 16-byte chunks XOR-swizzled by row so that neither side has bank conflicts, and
-            // writes them out two whole rows per instruction.
-            uint8_t* slab = q_s + group * kTileBytes + (warp % 4) * (32 * 256);
+            uint8_t* slab = q_s + h * kTileBytes + quarter * (32 * 256);
 #pragma unroll 1
-            for (int c4 = 0; c4 < 4; ++c4) {
-                if (n_tiles > 0) tmem_ld32(to + c4 * 32, v);
+            for (int c2 = 0; c2 < 2; ++c2) {
+                if (n_tiles > 0) tmem_ld32(to + c2 * 32, v);
 #pragma unroll
                 for (int c = 0; c < 32; c += 8) {
                     uint32_t w[4];
 #pragma unroll
                     for (int e = 0; e < 4; ++e) {
-                        const float a = (n_tiles > 0 && l > 0.f) ? __uint_as_float(v[c + 2 * e]) * inv : 0.f;
-                        const float b = (n_tiles > 0 && l > 0.f) ? __uint_as_float(v[c + 2 * e + 1]) * inv : 0.f;
+                        const float a = (n_tiles > 0 && lsum > 0.f) ? __uint_as_float(v[c + 2 * e]) * inv : 0.f;
+                        const float b = (n_tiles > 0 && lsum > 0.f) ? __uint_as_float(v[c + 2 * e + 1]) * inv : 0.f;
                         const T ra = gated_out<T>(a, gate, gate_on), rb = gated_out<T>(b, gate, gate_on);
                         w[e] = (uint32_t)*reinterpret_cast<const uint16_t*>(&ra) | ((uint32_t)*reinterpret_cast<const uint16_t*>(&rb) << 16);
                     }
-                    const int chunk = c4 * 4 + c / 8;
+                    const int chunk = colhalf * 8 + c2 * 4 + c / 8;
                     *reinterpret_cast<uint4*>(slab + lane * 256 + ((chunk ^ (lane & 15)) * 16)) = make_uint4(w[0], w[1], w[2], w[3]);
                 }
             }
-            __syncwarp();
+            asm volatile("bar.sync %0, 64;" ::"r"(1 + quarter) : "memory");         // both column halves of every row are staged
 #pragma unroll 4
-            for (int i = 0; i < 16; ++i) {
-                const int rr = 2 * i + (lane >> 4), chunk = lane & 15;
+            for (int i = 0; i < 8; ++i) {                  // this warp writes out 16 of the quarter's 32 rows
+                const int rr = colhalf * 16 + 2 * i + (lane >> 4), chunk = lane & 15;
                 const uint4 val = *reinterpret_cast<const uint4*>(slab + rr * 256 + ((chunk ^ (rr & 15)) * 16));
-                const int tk = t0 + (warp % 4) * 32 + rr;
+                const int tk = t0 + quarter * 32 + rr;
                 if (tk < prm.L) {
                     T* dst = out + (prm.epi.token_major ? ((size_t)tk * prm.Hq + hq) : ((size_t)hq * prm.L + tk)) * kHeadDim + chunk * 8;
                     *reinterpret_cast<uint4*>(dst) = val;
                 }
             }
-            if (tok < prm.L) prm.lse[(size_t)hq * prm.L + tok] = lse_nat;
+            if (colhalf == 0 && t0 + row < prm.L) prm.lse[(size_t)hq * prm.L + t0 + row] = lse_nat;
         }
     }
     if (!alive && lane == 0) {
@@ -645,7 +617,7 @@ EncodeFn encoder() {
     return fn;
 }
 
-constexpr int kPrefillSmem = 1024 + (2 + 2 * kStages) * kTileBytes + 24 * 8 + 16 * 4 + kMaxKeyTiles * 5 + 64;   // Q x2, K and V x kStages
+constexpr int kPrefillSmem = 1024 + (2 + 2 * kStages) * kTileBytes + 24 * 8 + 16 * 4 + kMaxKeyTiles * 5 + 2 * 2 * 128 * 4 + 64;   // Q x2, K and V x kStages
 
 }  // namespace
 
