@@ -52,6 +52,10 @@ constexpr int kMaxKeyTiles = 512;                      // 65 536 keys per sequen
 constexpr uint32_t kSpin = 1u << 22;
 constexpr uint32_t kTmemCols = 512;                    // S/P head 0, S/P head 1, O head 0, O head 1: 128 columns each
 constexpr float kRescaleThreshold = 8.f;
+#ifndef FPKV_POLY_EVERY
+#define FPKV_POLY_EVERY 4
+#endif
+constexpr int kPolyEvery = FPKV_POLY_EVERY;            // one pair in this many takes the polynomial 2^x (0x7fffffff: none)
 
 __device__ __forceinline__ uint32_t s32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
 __device__ __forceinline__ void bar_init(uint32_t bar, uint32_t count) {
@@ -205,6 +209,50 @@ __device__ unsigned long long g_cta_sums[8];               // all CTAs: [0] entr
 __device__ __forceinline__ unsigned long long gtime_ns() {
     unsigned long long t; asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t)); return t;
 }
+#endif
+// 2^x for a pair of arguments on the FMA and integer pipes instead of the exponential unit, which is the narrow
+// resource of the softmax phase (16 results per clock per SM): round to the nearest integer with the
+// 1.5 * 2^23 trick, a degree-3 polynomial on the remainder in [-0.5, 0.5] (maximum relative error 7.5e-5, far
+// below the 16-bit rounding of the probabilities), the integer added into the exponent bits.  Arguments
+// are clamped below at -126; they never exceed 8 here.  Packed f32x2 arithmetic halves the instruction count.
+struct F2 { float x, y; };
+__device__ __forceinline__ F2 fma2(F2 a, F2 b, F2 c) {
+    F2 d;
+    asm("{\n\t.reg .b64 ra, rb, rc, rd;\n\tmov.b64 ra, {%2, %3};\n\tmov.b64 rb, {%4, %5};\n\tmov.b64 rc, {%6, %7};\n\t"
+        "fma.rn.f32x2 rd, ra, rb, rc;\n\tmov.b64 {%0, %1}, rd;\n\t}"
+        : "=f"(d.x), "=f"(d.y) : "f"(a.x), "f"(a.y), "f"(b.x), "f"(b.y), "f"(c.x), "f"(c.y));
+    return d;
+}
+__device__ __forceinline__ F2 add2(F2 a, F2 b) {
+    F2 d;
+    asm("{\n\t.reg .b64 ra, rb, rd;\n\tmov.b64 ra, {%2, %3};\n\tmov.b64 rb, {%4, %5};\n\tadd.rn.f32x2 rd, ra, rb;\n\tmov.b64 {%0, %1}, rd;\n\t}"
+        : "=f"(d.x), "=f"(d.y) : "f"(a.x), "f"(a.y), "f"(b.x), "f"(b.y));
+    return d;
+}
+__device__ __forceinline__ F2 ex2_poly2(F2 x) {
+    x.x = fmaxf(x.x, -126.f); x.y = fmaxf(x.y, -126.f);
+    const F2 fl = add2(x, F2{12582912.f, 12582912.f});
+    const F2 n = add2(fl, F2{-12582912.f, -12582912.f});
+    const F2 f = add2(x, F2{-n.x, -n.y});
+    F2 p = fma2(f, F2{0.05517164617776871f, 0.05517164617776871f}, F2{0.2426111251115799f, 0.2426111251115799f});
+    p = fma2(p, f, F2{0.6932609677314758f, 0.6932609677314758f});
+    p = fma2(p, f, F2{0.9999280571937561f, 0.9999280571937561f});
+    F2 r;
+    r.x = __int_as_float(__float_as_int(p.x) + (__float_as_int(fl.x) << 23));
+    r.y = __int_as_float(__float_as_int(p.y) + (__float_as_int(fl.y) << 23));
+    return r;
+}
+
+#ifdef FPKV_PHASES
+// Development aid: cycles per softmax phase, summed over all tiles of warp 0 of every CTA.
+__device__ unsigned long long g_phase_sums[16];
+#define PH_DECL long long ph_t = clock64(), ph_acc[8] = {0, 0, 0, 0, 0, 0, 0, 0}
+#define PH(i) do { const long long ph_n = clock64(); ph_acc[i] += ph_n - ph_t; ph_t = ph_n; } while (0)
+#define PH_DUMP do { if (tid == 0) { for (int i = 0; i < 8; ++i) atomicAdd(&g_phase_sums[i], (unsigned long long)ph_acc[i]); atomicAdd(&g_phase_sums[8], (unsigned long long)(n_tiles * heads)); } } while (0)
+#else
+#define PH_DECL do { } while (0)
+#define PH(i) do { } while (0)
+#define PH_DUMP do { } while (0)
 #endif
 #ifdef FPKV_FINE
 // Development aid: cycle stamps of one CTA for two consecutive key tiles, [tile - 3][slot].
@@ -436,6 +484,7 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_consta
             ++xslot;
             return fmaxf(mine, other);
         };
+        PH_DECL;
         for (int j = 0; j < n_tiles; ++j) {
             const int valid_row = page_ok[j] ? min(kTileN, my_extent - j * kTileN) : 0;   // visible keys of this row in the tile
             const int valid_cols = valid_row - colhalf * 64;                               // ... among this thread's 64 columns
@@ -445,12 +494,15 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_consta
                 const uint32_t to = tmem + 256 + h * kTileN + lane_base + colhalf * 64;   // this thread's half of the O row
                 // s_full also tells that P.V of tile j-1 is complete: O is stable and the P columns are free.
                 // A wait that runs out does not leave the loop: every thread must reach the named barrier below.
+                PH(0);                                     // loop overhead, arrive of the previous tile
                 if (alive && !bar_wait(s_full0 + 8 * h, j & 1u, abort_flag)) alive = false;
                 tc_fence_after();
+                if (j == 0) PH(7); else PH(1);             // wait for the scores (first tile apart: it waits for the first copies)
                 uint32_t sv[2][32];
                 tmem_ld32_nowait(ts + colhalf * 64, sv[0]);
                 tmem_ld32_nowait(ts + colhalf * 64 + 32, sv[1]);
                 tmem_wait_ld();
+                PH(2);                                     // tensor-memory load
                 float mx;
                 if (full) {
                     float m2[2];
@@ -472,7 +524,9 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_consta
                 }
                 // after this barrier both threads of the row hold all their scores in registers, so the packed
                 // P columns may overwrite either thread's score columns
+                PH(3);                                     // local maximum
                 mx = exchange_max(mx) * prm.scale_log2;    // scale > 0: max commutes with it
+                PH(4);                                     // exchange with the partner thread
                 // raise the reference maximum only when this tile is far above it (both threads of a row decide alike)
                 const bool raise = mx > m_ref[h] + kRescaleThreshold || (m_ref[h] == -INFINITY && mx > -INFINITY);
                 if (__any_sync(0xffffffffu, raise)) {      // tensor-memory access is a whole-warp operation
@@ -501,8 +555,15 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_consta
                     for (int c2 = 0; c2 < 2; ++c2) {
 #pragma unroll
                         for (int c = 0; c < 32; c += 2) {
-                            float p0 = ex2(fmaf(__uint_as_float(sv[c2][c]), prm.scale_log2, neg_m));
-                            float p1 = ex2(fmaf(__uint_as_float(sv[c2][c + 1]), prm.scale_log2, neg_m));
+                            float p0, p1;
+                            if ((c >> 1) % kPolyEvery == kPolyEvery - 1) {     // every fourth pair off the exponential unit
+                                const F2 p = ex2_poly2(fma2(F2{__uint_as_float(sv[c2][c]), __uint_as_float(sv[c2][c + 1])},
+                                                            F2{prm.scale_log2, prm.scale_log2}, F2{neg_m, neg_m}));
+                                p0 = p.x; p1 = p.y;
+                            } else {
+                                p0 = ex2(fmaf(__uint_as_float(sv[c2][c]), prm.scale_log2, neg_m));
+                                p1 = ex2(fmaf(__uint_as_float(sv[c2][c + 1]), prm.scale_log2, neg_m));
+                            }
                             if (!kFull) {
                                 if (c2 * 32 + c >= valid_cols) p0 = 0.f;
                                 if (c2 * 32 + c + 1 >= valid_cols) p1 = 0.f;
@@ -514,14 +575,17 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_consta
                     }
                 };
                 if (full) probabilities(std::true_type{}); else probabilities(std::false_type{});
+                PH(5);                                     // raise check and exponentials
                 tmem_st32_nowait(ts + colhalf * 32, pk);
                 l[h] += (r4[0] + r4[1]) + (r4[2] + r4[3]);
                 asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
                 tc_fence_before();
                 __syncwarp();
                 if (lane == 0) bar_arrive(p_full0 + 8 * h);
+                PH(6);                                     // store, wait, fence, arrive
             }
         }
+        PH_DUMP;
         // ---- epilogue: O / l -> out, lse --------------------------------------
         // Each thread holds 64 of the 128 output values of its row.  Storing them straight from registers
         // would touch 32 different lines per warp instruction; the two warps of a row quarter stage their 32
@@ -625,6 +689,12 @@ constexpr int kPrefillSmem = 1024 + (2 + 2 * kStages) * kTileBytes + 24 * 8 + 16
 extern "C" __attribute__((visibility("default"))) int fpkv_debug_cta_sums(unsigned long long* host_out, int reset) {
     if (reset) { unsigned long long z[8] = {0}; return (int)cudaMemcpyToSymbol(g_cta_sums, z, sizeof(z)); }
     return (int)cudaMemcpyFromSymbol(host_out, g_cta_sums, sizeof(unsigned long long) * 8);
+}
+#endif
+#ifdef FPKV_PHASES
+extern "C" __attribute__((visibility("default"))) int fpkv_debug_phases(unsigned long long* host_out, int reset) {
+    if (reset) { unsigned long long z[16] = {0}; return (int)cudaMemcpyToSymbol(g_phase_sums, z, sizeof(z)); }
+    return (int)cudaMemcpyFromSymbol(host_out, g_phase_sums, sizeof(unsigned long long) * 16);
 }
 #endif
 #ifdef FPKV_FINE
