@@ -20,19 +20,34 @@
 //
 // One CTA = one 128-row query tile of a PAIR of query heads that share a stored
 // head (a single head when the GQA ratio is odd): the K/V tile staged in shared
-// memory feeds both heads, which halves the L2 traffic per FLOP (a one-head
-// CTA was measured L2-bound at 25 % of tensor peak).  Warps 0-3 and 4-7 are the
-// two heads' softmax groups (thread i owns query row i = TMEM lane i); warp 8
-// is the TMA producer; warp 9 issues the MMAs:
+// memory feeds both heads, which halves the L2 traffic per FLOP.  Per key tile
+// and head:
 //     S = Q K^T    128x128x128, A = Q (shared, K-major), B = K tile (shared, K-major) -> TMEM
 //     O += P V     128x128x128, A = P (TMEM, written in place over S), B = V tile (shared, MN-major) -> TMEM
-// The heads alternate on the tensor pipe: while one head's softmax runs, the
-// other head's P.V and next Q.K^T execute.  The running maximum is only raised
-// when a tile exceeds it by more than 2^8 (probabilities stay below 256, exact
-// in fp32 and harmless in bf16), so O in TMEM is rarely rescaled.
+// Tensor memory holds S/P and O of both heads (4 x 128 columns = all 512), so
+// each head is one dependent chain  S -> softmax -> P.V -> next S  and only two
+// chains are in flight.  Two resources bound a (tile, head pair) at 2048 clocks
+// each: the tensor pipe (32 MMAs of 64 clocks) and the exponential unit (2 x
+// 128 x 128 results at 16 per clock per SM); the kernel is about keeping both
+// busy at once.
+//   * Warps 0-7 do the softmax, all eight on ONE head's tile at a time, two
+//     threads per query row (warps w and w + 4 reach the same 32 TMEM lanes and
+//     take 64 key columns each).  Two warps per scheduler keep the exponential
+//     unit saturated; a quarter of the exponentials run as a polynomial on the
+//     FMA pipe instead.  While they work on one head, the other head's MMAs run.
+//   * Warp 8 is the TMA producer (2-stage K and V rings).
+//   * Warps 9 and 10 issue the MMAs, one warp per head: the tensor pipe takes the
+//     MMAs of a thread one after the other and idles through whatever else that
+//     thread does (a barrier wait costs it ~30-100 clocks), so each head gets its
+//     own issuer and waits for operand tiles before it waits for P.
+// The running maximum is only raised when a tile exceeds it by more than 2^8
+// (probabilities stay below 256, exact in fp32 and harmless in bf16), so O in
+// TMEM is rarely rescaled.  The output tile is staged through the idle query
+// buffer so that rows leave in whole lines.
 // Every wait is a bounded mbarrier wait; on expiry the CTA raises
-// FPKV_STATUS_TIMEOUT, every role leaves its loop, TMEM is freed and the
-// kernel returns.
+// FPKV_STATUS_TIMEOUT, the MMA and copy warps leave their loops, the softmax
+// warps run theirs to the end without waiting (they meet at named barriers),
+// TMEM is freed and the kernel returns.
 
 #include <cuda.h>
 #include <type_traits>
@@ -45,7 +60,7 @@ constexpr int kTileM = 128, kTileN = 128, kHeadDim = 128, kPage = 128;
 constexpr int kTileBytes = 128 * 128 * 2;              // any 128 x 128 16-bit tile
 constexpr int kHalfBytes = kTileBytes / 2;             // 64 columns (128 bytes) x 128 rows
 constexpr int kStages = 2;
-constexpr int kSoftmaxWarps = 4;                       // per head; two groups (warps 0-3, 4-7) for a head pair
+constexpr int kSoftmaxWarps = 4;                       // per key-column half: warps 0-3 take columns [0,64), warps 4-7 [64,128)
 constexpr int kLoadWarp = 8, kMmaWarp = 9;              // warps 9 and 10 issue the MMAs of head 0 and head 1 of the pair
 constexpr int kPrefillThreads = 12 * 32;               // warp 11 idles: registers are granted per four warps anyway
 constexpr int kMaxKeyTiles = 512;                      // 65 536 keys per sequence
