@@ -14,7 +14,7 @@ import sys
 HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 OUT = os.path.join(HERE, "fpkv", "libfpkv.so")
-SOURCES = ["api.cu", "append.cu", "decode_portable.cu", "decode_tma.cu", "decode_static.cu", "prefill_tc.cu", "tables.cu"]
+SOURCES = ["api.cu", "append.cu", "pre_append.cu", "decode_portable.cu", "decode_tma.cu", "decode_static.cu", "prefill_tc.cu", "tables.cu"]
 NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-O3", "-std=c++17", "-lineinfo",
               "--use_fast_math", "-Xcompiler", "-fPIC,-O3,-fvisibility=hidden", "-shared"]
 

@@ -121,6 +121,32 @@ int fpkv_append_packed(const fpkv_pool* pool, int32_t layer, const int64_t* batc
                          v_stride_h, L, /*decode_mode=*/false, status, static_cast<cudaStream_t>(stream));
 }
 
+int fpkv_pre_append(const fpkv_pool* pool, int32_t layer, const void* qkv, int64_t qkv_stride_t, int32_t n_q_heads,
+                    int32_t n_kv_heads, const float* freqs_cis, const float* freqs_cis_2d, const int64_t* batch_idx,
+                    const void* input_pos, int32_t pos_type, int32_t n_tok, int32_t decode_mode, void* q_out,
+                    int64_t q_stride_h, int64_t q_stride_t, float eps, int32_t* status, void* stream)
+{
+    PoolView pv;
+    int rc = make_view(pool, layer, &pv);
+    if (rc) return rc;
+    if (n_tok < 0 || (pos_type != FPKV_I32 && pos_type != FPKV_I64) || n_q_heads <= 0 || n_kv_heads <= 0) return FPKV_EINVAL;
+    if (n_q_heads % n_kv_heads) return FPKV_ESHAPE;
+    if (pv.H != n_q_heads && pv.H != n_kv_heads) return FPKV_ESHAPE;     // expanded or compact pool, nothing else
+    if (pv.D != 64 && pv.D != 128) return FPKV_ESHAPE;
+    if (qkv_stride_t < (int64_t)(n_q_heads + 2 * n_kv_heads) * pv.D) return FPKV_ESHAPE;
+    if (!(eps >= 0.f)) return FPKV_EINVAL;
+    if (n_tok == 0) return FPKV_OK;
+    if (qkv == nullptr || freqs_cis == nullptr || batch_idx == nullptr || input_pos == nullptr || q_out == nullptr)
+        return FPKV_EINVAL;
+    if ((rc = check_rows(qkv, qkv_stride_t, qkv_stride_t, pv.esize))) return rc;
+    if ((rc = check_rows(q_out, q_stride_h, q_stride_t, pv.esize))) return rc;
+    if ((reinterpret_cast<uintptr_t>(freqs_cis) & 7u) || (reinterpret_cast<uintptr_t>(freqs_cis_2d) & 7u)) return FPKV_EALIGN;
+    if ((rc = check_arch())) return rc;
+    return launch_pre_append(pv, layer, qkv, qkv_stride_t, n_q_heads, n_kv_heads, freqs_cis, freqs_cis_2d, batch_idx,
+                             input_pos, pos_type, n_tok, decode_mode != 0, q_out, q_stride_h, q_stride_t, eps, status,
+                             static_cast<cudaStream_t>(stream));
+}
+
 int fpkv_gather(const fpkv_pool* pool, int32_t layer, int32_t slot, int32_t n_tokens, void* k_out, void* v_out,
                 int32_t* status, void* stream)
 {

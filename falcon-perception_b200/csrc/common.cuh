@@ -78,6 +78,10 @@ int launch_append(const PoolView& pv, int layer, const int64_t* batch_idx, const
                   const void* v, long long v_stride_tok, long long v_stride_h,
                   int n_tok, bool decode_mode, int32_t* status, cudaStream_t stream);
 
+int launch_pre_append(const PoolView& pv, int layer, const void* qkv, long long qkv_stride_t, int Hq, int Hkv,
+                      const float* freqs_cis, const float* freqs_cis_2d, const int64_t* batch_idx, const void* pos,
+                      int pos_type, int n_tok, bool decode_mode, void* q_out, long long q_stride_h,
+                      long long q_stride_t, float eps, int32_t* status, cudaStream_t stream);
 int launch_gather(const PoolView& pv, int layer, int slot, int n_tokens, void* k_out, void* v_out,
                   int32_t* status, cudaStream_t stream);
 

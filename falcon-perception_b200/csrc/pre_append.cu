@@ -1,0 +1,192 @@
+// Per-head RMS norm, rotary embedding and K/V append in one pass over the QKV
+// projection: what Attention._pre_attention does behind the projection
+// (falcon_perception/model.py:107-120, falcon_perception/rope.py:30-104)
+// followed by insert_kv (model.py:150-155), without the intermediate tensors
+// (normalised q/k, GQA-expanded k/v, rotated q/k, permuted copies) and the
+// separate append.
+//
+// Eight lanes handle one head row of one token: a query head (normalise, rotate,
+// write to the query output), a stored key head (normalise, rotate, write into
+// the page pool) or a stored value head (copy into the pool); a warp has four
+// rows in flight.  A lane holds D / 8 consecutive elements (16-byte accesses),
+// i.e. whole rotation pairs (x[2i], x[2i+1]).
+//
+// Arithmetic follows the reference step by step so that results agree to the
+// last bit wherever the order of the sum of squares does not matter: fp32
+// throughout, x * rsqrt(mean(x^2) + eps) rounded to the storage type, then
+// each half of the head rotated in fp32 (products and sums rounded separately,
+// no fused multiply-add) and rounded again.  The first half uses the 1-D table
+// freqs_cis[t, i], the second half the 2-D table freqs_cis_2d[t, head, i] of
+// the QUERY head when one is given, and is left as normalised otherwise.
+//
+// Pool layouts: with n_heads == n_q_heads the pool holds the reference's
+// expanded heads (stored head h = key head h / n_rep rotated with query head
+// h's 2-D table); with n_heads == n_kv_heads it holds each key head once,
+// rotated with the table of the first query head of its group, which equals the
+// reference whenever the 2-D frequencies agree within a group or no 2-D table is
+// in use.  HBM/latency-bound byte work: no shared memory, no tensor cores.
+
+#include "common.cuh"
+
+namespace fpkv {
+namespace {
+
+struct PreAppendParams {
+    char* pool_layer; size_t plane_bytes; int H_out;
+    const int64_t* page_table; int n_pages, max_batch, P;
+    const char* qkv; long long qkv_row_bytes;
+    int Hq, Hkv;
+    const float2* freqs; const float2* freqs2d;
+    const int64_t* batch_idx; const void* pos;
+    int n_tok; int decode_mode;
+    char* q_out; long long q_head_bytes, q_tok_bytes;
+    float eps; int32_t* status;
+};
+
+template <typename T> __device__ __forceinline__ float to_f32(T v);
+template <> __device__ __forceinline__ float to_f32<float>(float v) { return v; }
+template <> __device__ __forceinline__ float to_f32<__nv_bfloat16>(__nv_bfloat16 v) { return __bfloat162float(v); }
+template <> __device__ __forceinline__ float to_f32<__half>(__half v) { return __half2float(v); }
+template <typename T> __device__ __forceinline__ T from_f32(float v);
+template <> __device__ __forceinline__ float from_f32<float>(float v) { return v; }
+template <> __device__ __forceinline__ __nv_bfloat16 from_f32<__nv_bfloat16>(float v) { return __float2bfloat16_rn(v); }
+template <> __device__ __forceinline__ __half from_f32<__half>(float v) { return __float2half_rn(v); }
+
+template <typename T, int E> struct alignas(16) Row { T v[E]; };   // E elements of one lane, moved as 16-byte vectors
+
+constexpr int kLanesPerRow = 8;
+
+template <typename T, int D, typename PosT>
+__global__ void __launch_bounds__(256)
+pre_append_kernel(const PreAppendParams prm)
+{
+    constexpr int E = D / kLanesPerRow;                    // elements per lane: 8 or 16, whole rotation pairs
+    using RowT = Row<T, E>;
+    const int lane = threadIdx.x % 32;
+    const int sub = lane % kLanesPerRow;                   // position of the lane within its row
+    const int items = prm.Hq + 2 * prm.H_out;              // per token: query heads, stored key heads, stored value heads
+    const long long total = (long long)prm.n_tok * items;
+    const int n_rep = prm.Hq / prm.Hkv;
+    const bool expanded = prm.H_out == prm.Hq;
+    const PosT* pos = static_cast<const PosT*>(prm.pos);
+    const long long rows_per_pass = (long long)gridDim.x * blockDim.x / kLanesPerRow;
+    // whole warps stay in the loop together (shuffles below): rows past the end are computed on row 0 and dropped
+    const long long padded = (total + 3) / 4 * 4;
+    for (long long w0 = (blockIdx.x * (long long)blockDim.x + threadIdx.x) / kLanesPerRow; w0 < padded; w0 += rows_per_pass) {
+        const bool live = w0 < total;
+        const long long w = live ? w0 : 0;
+        const int t = (int)(w / items);
+        const int item = (int)(w % items);
+        const int kind = item < prm.Hq ? 0 : (item < prm.Hq + prm.H_out ? 1 : 2);   // 0 query, 1 key, 2 value
+        const int ho = kind == 0 ? item : (kind == 1 ? item - prm.Hq : item - prm.Hq - prm.H_out);
+        // source head inside the token's QKV row, and the query head whose 2-D table applies
+        int src_head, table_head;
+        if (kind == 0) { src_head = ho; table_head = ho; }
+        else {
+            const int kvh = expanded ? ho / n_rep : ho;
+            src_head = (kind == 1 ? prm.Hq : prm.Hq + prm.Hkv) + kvh;
+            table_head = expanded ? ho : ho * n_rep;
+        }
+        // destination
+        char* dst = nullptr;
+        bool store = live;
+        if (kind == 0) {
+            dst = prm.q_out + ho * prm.q_head_bytes + t * prm.q_tok_bytes;
+        } else {
+            const bool reporter = live && sub == 0 && item == prm.Hq;
+            const long long slot = prm.batch_idx[t];
+            const long long p = (long long)pos[t];
+            if (slot < 0 || slot >= prm.max_batch) { if (reporter) raise_status(prm.status, FPKV_STATUS_BAD_SLOT); store = false; }
+            else if (p < 0 || p / prm.P >= prm.n_pages) { if (reporter) raise_status(prm.status, FPKV_STATUS_BAD_POS); store = false; }
+            else {
+                long long page = prm.page_table[slot * prm.n_pages + p / prm.P];
+                if (page < 0) {                            // decode: the reference clamps to the reserved page; packed: caller error
+                    if (!prm.decode_mode && reporter) raise_status(prm.status, FPKV_STATUS_BAD_PAGE);
+                    page = 0;
+                } else if (page >= prm.n_pages) {
+                    if (reporter) raise_status(prm.status, FPKV_STATUS_BAD_PAGE);
+                    store = false; page = 0;
+                }
+                const long long addr = page * prm.P + p % prm.P;
+                dst = prm.pool_layer + ((size_t)(kind - 1) * prm.H_out + ho) * prm.plane_bytes + (size_t)addr * D * sizeof(T);
+            }
+        }
+        const RowT in = *reinterpret_cast<const RowT*>(prm.qkv + t * prm.qkv_row_bytes + ((size_t)src_head * D + sub * E) * sizeof(T));
+        RowT out;
+        if (kind == 2) {
+            out = in;
+        }
+        // the norm's sum runs over the eight lanes of a row; value rows take part with a sum nobody uses
+        float x[E];
+        float ss = 0.f;
+#pragma unroll
+        for (int e = 0; e < E; ++e) { x[e] = to_f32<T>(in.v[e]); ss = __fadd_rn(ss, __fmul_rn(x[e], x[e])); }
+#pragma unroll
+        for (int o = kLanesPerRow / 2; o > 0; o >>= 1) ss = __fadd_rn(ss, __shfl_xor_sync(0xffffffffu, ss, o));
+        if (kind != 2) {
+            const float r = __fdiv_rn(1.f, __fsqrt_rn(__fadd_rn(__fdiv_rn(ss, (float)D), prm.eps)));
+#pragma unroll
+            for (int e = 0; e < E; ++e) x[e] = to_f32<T>(from_f32<T>(__fmul_rn(x[e], r)));   // the norm's output is rounded
+            const int i0 = sub * (E / 2);                  // first pair of this lane; a lane's pairs lie in one half of the head
+            const float2* table = nullptr;
+            if (i0 < D / 4) table = prm.freqs + (size_t)t * (D / 4) + i0;
+            else if (prm.freqs2d != nullptr) table = prm.freqs2d + ((size_t)t * prm.Hq + table_head) * (D / 4) + (i0 - D / 4);
+#pragma unroll
+            for (int pr = 0; pr < E / 2; ++pr) {
+                const float a = x[2 * pr], b = x[2 * pr + 1];
+                if (table != nullptr) {
+                    const float2 cs = table[pr];
+                    out.v[2 * pr] = from_f32<T>(__fsub_rn(__fmul_rn(a, cs.x), __fmul_rn(b, cs.y)));
+                    out.v[2 * pr + 1] = from_f32<T>(__fadd_rn(__fmul_rn(a, cs.y), __fmul_rn(b, cs.x)));
+                } else {
+                    out.v[2 * pr] = from_f32<T>(a);
+                    out.v[2 * pr + 1] = from_f32<T>(b);
+                }
+            }
+        }
+        if (store) *reinterpret_cast<RowT*>(dst + (size_t)sub * E * sizeof(T)) = out;
+    }
+}
+
+template <typename T, int D>
+int launch_typed(const PreAppendParams& prm, int pos_type, cudaStream_t stream)
+{
+    const long long rows = (long long)prm.n_tok * (prm.Hq + 2 * prm.H_out);
+    long long blocks = (rows + 31) / 32;                   // 256 threads = 32 rows of eight lanes
+    if (blocks > 148 * 8) blocks = 148 * 8;               // grid-stride beyond eight CTAs per SM
+    if (pos_type == FPKV_I32) pre_append_kernel<T, D, int32_t><<<(unsigned)blocks, 256, 0, stream>>>(prm);
+    else pre_append_kernel<T, D, int64_t><<<(unsigned)blocks, 256, 0, stream>>>(prm);
+    return cudaGetLastError() == cudaSuccess ? FPKV_OK : FPKV_ELAUNCH;
+}
+
+}  // namespace
+
+int launch_pre_append(const PoolView& pv, int layer, const void* qkv, long long qkv_stride_t, int Hq, int Hkv,
+                      const float* freqs_cis, const float* freqs_cis_2d, const int64_t* batch_idx, const void* pos,
+                      int pos_type, int n_tok, bool decode_mode, void* q_out, long long q_stride_h,
+                      long long q_stride_t, float eps, int32_t* status, cudaStream_t stream)
+{
+    if (n_tok == 0) return FPKV_OK;
+    PreAppendParams prm;
+    prm.pool_layer = pv.plane(layer, 0, 0); prm.plane_bytes = pv.plane_bytes(); prm.H_out = pv.H;
+    prm.page_table = pv.page_table; prm.n_pages = pv.n_pages; prm.max_batch = pv.max_batch; prm.P = pv.P;
+    prm.qkv = static_cast<const char*>(qkv); prm.qkv_row_bytes = qkv_stride_t * pv.esize;
+    prm.Hq = Hq; prm.Hkv = Hkv;
+    prm.freqs = reinterpret_cast<const float2*>(freqs_cis); prm.freqs2d = reinterpret_cast<const float2*>(freqs_cis_2d);
+    prm.batch_idx = batch_idx; prm.pos = pos; prm.n_tok = n_tok; prm.decode_mode = decode_mode ? 1 : 0;
+    prm.q_out = static_cast<char*>(q_out); prm.q_head_bytes = q_stride_h * pv.esize; prm.q_tok_bytes = q_stride_t * pv.esize;
+    prm.eps = eps; prm.status = status;
+    if (pv.D == 128) {
+        if (pv.dtype == FPKV_BF16) return launch_typed<__nv_bfloat16, 128>(prm, pos_type, stream);
+        if (pv.dtype == FPKV_F16) return launch_typed<__half, 128>(prm, pos_type, stream);
+        return launch_typed<float, 128>(prm, pos_type, stream);
+    }
+    if (pv.D == 64) {
+        if (pv.dtype == FPKV_BF16) return launch_typed<__nv_bfloat16, 64>(prm, pos_type, stream);
+        if (pv.dtype == FPKV_F16) return launch_typed<__half, 64>(prm, pos_type, stream);
+        return launch_typed<float, 64>(prm, pos_type, stream);
+    }
+    return FPKV_ESHAPE;
+}
+
+}  // namespace fpkv

@@ -22,7 +22,7 @@ ESTATIC = -8
 STATUS_BAD_SLOT, STATUS_BAD_POS, STATUS_BAD_PAGE, STATUS_TIMEOUT = 1, 2, 4, 8
 
 # every symbol include/fpkv.h declares
-EXPORTS = ("fpkv_version", "fpkv_strerror", "fpkv_append_decode", "fpkv_append_packed", "fpkv_gather",
+EXPORTS = ("fpkv_version", "fpkv_strerror", "fpkv_append_decode", "fpkv_append_packed", "fpkv_pre_append", "fpkv_gather",
            "fpkv_decode_workspace_bytes", "fpkv_decode_attn", "fpkv_decode_attn_static", "fpkv_prefill_attn", "fpkv_table_update")
 
 
@@ -62,6 +62,9 @@ def _load():
     lib.fpkv_append_decode.argtypes = [pool, i32, vp, vp, i32, vp, i64, i64, vp, i64, i64, i32, vp, vp]
     lib.fpkv_append_packed.restype = ctypes.c_int
     lib.fpkv_append_packed.argtypes = [pool, i32, vp, vp, i32, vp, i64, i64, vp, i64, i64, i32, vp, vp]
+    lib.fpkv_pre_append.restype = ctypes.c_int
+    lib.fpkv_pre_append.argtypes = [pool, i32, vp, i64, i32, i32, vp, vp, vp, vp, i32, i32, i32, vp, i64, i64,
+                                    ctypes.c_float, vp, vp]
     lib.fpkv_gather.restype = ctypes.c_int
     lib.fpkv_gather.argtypes = [pool, i32, i32, i32, vp, vp, vp, vp]
     lib.fpkv_decode_workspace_bytes.restype = ctypes.c_int

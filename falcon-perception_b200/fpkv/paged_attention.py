@@ -279,6 +279,57 @@ class PagedKVCache(KVCacheBase):
             kk.shape[2], self._status_ptr(), _stream(self._dev)), "fpkv_append_packed")
         return k_val, v_val
 
+    def pre_attention_append(self, layer_id: int, qkv: Tensor, n_q_heads: int, n_kv_heads: int, freqs_cis: Tensor,
+                             freqs_cis_2d: Tensor | None, batch_idx: Tensor, input_pos: Tensor,
+                             eps: float | None = None) -> Tensor:
+        """Norm, rotary embedding and K/V append in one kernel: everything
+        ``Attention._pre_attention`` does behind the QKV projection
+        (``falcon_perception/model.py:107-120``) plus the ``insert_kv`` that
+        follows (``model.py:150-155``).  qkv (B,S,(Hq+2*Hkv)*D) is the projection
+        output; freqs_cis (B,S,D/4) complex64 the 1-D rotary table indexed by
+        position; freqs_cis_2d (B,S,Hq,D/4) complex64 or None; batch_idx /
+        input_pos as ``insert_kv`` takes them ((B,) and (B,1) in a decode step,
+        (1,L) each in a packed prefill).  Returns the normalised, rotated
+        queries as a (B,Hq,S,D) view; K and V are in the pool.  The pool holds
+        n_q_heads heads (the reference's expanded copies) or n_kv_heads heads
+        (each key head once; exact when no 2-D table is in use or its
+        frequencies agree within a GQA group)."""
+        B, S, W = qkv.shape
+        D = self.head_dim
+        assert W == (n_q_heads + 2 * n_kv_heads) * D, "qkv width must be (Hq + 2*Hkv) * head_dim"
+        assert self.n_heads in (n_q_heads, n_kv_heads), "the pool must hold the query or the KV head count"
+        assert qkv.dtype == self.dtype, "dtype must match the pool"
+        assert freqs_cis.shape == (B, S, D // 4) and freqs_cis.dtype == torch.complex64
+        if freqs_cis_2d is not None:
+            assert freqs_cis_2d.shape == (B, S, n_q_heads, D // 4) and freqs_cis_2d.dtype == torch.complex64
+        decode_mode = batch_idx.ndim == 1
+        if decode_mode:
+            assert S == 1 and batch_idx.shape == (B,), "a decode step appends one token per row"
+        else:
+            assert B == 1 and batch_idx.shape == (1, S), "a packed prefill is one row of (1, L) indices"
+        self._require_cuda(qkv, batch_idx, input_pos, freqs_cis)
+        T = B * S
+        x = qkv.reshape(T, W)
+        if x.stride(1) != 1 or x.data_ptr() % 16 or (x.stride(0) * x.element_size()) % 16:
+            x = x.contiguous()
+        bi = batch_idx.reshape(-1)
+        bi = bi if bi.dtype == torch.int64 else bi.to(torch.int64)
+        bi = bi if bi.is_contiguous() else bi.contiguous()
+        ip = input_pos.reshape(-1)
+        ip = ip if ip.is_contiguous() else ip.contiguous()
+        assert bi.numel() == T and ip.numel() == T
+        fc = torch.view_as_real(freqs_cis.reshape(T, D // 4)).contiguous()
+        fc2 = torch.view_as_real(freqs_cis_2d.reshape(T, n_q_heads, D // 4)).contiguous() if freqs_cis_2d is not None else None
+        q_out = torch.empty((B, S, n_q_heads, D), dtype=self.dtype, device=qkv.device)
+        if eps is None:
+            eps = torch.finfo(torch.float32).eps
+        _lib.check(_lib.lib.fpkv_pre_append(
+            ctypes.byref(self._pool), layer_id, x.data_ptr(), x.stride(0), n_q_heads, n_kv_heads, fc.data_ptr(),
+            fc2.data_ptr() if fc2 is not None else None, bi.data_ptr(), ip.data_ptr(), _pos_type(ip), T,
+            1 if decode_mode else 0, q_out.data_ptr(), D, n_q_heads * D, float(eps), self._status_ptr(),
+            _stream(self._dev)), "fpkv_pre_append")
+        return q_out.permute(0, 2, 1, 3)
+
     def _rows16(self, t: Tensor) -> Tensor:
         """The kernels read whole head_dim rows with 16-byte accesses through
         arbitrary outer strides (so the model's permuted views need no copy);

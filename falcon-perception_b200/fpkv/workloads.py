@@ -159,3 +159,18 @@ def config3_prefill_case(n_seq=8, seed=3003) -> PrefillCase:
     toks = image_text_tokens(0, 1024, 63)
     return make_prefill_case(seed, [toks] * n_seq, Hq=16, Hkv=8, D=128, P=128,
                              dtype=torch.bfloat16, value_scale=128 ** -0.5)
+
+
+# Cases of the fused "norm + rotary embedding + append" step.  name: (seed, B, S, Hq, Hkv, D, with_2d, dtype).
+# The rotary tables of a case are stored with its golden file; the projection is rebuilt from the seed.
+PRE_ATTENTION_CASES = {
+    "pre_attention_bf16_2d": (5101, 2, 7, 8, 4, 128, True, torch.bfloat16),
+    "pre_attention_bf16_text": (5102, 5, 1, 8, 4, 128, False, torch.bfloat16),
+    "pre_attention_f16_d64": (5103, 1, 9, 4, 4, 64, True, torch.float16),
+    "pre_attention_f32": (5104, 2, 3, 4, 2, 64, True, torch.float32),
+}
+
+
+def pre_attention_qkv(rng, B, S, Hq, Hkv, D, dtype):
+    """The QKV projection output of a case: the first draw of its generator."""
+    return torch.from_numpy(rng.standard_normal((B, S, (Hq + 2 * Hkv) * D), dtype=np.float32) * 1.7).to(dtype)

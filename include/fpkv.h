@@ -153,6 +153,40 @@ FPKV_API int fpkv_append_packed(const fpkv_pool* pool, int32_t layer,
                        int32_t L, int32_t* status, void* stream);
 
 /*
+ * Norm + rotary embedding + append in one pass over the QKV projection.
+ * Replaces the part of Attention._pre_attention behind the projection
+ * (falcon_perception/model.py:107-120: split, per-head RMS norm of q and k,
+ * repeat_kv, apply_3d_rotary_emb of falcon_perception/rope.py:87-104, permutes)
+ * together with the insert_kv that follows it (model.py:150-155).
+ *   qkv          device (n_tok) rows of (n_q_heads + 2*n_kv_heads)*head_dim
+ *                elements of the pool's dtype, [q | k | v], row stride
+ *                qkv_stride_t elements (the (B,S,.) projection output flattened)
+ *   freqs_cis    device float (n_tok, head_dim/4, 2): cos, sin of the 1-D table
+ *                already indexed by position (complex64 viewed as real)
+ *   freqs_cis_2d device float (n_tok, n_q_heads, head_dim/4, 2), or NULL when no
+ *                token carries a 2-D position (the second half of every head is
+ *                then only normalised)
+ *   batch_idx, input_pos   slot and position of every token (as the two appends)
+ *   decode_mode  1: a negative page id is clamped to page 0 (fpkv_append_decode),
+ *                0: it is reported (fpkv_append_packed)
+ *   q_out        device: normalised, rotated queries, element (h, t, d) at
+ *                h*q_stride_h + t*q_stride_t + d
+ *   eps          the norm's epsilon (the reference leaves it at fp32 epsilon)
+ * The pool holds either n_q_heads heads (the reference's expanded layout: stored
+ * head h is key head h / n_rep rotated with query head h's 2-D table) or
+ * n_kv_heads heads (each key head once, rotated with the 2-D table of the first
+ * query head of its group: identical to the reference when the 2-D frequencies
+ * agree within a group or freqs_cis_2d is NULL).
+ */
+FPKV_API int fpkv_pre_append(const fpkv_pool* pool, int32_t layer,
+                    const void* qkv, int64_t qkv_stride_t, int32_t n_q_heads, int32_t n_kv_heads,
+                    const float* freqs_cis, const float* freqs_cis_2d,
+                    const int64_t* batch_idx, const void* input_pos, int32_t pos_type,
+                    int32_t n_tok, int32_t decode_mode,
+                    void* q_out, int64_t q_stride_h, int64_t q_stride_t,
+                    float eps, int32_t* status, void* stream);
+
+/*
  * Gather: read logical positions [0, n_tokens) of one slot back through the
  * page table into contiguous (n_heads, n_tokens, head_dim) buffers.  The
  * inverse of the two appends; what the reference's attention kernels do

@@ -281,3 +281,54 @@ def post_attention_gate(out, lse, sinks):
     scale = torch.sigmoid(lse - sinks.float().view(1, -1, 1))
     gated = (out.float() * scale.unsqueeze(-1)).to(out.dtype)
     return gated.permute(0, 2, 1, 3).contiguous().flatten(2)
+
+
+def _rms_norm_rows(x):
+    """F.rms_norm(x, (D,)) without weight and with eps left at its default
+    (falcon_perception/model.py:112-113): computed in fp32 as
+    x * rsqrt(mean(x^2) + eps), eps = machine epsilon of fp32 (the arithmetic
+    type, also for 16-bit inputs), and rounded back to x's dtype."""
+    x32 = x.float()
+    eps = torch.finfo(torch.float32).eps
+    return (x32 * torch.rsqrt(x32.pow(2).mean(-1, keepdim=True) + eps)).to(x.dtype)
+
+
+def _rotate_pairs(x, cos, sin):
+    """Adjacent pairs (x[2i], x[2i+1]) rotated by (cos, sin)[i], in fp32."""
+    x32 = x.float()
+    even, odd = x32[..., 0::2], x32[..., 1::2]
+    out = torch.empty_like(x32)
+    out[..., 0::2] = even * cos - odd * sin
+    out[..., 1::2] = even * sin + odd * cos
+    return out
+
+
+def pre_attention_tail(qkv, n_q_heads, n_kv_heads, head_dim, freqs_cis, freqs_cis_2d=None):
+    """What Attention._pre_attention does to the QKV projection before the
+    cache and the attention kernel see it (falcon_perception/model.py:107-120):
+    split, per-head RMS norm of q and k, GQA expansion of k and v to the query
+    head count (repeat_interleave), rotary embedding, (B,S,H,D) -> (B,H,S,D).
+    Rotary embedding (falcon_perception/rope.py:30-104): the first half of the
+    head dimension is rotated pairwise by freqs_cis[b, s, i] (1-D, complex64,
+    shape (B,S,D/4)); the second half by freqs_cis_2d[b, s, h, i] (per QUERY
+    head, shape (B,S,Hq,D/4)) when it is given, and left alone otherwise.  Each
+    half is rotated in fp32 and rounded to the input dtype.
+    qkv (B,S,(Hq+2*Hkv)*D).  Returns xq, xk, xv as (B,Hq,S,D)."""
+    B, S, _ = qkv.shape
+    D, Hq, Hkv = head_dim, n_q_heads, n_kv_heads
+    xq, xk, xv = qkv.split([Hq * D, Hkv * D, Hkv * D], dim=-1)
+    xq = _rms_norm_rows(xq.reshape(B, S, Hq, D))
+    xk = _rms_norm_rows(xk.reshape(B, S, Hkv, D))
+    xv = xv.reshape(B, S, Hkv, D)
+    n_rep = Hq // Hkv
+    xk = xk.repeat_interleave(n_rep, dim=2)
+    xv = xv.repeat_interleave(n_rep, dim=2)
+    fc = freqs_cis.reshape(B, S, 1, D // 4)
+    outs = []
+    for x in (xq, xk):
+        t = _rotate_pairs(x[..., :D // 2], fc.real, fc.imag).to(x.dtype)
+        hw = x[..., D // 2:]
+        if freqs_cis_2d is not None:
+            hw = _rotate_pairs(hw, freqs_cis_2d.real, freqs_cis_2d.imag).to(x.dtype)
+        outs.append(torch.cat([t, hw], dim=-1))
+    return outs[0].permute(0, 2, 1, 3), outs[1].permute(0, 2, 1, 3), xv.permute(0, 2, 1, 3)

@@ -314,8 +314,43 @@ def post_attention_golden():
     print("post_attention: oracle equals reference bit for bit,", tuple(ref.shape))
 
 
+# --------------------------------------------------------------------------
+# 5. norm, GQA expansion and rotary embedding in front of the cache (Attention._pre_attention, model.py:105-120)
+# --------------------------------------------------------------------------
+def pre_attention_inputs(seed, B, S, Hq, Hkv, D, with_2d, dtype):
+    """Seeded inputs of one case (the tests rebuild the projection from the seed and read the rotary tables from the file)."""
+    from falcon_perception.rope import precompute_freqs_cis, apply_golden_freqs_cis_to_visual_pos
+    rng = np.random.default_rng(seed)
+    qkv = wl.pre_attention_qkv(rng, B, S, Hq, Hkv, D, dtype)
+    pos = torch.from_numpy(rng.integers(0, 4096, (B, S)))
+    freqs_cis = precompute_freqs_cis(D // 2, 4096)[pos]                         # (B, S, D/4) complex64
+    freqs_2d = None
+    if with_2d:
+        freqs_hFP = torch.from_numpy(rng.standard_normal((Hq, D // 4, 2), dtype=np.float32) * 3)
+        pos_hw = torch.from_numpy(rng.uniform(-1, 1, (B, S, 2)).astype(np.float32))
+        pos_hw[:, ::3] = 0                                                       # text tokens: identity rotation
+        freqs_2d = apply_golden_freqs_cis_to_visual_pos(freqs_hFP, pos_hw)       # (B, S, Hq, D/4) complex64
+    return qkv, freqs_cis, freqs_2d
+
+
+def pre_attention_goldens():
+    from falcon_perception.model import Attention
+    for name, (seed, B, S, Hq, Hkv, D, with_2d, dtype) in wl.PRE_ATTENTION_CASES.items():
+        qkv, fc, fc2 = pre_attention_inputs(seed, B, S, Hq, Hkv, D, with_2d, dtype)
+        fake = types.SimpleNamespace(wqkv=lambda x: qkv, q_dim=Hq * D, kv_dim=Hkv * D, head_dim=D, n_rep=Hq // Hkv)
+        x = torch.zeros(B, S, 16, dtype=dtype)                                   # the projection is injected: x is unused
+        rq, rk, rv = Attention._pre_attention(fake, x, fc, fc2)
+        mq, mk, mv = orc.pre_attention_tail(qkv, Hq, Hkv, D, fc, fc2)
+        assert torch.equal(rq, mq) and torch.equal(rk, mk) and torch.equal(rv, mv), name
+        np.savez_compressed(os.path.join(OUT, name + ".npz"), xq=rq.float().numpy(), xk=rk.float().numpy(),
+                            freqs_cis=torch.view_as_real(fc).numpy(),
+                            freqs_cis_2d=torch.view_as_real(fc2).numpy() if fc2 is not None else np.zeros(0, np.float32))
+        print(name + ": oracle equals reference bit for bit,", tuple(rq.shape), tuple(rk.shape))
+
+
 if __name__ == "__main__":
     torch.manual_seed(0)
+    pre_attention_goldens()
     post_attention_golden()
     allocator_traces()
     decode_goldens()

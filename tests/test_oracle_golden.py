@@ -154,3 +154,26 @@ def test_sink_gate_matches_reference():
     sinks = torch.from_numpy(rng.standard_normal(Hq, dtype=np.float32)).bfloat16()
     got = orc.post_attention_gate(out, lse, sinks)
     assert np.array_equal(got.float().numpy(), golden("post_attention")["gated"])
+
+
+def pre_attention_case(name):
+    """Inputs of one fused norm + rotary case: the projection from the seed, the rotary tables and the
+    reference's outputs from the golden file."""
+    seed, B, S, Hq, Hkv, D, with_2d, dtype = wl.PRE_ATTENTION_CASES[name]
+    g = golden(name)
+    qkv = wl.pre_attention_qkv(np.random.default_rng(seed), B, S, Hq, Hkv, D, dtype)
+    fc = torch.view_as_complex(torch.from_numpy(g["freqs_cis"]).contiguous())
+    fc2 = torch.view_as_complex(torch.from_numpy(g["freqs_cis_2d"]).contiguous()) if with_2d else None
+    return qkv, fc, fc2, g, (B, S, Hq, Hkv, D)
+
+
+@pytest.mark.parametrize("name", list(wl.PRE_ATTENTION_CASES))
+def test_pre_attention_tail_matches_reference(name):
+    """Attention._pre_attention behind the QKV projection (norm, GQA expansion, 1-D and 2-D rotary embedding),
+    recorded from the reference: the oracle's restatement is bit-identical."""
+    qkv, fc, fc2, g, (B, S, Hq, Hkv, D) = pre_attention_case(name)
+    xq, xk, xv = orc.pre_attention_tail(qkv, Hq, Hkv, D, fc, fc2)
+    assert np.array_equal(xq.float().numpy(), g["xq"]) and np.array_equal(xk.float().numpy(), g["xk"])
+    # values pass through untouched, expanded to the query head count
+    v_in = qkv[..., (Hq + Hkv) * D:].reshape(B, S, Hkv, D).repeat_interleave(Hq // Hkv, 2).permute(0, 2, 1, 3)
+    assert torch.equal(xv, v_in)
