@@ -480,6 +480,22 @@ def run_prefill(args):
     a1.record(stream)
     torch.cuda.synchronize(device)
     ms_attn = a0.elapsed_time(a1) / K
+    # the fused norm + rotary embedding + append step on the same packed row (reported beside the headline)
+    gen = torch.Generator(device="cpu").manual_seed(3004)
+    L = q.shape[2]
+    qkv = (torch.randn(1, L, (HQ + 2 * HKV) * D, generator=gen) * 1.7).to(torch.bfloat16).to(device)
+    ang = torch.randn(1, L, D // 4, generator=gen).to(device)
+    fc = torch.polar(torch.ones_like(ang), ang)
+    for _ in range(3):
+        cache.pre_attention_append(0, qkv, HQ, HKV, fc, None, bidx, ipos)
+    p0, p1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    p0.record(stream)
+    for _ in range(min(K, 200)):
+        cache.pre_attention_append(0, qkv, HQ, HKV, fc, None, bidx, ipos)
+    p1.record(stream)
+    torch.cuda.synchronize(device)
+    ms_pre = p0.elapsed_time(p1) / min(K, 200)
+    pre_bytes = L * ((HQ + 2 * HKV) * D * 2 + HQ * D * 2 + 2 * HKV * D * 2 + (D // 4) * 8)
     clocks = sampler.stop()
     cache.check_status()
     try:
@@ -499,6 +515,9 @@ def run_prefill(args):
         "roofline": {"bound": "tensor", "kernel": "prefill_tc_kernel, timed alone", "achieved": tf, "peak": peak,
                      "unit": "TFLOP/s", "frac": tf / peak, "peak_source": src, "traffic": None,
                      "flops_per_launch": flops, "ms_per_launch": ms_attn},
+        "pre_append": {"what": "fused per-head norm + 1-D rotary embedding + K/V append of the same packed row "
+                               "(includes the wrapper's table repacking)", "ms": ms_pre,
+                       "algorithmic_bytes": pre_bytes, "gbps": pre_bytes / (ms_pre * 1e-3) / 1e9},
         "clocks": clocks}), flush=True)
 
 

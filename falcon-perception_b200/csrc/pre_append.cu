@@ -49,8 +49,22 @@ template <> __device__ __forceinline__ float to_f32<__nv_bfloat16>(__nv_bfloat16
 template <> __device__ __forceinline__ float to_f32<__half>(__half v) { return __half2float(v); }
 template <typename T> __device__ __forceinline__ T from_f32(float v);
 template <> __device__ __forceinline__ float from_f32<float>(float v) { return v; }
-template <> __device__ __forceinline__ __nv_bfloat16 from_f32<__nv_bfloat16>(float v) { return __float2bfloat16_rn(v); }
+template <> __device__ __forceinline__ __attribute__((unused)) __nv_bfloat16 from_f32<__nv_bfloat16>(float v) { return __float2bfloat16_rn(v); }
 template <> __device__ __forceinline__ __half from_f32<__half>(float v) { return __float2half_rn(v); }
+
+// Rounding to the storage type goes through the conversion unit, which is as narrow as the special-function unit
+// (16 results per clock per SM); for bf16 a pair is rounded by one packed conversion and unpacked with shifts.
+template <typename T> __device__ __forceinline__ void round_pair(float a, float b, float& ra, float& rb, T& ta, T& tb) {
+    ta = from_f32<T>(a); tb = from_f32<T>(b); ra = to_f32<T>(ta); rb = to_f32<T>(tb);
+}
+template <> __device__ __forceinline__ void round_pair<__nv_bfloat16>(float a, float b, float& ra, float& rb,
+                                                                      __nv_bfloat16& ta, __nv_bfloat16& tb) {
+    uint32_t w;
+    asm("cvt.rn.bf16x2.f32 %0, %1, %2;" : "=r"(w) : "f"(b), "f"(a));          // first source lands in the upper half
+    ra = __uint_as_float(w << 16); rb = __uint_as_float(w & 0xffff0000u);
+    const uint16_t lo = (uint16_t)(w & 0xffffu), hi = (uint16_t)(w >> 16);
+    ta = *reinterpret_cast<const __nv_bfloat16*>(&lo); tb = *reinterpret_cast<const __nv_bfloat16*>(&hi);
+}
 
 template <typename T, int E> struct alignas(16) Row { T v[E]; };   // E elements of one lane, moved as 16-byte vectors
 
@@ -65,18 +79,18 @@ pre_append_kernel(const PreAppendParams prm)
     const int lane = threadIdx.x % 32;
     const int sub = lane % kLanesPerRow;                   // position of the lane within its row
     const int items = prm.Hq + 2 * prm.H_out;              // per token: query heads, stored key heads, stored value heads
-    const long long total = (long long)prm.n_tok * items;
+    const unsigned total = (unsigned)prm.n_tok * (unsigned)items;      // the launcher keeps this below 2^31: 32-bit index math
     const int n_rep = prm.Hq / prm.Hkv;
     const bool expanded = prm.H_out == prm.Hq;
     const PosT* pos = static_cast<const PosT*>(prm.pos);
-    const long long rows_per_pass = (long long)gridDim.x * blockDim.x / kLanesPerRow;
+    const unsigned rows_per_pass = gridDim.x * blockDim.x / kLanesPerRow;
     // whole warps stay in the loop together (shuffles below): rows past the end are computed on row 0 and dropped
-    const long long padded = (total + 3) / 4 * 4;
-    for (long long w0 = (blockIdx.x * (long long)blockDim.x + threadIdx.x) / kLanesPerRow; w0 < padded; w0 += rows_per_pass) {
+    const unsigned padded = (total + 3u) / 4u * 4u;
+    for (unsigned w0 = (blockIdx.x * blockDim.x + threadIdx.x) / kLanesPerRow; w0 < padded; w0 += rows_per_pass) {
         const bool live = w0 < total;
-        const long long w = live ? w0 : 0;
-        const int t = (int)(w / items);
-        const int item = (int)(w % items);
+        const unsigned w = live ? w0 : 0u;
+        const int t = (int)(w / (unsigned)items);
+        const int item = (int)(w - (unsigned)t * (unsigned)items);
         const int kind = item < prm.Hq ? 0 : (item < prm.Hq + prm.H_out ? 1 : 2);   // 0 query, 1 key, 2 value
         const int ho = kind == 0 ? item : (kind == 1 ? item - prm.Hq : item - prm.Hq - prm.H_out);
         // source head inside the token's QKV row, and the query head whose 2-D table applies
@@ -126,7 +140,11 @@ pre_append_kernel(const PreAppendParams prm)
         if (kind != 2) {
             const float r = __fdiv_rn(1.f, __fsqrt_rn(__fadd_rn(__fdiv_rn(ss, (float)D), prm.eps)));
 #pragma unroll
-            for (int e = 0; e < E; ++e) x[e] = to_f32<T>(from_f32<T>(__fmul_rn(x[e], r)));   // the norm's output is rounded
+            for (int e = 0; e < E; e += 2) {               // the norm's output is rounded to the storage type
+                T ta, tb;
+                round_pair<T>(__fmul_rn(x[e], r), __fmul_rn(x[e + 1], r), x[e], x[e + 1], ta, tb);
+                out.v[e] = ta; out.v[e + 1] = tb;          // what stays when the half is not rotated
+            }
             const int i0 = sub * (E / 2);                  // first pair of this lane; a lane's pairs lie in one half of the head
             const float2* table = nullptr;
             if (i0 < D / 4) table = prm.freqs + (size_t)t * (D / 4) + i0;
@@ -136,11 +154,9 @@ pre_append_kernel(const PreAppendParams prm)
                 const float a = x[2 * pr], b = x[2 * pr + 1];
                 if (table != nullptr) {
                     const float2 cs = table[pr];
-                    out.v[2 * pr] = from_f32<T>(__fsub_rn(__fmul_rn(a, cs.x), __fmul_rn(b, cs.y)));
-                    out.v[2 * pr + 1] = from_f32<T>(__fadd_rn(__fmul_rn(a, cs.y), __fmul_rn(b, cs.x)));
-                } else {
-                    out.v[2 * pr] = from_f32<T>(a);
-                    out.v[2 * pr + 1] = from_f32<T>(b);
+                    float ra, rb;
+                    round_pair<T>(__fsub_rn(__fmul_rn(a, cs.x), __fmul_rn(b, cs.y)),
+                                  __fadd_rn(__fmul_rn(a, cs.y), __fmul_rn(b, cs.x)), ra, rb, out.v[2 * pr], out.v[2 * pr + 1]);
                 }
             }
         }
@@ -167,6 +183,7 @@ int launch_pre_append(const PoolView& pv, int layer, const void* qkv, long long 
                       long long q_stride_t, float eps, int32_t* status, cudaStream_t stream)
 {
     if (n_tok == 0) return FPKV_OK;
+    if ((long long)n_tok * (Hq + 2 * pv.H) >= (1ll << 31) - 4) return FPKV_ESHAPE;
     PreAppendParams prm;
     prm.pool_layer = pv.plane(layer, 0, 0); prm.plane_bytes = pv.plane_bytes(); prm.H_out = pv.H;
     prm.page_table = pv.page_table; prm.n_pages = pv.n_pages; prm.max_batch = pv.max_batch; prm.P = pv.P;
