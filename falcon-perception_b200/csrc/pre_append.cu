@@ -86,33 +86,21 @@ pre_append_kernel(const PreAppendParams prm)
     const unsigned rows_per_pass = gridDim.x * blockDim.x / kLanesPerRow;
     // whole warps stay in the loop together (shuffles below): rows past the end are computed on row 0 and dropped
     const unsigned padded = (total + 3u) / 4u * 4u;
-    // source row of work item w (its loads are issued one pass ahead of their use)
-    auto source = [&](unsigned w0) -> const RowT* {
-        const unsigned w = w0 < total ? w0 : 0u;
-        const int t = (int)(w / (unsigned)items);
-        const int item = (int)(w - (unsigned)t * (unsigned)items);
-        int src_head = item;                               // query heads come first in the row
-        if (item >= prm.Hq) {
-            const bool is_key = item < prm.Hq + prm.H_out;
-            const int ho = is_key ? item - prm.Hq : item - prm.Hq - prm.H_out;
-            src_head = (is_key ? prm.Hq : prm.Hq + prm.Hkv) + (expanded ? ho / n_rep : ho);
-        }
-        return reinterpret_cast<const RowT*>(prm.qkv + t * prm.qkv_row_bytes + ((size_t)src_head * D + sub * E) * sizeof(T));
-    };
-    const unsigned first = (blockIdx.x * blockDim.x + threadIdx.x) / kLanesPerRow;
-    RowT in_next;
-    if (first < padded) in_next = *source(first);
-    for (unsigned w0 = first; w0 < padded; w0 += rows_per_pass) {
-        const RowT in = in_next;
-        if (w0 + rows_per_pass < padded) in_next = *source(w0 + rows_per_pass);
+    for (unsigned w0 = (blockIdx.x * blockDim.x + threadIdx.x) / kLanesPerRow; w0 < padded; w0 += rows_per_pass) {
         const bool live = w0 < total;
         const unsigned w = live ? w0 : 0u;
         const int t = (int)(w / (unsigned)items);
         const int item = (int)(w - (unsigned)t * (unsigned)items);
         const int kind = item < prm.Hq ? 0 : (item < prm.Hq + prm.H_out ? 1 : 2);   // 0 query, 1 key, 2 value
         const int ho = kind == 0 ? item : (kind == 1 ? item - prm.Hq : item - prm.Hq - prm.H_out);
-        // the query head whose 2-D table applies
-        const int table_head = (kind == 0 || expanded) ? ho : ho * n_rep;
+        // source head inside the token's QKV row, and the query head whose 2-D table applies
+        int src_head, table_head;
+        if (kind == 0) { src_head = ho; table_head = ho; }
+        else {
+            const int kvh = expanded ? ho / n_rep : ho;
+            src_head = (kind == 1 ? prm.Hq : prm.Hq + prm.Hkv) + kvh;
+            table_head = expanded ? ho : ho * n_rep;
+        }
         // destination
         char* dst = nullptr;
         bool store = live;
@@ -137,6 +125,7 @@ pre_append_kernel(const PreAppendParams prm)
                 dst = prm.pool_layer + ((size_t)(kind - 1) * prm.H_out + ho) * prm.plane_bytes + (size_t)addr * D * sizeof(T);
             }
         }
+        const RowT in = *reinterpret_cast<const RowT*>(prm.qkv + t * prm.qkv_row_bytes + ((size_t)src_head * D + sub * E) * sizeof(T));
         RowT out;
         if (kind == 2) {
             out = in;
