@@ -121,3 +121,82 @@ def test_prefill_then_decode_matches_dense_recomputation():
         cos = F.cosine_similarity(got, ref, dim=-1)
         rel = (got - ref).norm(dim=-1) / ref.norm(dim=-1)
         assert cos.min().item() > 0.999 and rel.max().item() < 0.05, (i, cos.min().item(), rel.max().item())
+
+
+def rope_table(positions, D):
+    """1-D rotary table of the given positions, (len, D/4) complex64, theta 10000 over the first half of head_dim."""
+    freqs = 1.0 / (10000.0 ** (torch.arange(0, D // 2, 2).float() / (D // 2)))
+    ang = torch.outer(torch.as_tensor(positions).float(), freqs)
+    return torch.polar(torch.ones_like(ang), ang)
+
+
+def test_flow_with_fused_norm_rotary_append():
+    """The same flow with the front of the call site folded in: the projection output goes through
+    pre_attention_append (norm, rotary embedding, append in one kernel) in the prefill and in every decode step,
+    against dense recomputation built on the oracle's pre_attention_tail."""
+    gen = torch.Generator().manual_seed(77)
+    W = make_weights(gen)
+    Wd = dict(emb=W["emb"].cuda(), head=W["head"].cuda(), layers=[{k: v.cuda() for k, v in lw.items()} for lw in W["layers"]])
+    ids = lambda n: torch.randint(10, VOCAB, (n,), generator=gen).tolist()
+    prompts = [ids(120), ids(250)]
+    n_new = 10
+    cache = PagedKVCache(16, P, 4, HKV, D, NL, torch.bfloat16, "cuda")
+    case = wl.make_prefill_case(0, prompts, Hq=HQ, Hkv=HKV, D=D, P=P, dtype=torch.bfloat16)
+    slots = []
+    for p in prompts:
+        s = cache.allocate(); slots.append(s); cache.reserve(s, None, len(p))
+    bidx, ipos, tok = case.batch_idx_for(slots).cuda(), case.input_pos.cuda(), case.input_ids.cuda()
+    L = case.L
+    mask = cache.create_prefill_blockmask(bidx, tok, wl.IMG_CLS_ID, wl.END_OF_IMG_ID)
+    fc = rope_table(case.input_pos.view(-1), D).view(1, L, D // 4).cuda()
+    x = Wd["emb"][tok.view(-1)]
+    for li, lw in enumerate(Wd["layers"]):
+        qkv = (F.rms_norm(x, (DIM,)) @ lw["qkv"]).view(1, L, -1)
+        xq = cache.pre_attention_append(li, qkv, HQ, HKV, fc, None, bidx, ipos)
+        o, _ = cache.prefill_attention(li, xq, bidx, ipos, mask, sinks=lw["sinks"], token_major=True)
+        x = ffn(x + o.view(L, HQ * D) @ lw["wo"], lw)
+    hidden = {i: [x[case.offsets[i]:case.offsets[i] + len(p)].float().cpu()] for i, p in enumerate(prompts)}
+    seqs = [list(p) for p in prompts]
+    last = torch.stack([x[case.offsets[i] + len(p) - 1] for i, p in enumerate(prompts)])
+    for step in range(n_new):
+        nxt = (last.float() @ Wd["head"].float()).argmax(-1).tolist()
+        for i, t in enumerate(nxt):
+            seqs[i].append(int(t)); cache.reserve(slots[i], None, len(seqs[i]))
+        B = len(seqs)
+        bi = torch.tensor(slots, device="cuda")
+        pos = torch.tensor([len(s) - 1 for s in seqs], dtype=torch.int32, device="cuda")
+        fcd = rope_table(pos.cpu(), D).view(B, 1, D // 4).cuda()
+        x = Wd["emb"][torch.tensor(nxt, device="cuda")]
+        for li, lw in enumerate(Wd["layers"]):
+            qkv = (F.rms_norm(x, (DIM,)) @ lw["qkv"]).view(B, 1, -1)
+            xq = cache.pre_attention_append(li, qkv, HQ, HKV, fcd, None, bi, pos.view(B, 1))
+            o, _ = cache.decode_attention(li, xq, bi, pos, sinks=lw["sinks"])
+            x = ffn(x + o.view(B, HQ * D) @ lw["wo"], lw)
+        for i in range(B):
+            hidden[i].append(x[i:i + 1].float().cpu())
+        last = x
+    cache.check_status()
+
+    # dense recomputation: the oracle's norm + rotary on the whole sequence, causal attention, no cache
+    for i, toks in enumerate(seqs):
+        T = len(toks)
+        Wf = lambda t: t.float()
+        xr = Wf(W["emb"])[torch.tensor(toks)]
+        allowed = torch.from_numpy(orc.prefill_allowed([1] * T, [0] * T))
+        fcr = rope_table(range(T), D).view(1, T, D // 4)
+        for lw in W["layers"]:
+            qkv = (F.rms_norm(xr, (DIM,)) @ Wf(lw["qkv"])).bfloat16().view(1, T, -1)     # the product's projection is bf16
+            q, k, v = orc.pre_attention_tail(qkv, HQ, HKV, D, fcr, None)                  # (1, HQ, T, D), expanded
+            q, k, v = q[0].float(), k[0].float(), v[0].float()
+            s = torch.einsum("htd,hud->htu", q, k) / math.sqrt(D)
+            s = s.masked_fill(~allowed.unsqueeze(0), float("-inf"))
+            lse = torch.logsumexp(s, -1)
+            o = torch.einsum("htu,hud->thd", torch.softmax(s, -1), v)
+            o = o.bfloat16().float() * torch.sigmoid(lse.t() - Wf(lw["sinks"]).view(1, HQ)).unsqueeze(-1)
+            xr = xr + o.bfloat16().float().reshape(T, HQ * D) @ Wf(lw["wo"])
+            xr = ffn(xr, {k_: Wf(v_) for k_, v_ in lw.items()})
+        got = torch.cat(hidden[i])
+        assert got.shape == xr.shape
+        cos = F.cosine_similarity(got, xr, dim=-1)
+        rel = (got - xr).norm(dim=-1) / xr.norm(dim=-1)
+        assert cos.min().item() > 0.999 and rel.max().item() < 0.05, (i, cos.min().item(), rel.max().item())
