@@ -242,7 +242,7 @@ def run_fpkv(args):
     # One pinned staging buffer per direction: the step's q, k, v, positions and slots travel in one
     # host-to-device copy, out and lse come back in one device-to-host copy; the API gets views.
     nq, nk = B * HQ * D * 2, B * HKV * D * 2
-    in_bytes = nq + 2 * nk + B * 4 + B * 8
+    in_bytes = (nq + 2 * nk + B * 4 + B * 8 + 15) // 16 * 16           # rows of the staging array stay 16-byte aligned
     in_h = torch.empty((NV, in_bytes), dtype=torch.uint8).pin_memory()
     in_d = torch.empty(in_bytes, dtype=torch.uint8, device=device)
     # The result needs no staging copy: out and lse are pinned host memory that the kernels write directly

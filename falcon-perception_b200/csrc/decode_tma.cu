@@ -61,6 +61,12 @@ constexpr int kThreads = (kConsumerWarps + 2) * 32;
 #define FPKV_PHASES 5
 #endif
 constexpr int kPhases = FPKV_PHASES;           // unit sizes halve from phase to phase
+constexpr int kSmallPhaseTiles = 8;            // a remainder of at most this many tiles per unit is not halved again
+// Tiles taken by phase p when `rem` are left: half of them, or all of them in the last phase and when halving
+// would leave units of a tile or two (small batches: each piece of a segment costs a partial and a merge step).
+__device__ __forceinline__ int phase_step(int rem, int p, int G) {
+    return (p == kPhases - 1 || rem <= kSmallPhaseTiles * G) ? rem : (rem + 1) / 2;
+}
 constexpr int kDescBlocks = 8;                 // resolved-tile blocks (32 tiles each) between scout and issue warp
 constexpr int kUnitQueue = 8;                  // claimed units in flight between scout and consumers
 constexpr int kClaimAhead = 3;                 // the scout claims the next unit when this few resolved tiles are unissued
@@ -280,7 +286,7 @@ decode_tma_kernel(const __grid_constant__ CUtensorMap tmap, const __grid_constan
         if (lane == 0) {
             cum[0] = 0;
             int at = 0;                                // phase p takes half of what is left, the last one all of it
-            for (int p = 0; p < kPhases; ++p) { pb[p] = at; at += (p == kPhases - 1) ? carry - at : (carry - at + 1) / 2; }
+            for (int p = 0; p < kPhases; ++p) { pb[p] = at; at += phase_step(carry - at, p, G); }
             pb[kPhases] = carry;
         }
     }
@@ -704,7 +710,7 @@ decode_tma_finish_kernel(const Params prm, int G)
         const int p = u / G, j = u - p * G;
 #pragma unroll
         for (int pp = 0; pp < kPhases; ++pp) {
-            const int step = (pp == kPhases - 1) ? Ttot - at : (Ttot - at + 1) / 2;
+            const int step = phase_step(Ttot - at, pp, G);
             if (pp == p) len = step;
             at += step;
         }
