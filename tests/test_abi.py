@@ -70,3 +70,27 @@ def test_validation_happens_before_any_launch():
     if not torch.cuda.is_available():
         # valid arguments but no device: refused, never a silent CPU path
         assert call(p) == -4
+
+
+def test_pre_append_validation():
+    """fpkv_pre_append checks head counts, layout, strides and alignment on the host."""
+    L = _lib.lib
+    p, buf = _pool(n_heads=2, head_dim=64)                    # pool of 2 stored heads
+    ptr = buf.data_ptr()
+    width = (4 + 2 * 2) * 64                                  # 4 query heads, 2 KV heads
+
+    def call(pool=p, hq=4, hkv=2, stride=width, n_tok=3, qkv=ptr, fc=ptr, fc2=None, q_out=ptr, qs=(64, 256),
+             eps=1e-6, pt=0, bi=ptr):
+        return L.fpkv_pre_append(ctypes.byref(pool), 0, qkv, stride, hq, hkv, fc, fc2, bi, ptr, pt, n_tok, 1,
+                                 q_out, qs[0], qs[1], eps, None, None)
+    assert call(hq=3, hkv=2) == -2                            # query heads not a multiple of KV heads
+    assert call(hq=8, hkv=4, stride=(8 + 8) * 64) == -2       # pool holds neither 8 nor 4 heads
+    assert call(stride=width - 64) == -2                      # row shorter than (Hq + 2 Hkv) * D
+    assert call(pool=_pool(n_heads=2, head_dim=32)[0]) == -2  # head_dim outside {64, 128}
+    assert call(n_tok=-1) == -1 and call(pt=7) == -1 and call(eps=-1.0) == -1
+    assert call(qkv=0) == -1 and call(fc=0) == -1 and call(q_out=0) == -1 and call(bi=0) == -1
+    assert call(qkv=ptr + 2) == -3 and call(stride=width + 3) == -3 and call(qs=(64, 250)) == -3
+    assert call(fc=ptr + 4) == -3 and call(fc2=ptr + 4) == -3   # rotary tables are read as 8-byte pairs
+    assert call(n_tok=0) == 0                                 # nothing to do
+    if not torch.cuda.is_available():
+        assert call() == -4                                   # valid arguments, no device: refused
