@@ -213,6 +213,23 @@ template <> __device__ __forceinline__ uint32_t pack2<__half>(float a, float b) 
     asm("cvt.rn.f16x2.f32 %0, %1, %2;" : "=r"(w) : "f"(b), "f"(a));
     return w;
 }
+// Two output values rounded to the storage type (and, with the sink gate on, multiplied by the gate and rounded
+// again, the reference's two-step value), as one packed word.  Conversions go through a unit as narrow as the
+// exponential unit, so they are done two at a time.
+template <typename T> __device__ __forceinline__ uint32_t gated_pair(float a, float b, float gate, bool on);
+template <> __device__ __forceinline__ uint32_t gated_pair<__nv_bfloat16>(float a, float b, float gate, bool on) {
+    uint32_t w = pack2<__nv_bfloat16>(a, b);
+    if (on) w = pack2<__nv_bfloat16>(__uint_as_float(w << 16) * gate, __uint_as_float(w & 0xffff0000u) * gate);
+    return w;
+}
+template <> __device__ __forceinline__ uint32_t gated_pair<__half>(float a, float b, float gate, bool on) {
+    uint32_t w = pack2<__half>(a, b);
+    if (on) {
+        const float2 f = __half22float2(*reinterpret_cast<const __half2*>(&w));
+        w = pack2<__half>(f.x * gate, f.y * gate);
+    }
+    return w;
+}
 __device__ __forceinline__ float ex2(float x) {
     float y;
     asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
@@ -220,7 +237,7 @@ __device__ __forceinline__ float ex2(float x) {
 }
 
 #if defined(FPKV_CTA_SUMS)
-__device__ unsigned long long g_cta_sums[8];               // all CTAs: [0] entry->loop start, [1] loop, [2] loop end->exit, [3] count, [4] tiles
+__device__ unsigned long long g_cta_sums[8];               // all CTAs: [0] entry->loop start, [1] loop, [2] loop end->exit, [3] count, [4] tiles, [5..7] parts of the exit phase
 __device__ __forceinline__ unsigned long long gtime_ns() {
     unsigned long long t; asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t)); return t;
 }
@@ -348,7 +365,7 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_consta
 
 #if defined(FPKV_CTA_SUMS)
     const unsigned long long cta_t0 = gtime_ns();
-    __shared__ unsigned long long cta_marks[2];
+    __shared__ unsigned long long cta_marks[6];           // [2] softmax loop done, [3] first epilogue done, [4] second epilogue done
 #endif
     // ---- prologue ----------------------------------------------------------
     if (tid == 0) {
@@ -601,6 +618,9 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_consta
             }
         }
         PH_DUMP;
+#if defined(FPKV_CTA_SUMS)
+        if (tid == 0) cta_marks[2] = gtime_ns();
+#endif
         // ---- epilogue: O / l -> out, lse --------------------------------------
         // Each thread holds 64 of the 128 output values of its row.  Storing them straight from registers
         // would touch 32 different lines per warp instruction; the two warps of a row quarter stage their 32
@@ -635,8 +655,7 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_consta
                     for (int e = 0; e < 4; ++e) {
                         const float a = (n_tiles > 0 && lsum > 0.f) ? __uint_as_float(v[c + 2 * e]) * inv : 0.f;
                         const float b = (n_tiles > 0 && lsum > 0.f) ? __uint_as_float(v[c + 2 * e + 1]) * inv : 0.f;
-                        const T ra = gated_out<T>(a, gate, gate_on), rb = gated_out<T>(b, gate, gate_on);
-                        w[e] = (uint32_t)*reinterpret_cast<const uint16_t*>(&ra) | ((uint32_t)*reinterpret_cast<const uint16_t*>(&rb) << 16);
+                        w[e] = gated_pair<T>(a, b, gate, gate_on);
                     }
                     const int chunk = colhalf * 8 + c2 * 4 + c / 8;
                     *reinterpret_cast<uint4*>(slab + lane * 256 + ((chunk ^ (lane & 15)) * 16)) = make_uint4(w[0], w[1], w[2], w[3]);
@@ -654,6 +673,9 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_consta
                 }
             }
             if (colhalf == 0 && t0 + row < prm.L) prm.lse[(size_t)hq * prm.L + t0 + row] = lse_nat;
+#if defined(FPKV_CTA_SUMS)
+            if (tid == 0) cta_marks[3 + h] = gtime_ns();
+#endif
         }
     }
     if (!alive && lane == 0) {
@@ -672,7 +694,9 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_consta
     if (tid == 0 && n_tiles > 0) {
         const unsigned long long t3 = gtime_ns();
         atomicAdd(&g_cta_sums[0], cta_marks[0] - cta_t0); atomicAdd(&g_cta_sums[1], cta_marks[1] - cta_marks[0]);
-        atomicAdd(&g_cta_sums[2], t3 - cta_marks[1]); atomicAdd(&g_cta_sums[3], 1ull); atomicAdd(&g_cta_sums[4], (unsigned long long)n_tiles);
+        atomicAdd(&g_cta_sums[2], t3 - cta_marks[1]); atomicAdd(&g_cta_sums[3], 1ull);
+        atomicAdd(&g_cta_sums[5], cta_marks[2] - cta_marks[1]); atomicAdd(&g_cta_sums[6], cta_marks[3] - cta_marks[2]);
+        atomicAdd(&g_cta_sums[7], cta_marks[3 + prm.heads_per_cta - 1] - cta_marks[3]); atomicAdd(&g_cta_sums[4], (unsigned long long)n_tiles);
     }
 #endif
     if (warp == kMmaWarp) {
