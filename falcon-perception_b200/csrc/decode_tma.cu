@@ -335,7 +335,13 @@ decode_tma_kernel(const __grid_constant__ CUtensorMap tmap, const __grid_constan
             }
             int r0 = 0, r1 = 0;
             if (u >= 0) { r0 = ub[u]; r1 = ub[u + 1]; }
-            if (u < 0 || r1 > r0) {                    // empty units are skipped without telling anyone
+            if (u >= 0 && r1 == r0) {
+                // An empty unit (small batches) leaves a neutral partial, so that the finish kernel can read
+                // every unit of a segment's range without working out which ones hold tiles.
+                if (lane < NREP) __stcg(reinterpret_cast<float2*>(prm.ws + (((size_t)u * 2) * NREP + lane) * (D + 2)),
+                                        make_float2(-INFINITY, 0.f));
+            }
+            if (u < 0 || r1 > r0) {                    // empty units are not handed to the consumers
                 if (lane == 0) {
                     const uint32_t s = qn % kUnitQueue, ph = (qn / kUnitQueue) & 1u;
                     ok = mbar_wait(uempty0 + 8 * s, ph ^ 1u, abort_flag);
@@ -703,31 +709,18 @@ decode_tma_finish_kernel(const Params prm, int G)
     if (threadIdx.x == 0) g_fin_times[blockIdx.x % 1024][1] = gtime();
 #endif
     if (u_first == u_last) return;                     // inside one unit (written by the main kernel) or no tile
-    const bool maybe_empty = (info.z & 2) != 0;        // only tiny batches have units without tiles
-    const int Ttot = info.w;
-    auto empty_unit = [&](int u) -> bool {             // the main kernel's unit schedule, by arithmetic
-        int at = 0, len = 0;
-        const int p = u / G, j = u - p * G;
-#pragma unroll
-        for (int pp = 0; pp < kPhases; ++pp) {
-            const int step = phase_step(Ttot - at, pp, G);
-            if (pp == p) len = step;
-            at += step;
-        }
-        return (int)((long long)len * j / G) == (int)((long long)len * (j + 1) / G);
-    };
     // group g takes units u_first + g, u_first + g + kFinishGroups, ...: all loads of a thread are independent
     float M = -INFINITY, Lsum = 0.f;
     float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
 #pragma unroll 4
     for (int c = u_first + grp; c <= u_last; c += kFinishGroups) {
-        if (maybe_empty && empty_unit(c)) continue;                            // an empty unit wrote nothing
         const float* src = prm.ws + (((size_t)c * 2 + (c == u_first ? first_slot : 0)) * NREP + r) * (D + 2);
         const float2 ml = __ldcg(reinterpret_cast<const float2*>(src));
         const float2 x01 = __ldcg(reinterpret_cast<const float2*>(src + 2 + d4));   // rows are 8-byte aligned
         const float2 x23 = __ldcg(reinterpret_cast<const float2*>(src + 4 + d4));
+        if (ml.x == -INFINITY) continue;               // an empty unit's neutral record, or a piece that saw no key: the rest of the record is not defined
         const float Mn = fmaxf(M, ml.x);
-        const float a = (Mn == -INFINITY) ? 0.f : exp2f(M - Mn), w = (ml.x == -INFINITY) ? 0.f : exp2f(ml.x - Mn);
+        const float a = (M == -INFINITY) ? 0.f : exp2f(M - Mn), w = exp2f(ml.x - Mn);
         Lsum = Lsum * a + ml.y * w;
         acc.x = acc.x * a + x01.x * w; acc.y = acc.y * a + x01.y * w;
         acc.z = acc.z * a + x23.x * w; acc.w = acc.w * a + x23.y * w;
