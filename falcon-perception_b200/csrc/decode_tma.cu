@@ -61,7 +61,10 @@ constexpr int kThreads = (kConsumerWarps + 2) * 32;
 #define FPKV_PHASES 5
 #endif
 constexpr int kPhases = FPKV_PHASES;           // unit sizes halve from phase to phase
-constexpr int kSmallPhaseTiles = 8;            // a remainder of at most this many tiles per unit is not halved again
+#ifndef FPKV_SMALL_PHASE_TILES
+#define FPKV_SMALL_PHASE_TILES 8
+#endif
+constexpr int kSmallPhaseTiles = FPKV_SMALL_PHASE_TILES;   // a remainder of at most this many tiles per unit is not halved again
 // Tiles taken by phase p when `rem` are left: half of them, or all of them in the last phase and when halving
 // would leave units of a tile or two (small batches: each piece of a segment costs a partial and a merge step).
 __device__ __forceinline__ int phase_step(int rem, int p, int G) {
