@@ -389,8 +389,9 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_consta
     int my_slot = 0, my_extent = 0;
     if (is_softmax && t0 + row < prm.L) {
         const long long s = prm.batch_idx[t0 + row];
+        const int e = prm.extent[t0 + row];                // both loads in flight together
         if (s < 0 || s >= prm.max_batch) raise_status(prm.status, FPKV_STATUS_BAD_SLOT);
-        else { my_slot = (int)s; my_extent = s > 0 ? prm.extent[t0 + row] : 0; }
+        else { my_slot = (int)s; my_extent = s > 0 ? e : 0; }
         if (my_extent < 0) my_extent = 0;
     }
     {
@@ -403,6 +404,16 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_consta
     __syncthreads();
     tc_fence_after();
     const int slot = max(max(warp_red[0], warp_red[1]), max(warp_red[2], warp_red[3]));
+    // The copy warp starts as early as it can: the query tile depends on nothing (issued now), the first K / V
+    // tile only on the sequence's first page id (load started now, used after the next barrier), so that the first
+    // Q.K^T does not wait for the rest of the set-up.
+    const bool early = warp == kLoadWarp && lane == 0 && slot > 0;
+    long long early_pg = -1;
+    if (early) {
+        bar_expect_tx(q_full, heads * kTileBytes);
+        for (int g = 0; g < heads; ++g) tma_4d(s32(q_s + g * kTileBytes), &q_map, 0, t0, 0, hq0 + g, q_full);
+        early_pg = prm.page_table[(long long)slot * prm.n_pages];
+    }
     if (my_slot != 0 && my_slot != slot) {                 // two live sequences in one query tile: not supported
         raise_status(prm.status, FPKV_STATUS_BAD_SLOT);
         my_extent = 0;
@@ -417,6 +428,13 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_consta
     __syncthreads();
     int n_tiles = (max(max(warp_red[4], warp_red[5]), max(warp_red[6], warp_red[7])) + kTileN - 1) / kTileN;
     if (n_tiles > kMaxKeyTiles) { if (tid == 0) raise_status(prm.status, FPKV_STATUS_BAD_POS); n_tiles = kMaxKeyTiles; }
+    if (early && n_tiles > 0) {                            // first K and V tile (an unmapped first page is masked later)
+        const int row0 = hkv * prm.rows_per_plane + ((early_pg >= 0 && early_pg < prm.n_pages) ? (int)early_pg : 0) * kPage;
+        bar_expect_tx(k_full0, kTileBytes);
+        tma_3d(s32(k_s), &kv_map, 0, row0, 0, k_full0);
+        bar_expect_tx(v_full0, kTileBytes);
+        tma_3d(s32(v_s), &kv_map, 0, row0 + prm.Hkv * prm.rows_per_plane, 0, v_full0);
+    }
     // page ids of all key tiles, resolved once (coalesced) instead of one dependent load per tile
     for (int j = tid; j < n_tiles; j += kPrefillThreads) {
         const long long trow = (long long)slot * prm.n_pages;
@@ -435,9 +453,11 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_consta
     if (warp == kLoadWarp) {
         // ============================== TMA producer ========================
         if (lane == 0 && n_tiles > 0) {
-            bar_expect_tx(q_full, heads * kTileBytes);
-            for (int g = 0; g < heads; ++g) tma_4d(s32(q_s + g * kTileBytes), &q_map, 0, t0, 0, hq0 + g, q_full);
-            for (int j = 0; j < n_tiles; ++j) {
+            if (!early) {
+                bar_expect_tx(q_full, heads * kTileBytes);
+                for (int g = 0; g < heads; ++g) tma_4d(s32(q_s + g * kTileBytes), &q_map, 0, t0, 0, hq0 + g, q_full);
+            }
+            for (int j = early ? 1 : 0; j < n_tiles; ++j) {
                 const int st = j % kStages;
                 const uint32_t ph = (j / kStages) & 1u;
                 if (!bar_wait(k_empty0 + 8 * st, ph ^ 1u, abort_flag)) { alive = false; break; }
@@ -685,6 +705,9 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_consta
     // ---- teardown: everyone meets here, then the allocating warp frees TMEM ---
     tc_fence_before();
     __syncthreads();
+    if (early && n_tiles == 0) {                          // the query tile was requested before it turned out that no row sees a key
+        for (uint32_t k = 0; k < (1u << 20) && !bar_try(q_full, 0); ++k) {}
+    }
     if (warp == kLoadWarp && lane == 0 && *abort_flag) {
         // copies still in flight target this CTA's shared memory: give them a bounded time to land
         for (int s = 0; s < kStages; ++s)
