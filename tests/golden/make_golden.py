@@ -4,6 +4,8 @@ Run from the repository root, in a container that has the reference checkout:
 
     TORCHDYNAMO_DISABLE=1 python tests/golden/make_golden.py [/path/to/reference]
 
+(default: $FALCON_PERCEPTION_SRC, else a `reference` checkout beside this repository)
+
 The reference (tiiuae/Falcon-Perception) is imported read-only and driven on
 the CPU in fp32 through its own code: ``PagedKVCache`` for the allocator and
 the two append paths, ``PagedInferenceEngine.get_decoding_block_mask`` +
@@ -37,7 +39,7 @@ import numpy as np
 import torch
 
 ROOT = os.path.dirname(os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
-REF = sys.argv[1] if len(sys.argv) > 1 else "/root/reference"
+REF = sys.argv[1] if len(sys.argv) > 1 else os.environ.get("FALCON_PERCEPTION_SRC", os.path.join(os.path.dirname(ROOT), "reference"))
 sys.path.insert(0, REF)
 sys.path.insert(0, os.path.join(ROOT, "falcon-perception_b200"))
 sys.path.insert(0, ROOT)
