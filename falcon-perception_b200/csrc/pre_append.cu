@@ -68,7 +68,11 @@ template <> __device__ __forceinline__ void round_pair<__nv_bfloat16>(float a, f
 
 template <typename T, int E> struct alignas(16) Row { T v[E]; };   // E elements of one lane, moved as 16-byte vectors
 
-constexpr int kLanesPerRow = 8;
+#ifndef FPKV_LANES_PER_ROW
+#define FPKV_LANES_PER_ROW 8
+#endif
+constexpr int kLanesPerRow = FPKV_LANES_PER_ROW;        // lanes that share one head row
+constexpr int kRowsPerWarp = 32 / kLanesPerRow;
 
 template <typename T, int D, typename PosT>
 __global__ void __launch_bounds__(256)
@@ -85,7 +89,7 @@ pre_append_kernel(const PreAppendParams prm)
     const PosT* pos = static_cast<const PosT*>(prm.pos);
     const unsigned rows_per_pass = gridDim.x * blockDim.x / kLanesPerRow;
     // whole warps stay in the loop together (shuffles below): rows past the end are computed on row 0 and dropped
-    const unsigned padded = (total + 3u) / 4u * 4u;
+    const unsigned padded = (total + kRowsPerWarp - 1u) / kRowsPerWarp * kRowsPerWarp;
     for (unsigned w0 = (blockIdx.x * blockDim.x + threadIdx.x) / kLanesPerRow; w0 < padded; w0 += rows_per_pass) {
         const bool live = w0 < total;
         const unsigned w = live ? w0 : 0u;
@@ -168,7 +172,8 @@ template <typename T, int D>
 int launch_typed(const PreAppendParams& prm, int pos_type, cudaStream_t stream)
 {
     const long long rows = (long long)prm.n_tok * (prm.Hq + 2 * prm.H_out);
-    long long blocks = (rows + 31) / 32;                   // 256 threads = 32 rows of eight lanes
+    const int rows_per_block = 256 / kLanesPerRow;
+    long long blocks = (rows + rows_per_block - 1) / rows_per_block;
     if (blocks > 148 * 8) blocks = 148 * 8;               // grid-stride beyond eight CTAs per SM
     if (pos_type == FPKV_I32) pre_append_kernel<T, D, int32_t><<<(unsigned)blocks, 256, 0, stream>>>(prm);
     else pre_append_kernel<T, D, int64_t><<<(unsigned)blocks, 256, 0, stream>>>(prm);
