@@ -357,7 +357,9 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_consta
     const uint32_t all_done0 = s32(bars + 13);             // [2] one per head
 
     const int tid = threadIdx.x, warp = tid / 32, lane = tid % 32;
-    const int t0 = blockIdx.x * kTileM;                    // first packed token of the query tile
+    // Query tiles are taken from the end of the packed row backwards: under a causal mask the later tiles of a
+    // sequence see more keys, and the long CTAs should not be the last ones to start.
+    const int t0 = (int)(gridDim.x - 1 - blockIdx.x) * kTileM;   // first packed token of the query tile
     const int heads = prm.heads_per_cta;                   // 1 or 2 query heads of one stored head
     const int hq0 = blockIdx.y * heads;
     const int hkv = hq0 / (prm.Hq / prm.Hkv);
