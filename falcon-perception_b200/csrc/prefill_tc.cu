@@ -289,7 +289,7 @@ __device__ unsigned long long g_phase_sums[16];
 #ifdef FPKV_FINE
 // Development aid: cycle stamps of one CTA for two consecutive key tiles, [tile - 3][slot].
 __device__ long long g_fine[2][64];
-#define FT(j, slot) do { if (((j) == 3 || (j) == 4) && blockIdx.x == 3 && blockIdx.y == 2) g_fine[(j) - 3][slot] = clock64(); } while (0)
+#define FT(j, slot) do { if (((j) == 3 || (j) == 4) && blockIdx.y == 3 && blockIdx.x == 2) g_fine[(j) - 3][slot] = clock64(); } while (0)
 #else
 #define FT(j, slot) do { } while (0)
 #endif
@@ -357,11 +357,11 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_consta
     const uint32_t all_done0 = s32(bars + 13);             // [2] one per head
 
     const int tid = threadIdx.x, warp = tid / 32, lane = tid % 32;
-    // Query tiles are taken from the end of the packed row backwards: under a causal mask the later tiles of a
-    // sequence see more keys, and the long CTAs should not be the last ones to start.
-    const int t0 = (int)(gridDim.x - 1 - blockIdx.x) * kTileM;   // first packed token of the query tile
+    // Query tiles are taken from the end of the packed row backwards, all head pairs of a tile before the next tile:
+    // under a causal mask the later tiles of a sequence see more keys, and the long CTAs should start first.
+    const int t0 = (int)(gridDim.y - 1 - blockIdx.y) * kTileM;   // first packed token of the query tile
     const int heads = prm.heads_per_cta;                   // 1 or 2 query heads of one stored head
-    const int hq0 = blockIdx.y * heads;
+    const int hq0 = blockIdx.x * heads;
     const int hkv = hq0 / (prm.Hq / prm.Hkv);
     const bool is_softmax = warp < 2 * kSoftmaxWarps;
 
@@ -812,7 +812,8 @@ int launch_prefill_tc(const PoolView& pv, int layer, void* out, float* lse, cons
     prm.is_bf16 = pv.dtype == FPKV_BF16;
     prm.heads_per_cta = ((Hq / pv.H) % 2 == 0) ? 2 : 1;
     prm.epi = epi;
-    dim3 grid((L + kTileM - 1) / kTileM, Hq / prm.heads_per_cta);
+    if ((L + kTileM - 1) / kTileM > 65535) return FPKV_ESHAPE;
+    dim3 grid(Hq / prm.heads_per_cta, (L + kTileM - 1) / kTileM);
     if (pv.dtype == FPKV_BF16) {
         auto kern = prefill_tc_kernel<__nv_bfloat16>;
         if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, kPrefillSmem) != cudaSuccess) return FPKV_ELAUNCH;
