@@ -52,7 +52,9 @@ int make_epilogue(const fpkv_epilogue* e, int n_q_heads, Epilogue* out) {
     out->sinks = nullptr; out->sinks_dtype = FPKV_F32; out->token_major = 0;
     if (e == nullptr) return FPKV_OK;
     if (e->sinks != nullptr && esize_of(e->sinks_dtype) == 0) return FPKV_EDTYPE;
-    (void)n_q_heads;
+    // the kernels read sinks[hq] with 2- or 4-byte loads for hq < n_q_heads
+    if (e->sinks != nullptr && (n_q_heads <= 0 || reinterpret_cast<uintptr_t>(e->sinks) % esize_of(e->sinks_dtype)))
+        return FPKV_EALIGN;
     out->sinks = e->sinks; out->sinks_dtype = e->sinks_dtype; out->token_major = e->token_major != 0;
     return FPKV_OK;
 }
@@ -66,9 +68,61 @@ int check_arch() {
 
 }  // namespace
 
+namespace fpkv {
+
+// fpkv_decode_attn behind its argument checks; `clear_counters` zeroes the work counters at the head of the
+// workspace on the stream first (for a workspace whose previous contents are not known to be clean), after
+// every check has passed, so that a refused call enqueues nothing.
+int decode_attn_checked(const fpkv_pool* pool, int32_t layer, void* out, float* lse, const void* q,
+                        int64_t q_stride_b, int64_t q_stride_h, const int64_t* batch_idx, const void* input_pos,
+                        int32_t pos_type, int32_t B, int32_t n_q_heads, float sm_scale, void* workspace,
+                        size_t workspace_bytes, int32_t flags, const fpkv_epilogue* epilogue, int32_t* status,
+                        void* stream, bool clear_counters)
+{
+    PoolView pv;
+    int rc = make_view(pool, layer, &pv);
+    if (rc) return rc;
+    Epilogue epi;
+    if ((rc = make_epilogue(epilogue, n_q_heads, &epi))) return rc;
+    if (B < 0 || n_q_heads <= 0 || (pos_type != FPKV_I32 && pos_type != FPKV_I64)) return FPKV_EINVAL;
+    if (n_q_heads % pv.H) return FPKV_ESHAPE;
+    if (B == 0) return FPKV_OK;
+    if (out == nullptr || lse == nullptr || batch_idx == nullptr || input_pos == nullptr || workspace == nullptr)
+        return FPKV_EINVAL;
+    if ((rc = check_rows(q, q_stride_b, q_stride_h, pv.esize))) return rc;
+    if (!aligned16(out) || !aligned16(workspace)) return FPKV_EALIGN;
+    const int which = flags & 3;
+    const bool tma_ok = decode_tma_supported(pv, n_q_heads);
+    if (which == FPKV_DECODE_TMA && !tma_ok) return FPKV_ESHAPE;
+    const bool use_tma = which == FPKV_DECODE_TMA || (which == FPKV_DECODE_AUTO && tma_ok);
+    // both kernels leave the counter words at the head of the workspace alone or at zero
+    const size_t need = use_tma ? decode_tma_workspace_bytes(n_q_heads, pv.H, pv.D)
+                                : decode_portable_workspace_bytes(B, n_q_heads, pv.D) + kCounterBytes;
+    if (workspace_bytes < need) return FPKV_EWORKSPACE;
+    if ((rc = check_arch())) return rc;
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    if (clear_counters && cudaMemsetAsync(workspace, 0, 1024, s) != cudaSuccess) return FPKV_ELAUNCH;
+    return use_tma ? launch_decode_tma(pv, layer, out, lse, q, q_stride_b, q_stride_h, batch_idx, input_pos,
+                                       pos_type, B, n_q_heads, sm_scale, workspace, epi, status, s,
+                                       (flags & FPKV_DECODE_AFTER_APPEND) != 0)
+                   : launch_decode_portable(pv, layer, out, lse, q, q_stride_b, q_stride_h, batch_idx,
+                                            input_pos, pos_type, B, n_q_heads, sm_scale,
+                                            static_cast<char*>(workspace) + kCounterBytes, epi, status, s);
+}
+
+}  // namespace fpkv
+
 extern "C" {
 
-int fpkv_version(void) { return 100; }
+int fpkv_version(void) { return 200; }
+
+// The hash of the sources this library was compiled from (the build script passes it in); the marker
+// prefix lets the build script find it in the file without loading the library.
+#ifndef FPKV_SRC_HASH
+#define FPKV_SRC_HASH "0000000000000000"
+#endif
+static const char kBuildId[] = "fpkv-build-id:" FPKV_SRC_HASH;
+const char* fpkv_build_id(void) { return kBuildId + 14; }
 
 const char* fpkv_strerror(int code) {
     switch (code) {
@@ -162,16 +216,20 @@ int fpkv_gather(const fpkv_pool* pool, int32_t layer, int32_t slot, int32_t n_to
     return launch_gather(pv, layer, slot, n_tokens, k_out, v_out, status, static_cast<cudaStream_t>(stream));
 }
 
-int fpkv_decode_workspace_bytes(const fpkv_pool* pool, int32_t B, int32_t n_q_heads, size_t* bytes)
+int fpkv_decode_workspace_bytes(const fpkv_pool* pool, int32_t B, int32_t n_q_heads, int32_t flags, size_t* bytes)
 {
     PoolView pv;
     int rc = make_view(pool, 0, &pv);
     if (rc) return rc;
     if (bytes == nullptr || B < 0 || n_q_heads <= 0) return FPKV_EINVAL;
     if (n_q_heads % pv.H) return FPKV_ESHAPE;
-    size_t a = decode_portable_workspace_bytes(B, n_q_heads, pv.D) + kCounterBytes;
-    size_t b = decode_tma_workspace_bytes(n_q_heads, pv.H, pv.D);
-    *bytes = (a > b ? a : b) + 256;
+    // sized for the kernel that `flags` selects, exactly as fpkv_decode_attn checks it
+    const int which = flags & 3;
+    const bool tma_ok = decode_tma_supported(pv, n_q_heads);
+    if (which == FPKV_DECODE_TMA && !tma_ok) return FPKV_ESHAPE;
+    const bool use_tma = which == FPKV_DECODE_TMA || (which == FPKV_DECODE_AUTO && tma_ok);
+    *bytes = (use_tma ? decode_tma_workspace_bytes(n_q_heads, pv.H, pv.D)
+                      : decode_portable_workspace_bytes(B, n_q_heads, pv.D) + kCounterBytes) + 256;
     return FPKV_OK;
 }
 
@@ -181,49 +239,27 @@ int fpkv_decode_attn(const fpkv_pool* pool, int32_t layer, void* out, float* lse
                      size_t workspace_bytes, int32_t flags, const fpkv_epilogue* epilogue, int32_t* status,
                      void* stream)
 {
-    PoolView pv;
-    int rc = make_view(pool, layer, &pv);
-    if (rc) return rc;
-    Epilogue epi;
-    if ((rc = make_epilogue(epilogue, n_q_heads, &epi))) return rc;
-    if (B < 0 || n_q_heads <= 0 || (pos_type != FPKV_I32 && pos_type != FPKV_I64)) return FPKV_EINVAL;
-    if (n_q_heads % pv.H) return FPKV_ESHAPE;
-    if (B == 0) return FPKV_OK;
-    if (out == nullptr || lse == nullptr || batch_idx == nullptr || input_pos == nullptr || workspace == nullptr)
-        return FPKV_EINVAL;
-    if ((rc = check_rows(q, q_stride_b, q_stride_h, pv.esize))) return rc;
-    if (!aligned16(out) || !aligned16(workspace)) return FPKV_EALIGN;
-    const int which = flags & 3;
-    const bool tma_ok = decode_tma_supported(pv, n_q_heads);
-    if (which == FPKV_DECODE_TMA && !tma_ok) return FPKV_ESHAPE;
-    const bool use_tma = which == FPKV_DECODE_TMA || (which == FPKV_DECODE_AUTO && tma_ok);
-    // both kernels leave the counter words at the head of the workspace alone or at zero
-    const size_t need = use_tma ? decode_tma_workspace_bytes(n_q_heads, pv.H, pv.D)
-                                : decode_portable_workspace_bytes(B, n_q_heads, pv.D) + kCounterBytes;
-    if (workspace_bytes < need) return FPKV_EWORKSPACE;
-    if ((rc = check_arch())) return rc;
-    cudaStream_t s = static_cast<cudaStream_t>(stream);
-    return use_tma ? launch_decode_tma(pv, layer, out, lse, q, q_stride_b, q_stride_h, batch_idx, input_pos,
-                                       pos_type, B, n_q_heads, sm_scale, workspace, epi, status, s,
-                                       (flags & FPKV_DECODE_AFTER_APPEND) != 0)
-                   : launch_decode_portable(pv, layer, out, lse, q, q_stride_b, q_stride_h, batch_idx,
-                                            input_pos, pos_type, B, n_q_heads, sm_scale,
-                                            static_cast<char*>(workspace) + kCounterBytes, epi, status, s);
+    return fpkv::decode_attn_checked(pool, layer, out, lse, q, q_stride_b, q_stride_h, batch_idx, input_pos, pos_type, B,
+                                     n_q_heads, sm_scale, workspace, workspace_bytes, flags, epilogue, status, stream,
+                                     /*clear_counters=*/false);
 }
 
-int fpkv_table_update(const fpkv_pool* pool, const int32_t* ops, int32_t n_ops, int32_t* status, void* stream)
+int fpkv_alloc_step(const fpkv_pool* pool, const fpkv_alloc_state* state, const int32_t* ops, int32_t n_ops,
+                    int32_t* status, void* stream)
 {
     // only the tables matter here: any page size or head_dim is fine
     if (pool == nullptr || pool->page_table == nullptr || pool->physical_to_logical == nullptr) return FPKV_EINVAL;
+    if (state == nullptr || state->free_pages == nullptr || state->free_slots == nullptr || state->counts == nullptr)
+        return FPKV_EINVAL;
     if (pool->n_pages <= 0 || pool->max_batch_size <= 0 || n_ops < 0) return FPKV_EINVAL;
     if (n_ops == 0) return FPKV_OK;
     if (ops == nullptr) return FPKV_EINVAL;
     if (!aligned16(ops)) return FPKV_EALIGN;
     const int rc = check_arch();
     if (rc) return rc;
-    return launch_table_update(const_cast<int64_t*>(pool->page_table), const_cast<int64_t*>(pool->physical_to_logical),
-                               pool->n_pages, pool->max_batch_size, ops, n_ops, status,
-                               static_cast<cudaStream_t>(stream));
+    return launch_alloc_step(const_cast<int64_t*>(pool->page_table), const_cast<int64_t*>(pool->physical_to_logical),
+                             pool->n_pages, pool->max_batch_size, state->free_pages, state->free_slots, state->counts,
+                             ops, n_ops, status, static_cast<cudaStream_t>(stream));
 }
 
 int fpkv_prefill_attn(const fpkv_pool* pool, int32_t layer, void* out, float* lse, const void* q,

@@ -101,8 +101,14 @@ int launch_decode_tma(const PoolView& pv, int layer, void* out, float* lse, cons
 int launch_prefill_portable(const PoolView& pv, int layer, void* out, float* lse, const void* q, long long q_stride_h,
                             long long q_stride_t, const int64_t* batch_idx, const int32_t* extent, int L, int Hq,
                             float sm_scale, const Epilogue& epi, int32_t* status, cudaStream_t stream);
-int launch_table_update(int64_t* page_table, int64_t* p2l, int n_pages, int max_batch, const int32_t* ops,
-                        int n_ops, int32_t* status, cudaStream_t stream);
+int launch_alloc_step(int64_t* page_table, int64_t* p2l, int n_pages, int max_batch, int32_t* free_pages,
+                      int32_t* free_slots, int32_t* counts, const int32_t* ops, int n_ops, int32_t* status,
+                      cudaStream_t stream);
+int decode_attn_checked(const fpkv_pool* pool, int32_t layer, void* out, float* lse, const void* q,
+                        int64_t q_stride_b, int64_t q_stride_h, const int64_t* batch_idx, const void* input_pos,
+                        int32_t pos_type, int32_t B, int32_t n_q_heads, float sm_scale, void* workspace,
+                        size_t workspace_bytes, int32_t flags, const fpkv_epilogue* epilogue, int32_t* status,
+                        void* stream, bool clear_counters);
 bool prefill_tc_supported(const PoolView& pv, int Hq);
 int launch_prefill_tc(const PoolView& pv, int layer, void* out, float* lse, const void* q, long long q_stride_h,
                       long long q_stride_t, const int64_t* batch_idx, const int32_t* extent, int L, int Hq,

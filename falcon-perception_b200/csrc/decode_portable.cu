@@ -165,7 +165,7 @@ decode_portable_merge_kernel(const float* __restrict__ ws, int S, T* __restrict_
 }
 
 size_t decode_portable_workspace_bytes(int B, int Hq, int D) {
-    return (size_t)B * Hq * kPortableMaxSplits * (D + 2) * sizeof(float);
+    return (size_t)B * Hq * portable_splits(B, Hq) * (D + 2) * sizeof(float);
 }
 
 template <typename T, int D, typename PosT>

@@ -59,9 +59,9 @@ extern "C" int fpkv_decode_attn_static(const fpkv_pool* pool, int32_t layer, voi
     int rc = static_scratch_address(&scratch);
     if (rc != FPKV_OK) return rc;
     // The previous call's leftovers are harmless except for the work counter at the head, which the
-    // kernel expects at zero (a call that timed out may have left it dirty).
-    if (cudaMemsetAsync(scratch, 0, 1024, static_cast<cudaStream_t>(stream)) != cudaSuccess) return FPKV_ELAUNCH;
-    return fpkv_decode_attn(pool, layer, out, lse, q, q_stride_b, q_stride_h, batch_idx, input_pos, pos_type, B,
-                            n_q_heads, sm_scale, scratch, (size_t)FPKV_STATIC_SCRATCH_BYTES, FPKV_DECODE_TMA,
-                            nullptr, status, stream);
+    // kernel expects at zero (a call that timed out may have left it dirty): it is cleared on the stream
+    // once every argument check has passed, so a refused call enqueues nothing.
+    return fpkv::decode_attn_checked(pool, layer, out, lse, q, q_stride_b, q_stride_h, batch_idx, input_pos, pos_type, B,
+                                     n_q_heads, sm_scale, scratch, (size_t)FPKV_STATIC_SCRATCH_BYTES, FPKV_DECODE_TMA,
+                                     nullptr, status, stream, /*clear_counters=*/true);
 }

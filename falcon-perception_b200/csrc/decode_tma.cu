@@ -57,10 +57,10 @@ namespace {
 constexpr int kConsumerWarps = 8;
 constexpr int kIssueWarp = kConsumerWarps, kScoutWarp = kConsumerWarps + 1;
 constexpr int kThreads = (kConsumerWarps + 2) * 32;
-#ifndef FPKV_PHASES
-#define FPKV_PHASES 5
+#ifndef FPKV_DECODE_PHASES
+#define FPKV_DECODE_PHASES 5
 #endif
-constexpr int kPhases = FPKV_PHASES;           // unit sizes halve from phase to phase
+constexpr int kPhases = FPKV_DECODE_PHASES;           // unit sizes halve from phase to phase
 #ifndef FPKV_SMALL_PHASE_TILES
 #define FPKV_SMALL_PHASE_TILES 8
 #endif
@@ -182,18 +182,6 @@ struct Params {
     Epilogue epi;
 };
 
-#ifdef FPKV_PROFILE
-// Development aid: per-CTA time stamps (kernel entry, first unit started, last piece merged, exit).
-__device__ unsigned long long g_cta_times[256][12];
-__device__ __forceinline__ unsigned long long gtime() {
-    unsigned long long t; asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t)); return t;
-}
-#define FPKV_STAMP(i) do { if (tid == 0) g_cta_times[blockIdx.x][i] = gtime(); } while (0)
-#define FPKV_STAMP_LANE0(i) do { if (lane == 0) g_cta_times[blockIdx.x][i] = gtime(); } while (0)
-#else
-#define FPKV_STAMP_LANE0(i) do { } while (0)
-#define FPKV_STAMP(i) do { } while (0)
-#endif
 
 // Unit schedule.  Phase p covers half of the tiles left after phase p-1 (the last one all of them) and
 // is cut into G equal units; unit id u = p * G + j.  ub[u] = first flat tile of unit u, ub[NU] = total;
@@ -245,10 +233,6 @@ decode_tma_kernel(const __grid_constant__ CUtensorMap tmap, const __grid_constan
     // preceding kernel is complete.  Behind this library's append kernel (which writes only the pool)
     // everything up to the first pool read may overlap it; the issue warp waits before its first copy.
     if (!prm.after_append) asm volatile("griddepcontrol.wait;" ::: "memory");
-    FPKV_STAMP(0);
-#ifdef FPKV_PROFILE
-    if (tid == 0) for (int i = 8; i < 12; ++i) g_cta_times[blockIdx.x][i] = 0;
-#endif
     const uint32_t full0 = smem_u32(bars), empty0 = full0 + 8 * NS;
     const uint32_t dfull0 = empty0 + 8 * NS, dempty0 = dfull0 + 8 * kDescBlocks;
     const uint32_t ufull0 = dempty0 + 8 * kDescBlocks, uempty0 = ufull0 + 8 * kUnitQueue;
@@ -404,7 +388,6 @@ decode_tma_kernel(const __grid_constant__ CUtensorMap tmap, const __grid_constan
                 else give_up();
             }
         }
-        FPKV_STAMP_LANE0(4);
         return;
     }
 
@@ -458,7 +441,6 @@ decode_tma_kernel(const __grid_constant__ CUtensorMap tmap, const __grid_constan
                 for (uint32_t k = 0; k < kSpinLimit && !mbar_try_wait(full0 + 8 * s, ph); ++k) {}
             }
         }
-        FPKV_STAMP_LANE0(6);
         return;
     }
 
@@ -508,7 +490,6 @@ decode_tma_kernel(const __grid_constant__ CUtensorMap tmap, const __grid_constan
         }
         if (u < 0) break;
         const int r0 = ub[u], r1 = ub[u + 1];
-        if (qn == 1) FPKV_STAMP(1);
 
         for (int t = r0; t < r1 && alive; ++piece) {
             // ---- piece = part of one (b, h) segment inside this unit -------
@@ -606,6 +587,21 @@ decode_tma_kernel(const __grid_constant__ CUtensorMap tmap, const __grid_constan
                 if (!mbar_wait(full0 + 8 * s, ph, abort_flag)) { alive = false; break; }
                 if (valid) {
                     const uint32_t vt = smem_u32(ring + s * kTile);
+                    // Rows of this warp's group past the row's last key were fetched with the group but never
+                    // appended: the pool may hold anything there, and 0 x NaN would poison the sum.  Clear them
+                    // in shared memory (only the group that holds a sequence's last key ever does this).  The
+                    // slot's next user is a tensor copy (async proxy), hence the proxy fence behind the stores.
+                    const int first_bad = (int)(n_keys - (long long)pg * P) - warp * RW;   // >= 1: the group was fetched
+                    if (first_bad < RW) {
+                        constexpr int kChunks = (D / 64) * 8;               // 16-byte pieces of one token row
+                        for (int i = lane; i < (RW - first_bad) * kChunks; i += 32) {
+                            const int row = warp * RW + first_bad + i / kChunks, c = i % kChunks;
+                            asm volatile("st.shared.v4.b32 [%0], {%1, %1, %1, %1};"
+                                         ::"r"(vt + (c >> 3) * (P * 128) + row * 128 + ((c & 7) << 4)), "r"(0u) : "memory");
+                        }
+                        asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+                        __syncwarp();
+                    }
 #pragma unroll
                     for (int ks = 0; ks < RW / 16; ++ks) {              // 16 tokens per k-step
                         const int row = warp * RW + ks * 16 + (lane & 15);   // matrices 0/2: tokens 0-7, 1/3: 8-15
@@ -643,7 +639,6 @@ decode_tma_kernel(const __grid_constant__ CUtensorMap tmap, const __grid_constan
                     *reinterpret_cast<float2*>(dst + 2 + n * 8 + 2 * tq) = make_float2(o[n][0], o[n][1]);
             }
             if (!consumer_bar()) { alive = false; break; }
-            FPKV_STAMP(2);
             for (int e = tid; e < NREP * D; e += kConsumerWarps * 32) {
                 const int r = e / D, d = e - r * D;
                 float M = -INFINITY;
@@ -676,7 +671,6 @@ decode_tma_kernel(const __grid_constant__ CUtensorMap tmap, const __grid_constan
         }
     }
     if (!alive) { if (lane == 0) give_up(); return; }
-    FPKV_STAMP(3);
 }
 
 // Second kernel, one CTA per (row b, stored head h) segment.  A segment that unit boundaries cut is
@@ -684,9 +678,6 @@ decode_tma_kernel(const __grid_constant__ CUtensorMap tmap, const __grid_constan
 // by the main kernel.  Launched with programmatic stream serialisation: its CTAs may become resident
 // while the main grid is still busy and wait for it in griddepcontrol.wait.  After that it is two
 // rounds of loads (the row's tile counts, then all partials at once) and a store.
-#ifdef FPKV_PROFILE
-__device__ unsigned long long g_fin_times[1024][3];
-#endif
 constexpr int kFinishGroups = 4;                   // thread groups that split a segment's units among them
 
 template <typename T, int D, int NREP>
@@ -702,15 +693,9 @@ decode_tma_finish_kernel(const Params prm, int G)
     const int r = v4 / (D / 4), d4 = (v4 % (D / 4)) * 4;
     T* out = reinterpret_cast<T*>(prm.out);
     asm volatile("griddepcontrol.wait;" ::: "memory");
-#ifdef FPKV_PROFILE
-    if (threadIdx.x == 0) { g_fin_times[blockIdx.x % 1024][0] = gtime(); g_fin_times[blockIdx.x % 1024][1] = 0; g_fin_times[blockIdx.x % 1024][2] = 0; }
-#endif
     asm volatile("griddepcontrol.launch_dependents;");   // a following kernel launched the same way may take its seats
     const int4 info = __ldcg(prm.seginfo + blockIdx.x);
     const int u_first = info.x, u_last = info.y, first_slot = info.z & 1;
-#ifdef FPKV_PROFILE
-    if (threadIdx.x == 0) g_fin_times[blockIdx.x % 1024][1] = gtime();
-#endif
     if (u_first == u_last) return;                     // inside one unit (written by the main kernel) or no tile
     // group g takes units u_first + g, u_first + g + kFinishGroups, ...: all loads of a thread are independent
     float M = -INFINITY, Lsum = 0.f;
@@ -757,9 +742,6 @@ decode_tma_finish_kernel(const Params prm, int G)
         dst[2] = gated_out<T>(o.z * inv, gate, on); dst[3] = gated_out<T>(o.w * inv, gate, on);
         if (d4 == 0) prm.lse[(size_t)b * Hq + hq] = lse_nat;
     }
-#ifdef FPKV_PROFILE
-    if (threadIdx.x == 0) g_fin_times[blockIdx.x % 1024][2] = gtime();
-#endif
 }
 
 // ------------------------------------------------------------------- host
@@ -841,12 +823,6 @@ int launch_shape(int D, int nrep, const CUtensorMap& map, const CUtensorMap& map
 
 }  // namespace
 
-#ifdef FPKV_PROFILE
-extern "C" __attribute__((visibility("default"))) int fpkv_debug_cta_times(unsigned long long* host_out) {
-    cudaMemcpyFromSymbol(host_out + 256 * 12, g_fin_times, sizeof(unsigned long long) * 1024 * 3);
-    return (int)cudaMemcpyFromSymbol(host_out, g_cta_times, sizeof(unsigned long long) * 256 * 12);
-}
-#endif
 
 bool decode_tma_supported(const PoolView& pv, int Hq)
 {

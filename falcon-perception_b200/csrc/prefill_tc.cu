@@ -236,12 +236,6 @@ __device__ __forceinline__ float ex2(float x) {
     return y;
 }
 
-#if defined(FPKV_CTA_SUMS)
-__device__ unsigned long long g_cta_sums[8];               // all CTAs: [0] entry->loop start, [1] loop, [2] loop end->exit, [3] count, [4] tiles, [5..7] parts of the exit phase
-__device__ __forceinline__ unsigned long long gtime_ns() {
-    unsigned long long t; asm volatile("mov.u64 %0, %globaltimer;" : "=l"(t)); return t;
-}
-#endif
 // 2^x for a pair of arguments on the FMA and integer pipes instead of the exponential unit, which is the narrow
 // resource of the softmax phase (16 results per clock per SM): round to the nearest integer with the
 // 1.5 * 2^23 trick, a degree-3 polynomial on the remainder in [-0.5, 0.5] (maximum relative error 7.5e-5, far
@@ -275,24 +269,6 @@ __device__ __forceinline__ F2 ex2_poly2(F2 x) {
     return r;
 }
 
-#ifdef FPKV_PHASES
-// Development aid: cycles per softmax phase, summed over all tiles of warp 0 of every CTA.
-__device__ unsigned long long g_phase_sums[16];
-#define PH_DECL long long ph_t = clock64(), ph_acc[8] = {0, 0, 0, 0, 0, 0, 0, 0}
-#define PH(i) do { const long long ph_n = clock64(); ph_acc[i] += ph_n - ph_t; ph_t = ph_n; } while (0)
-#define PH_DUMP do { if (tid == 0) { for (int i = 0; i < 8; ++i) atomicAdd(&g_phase_sums[i], (unsigned long long)ph_acc[i]); atomicAdd(&g_phase_sums[8], (unsigned long long)(n_tiles * heads)); } } while (0)
-#else
-#define PH_DECL do { } while (0)
-#define PH(i) do { } while (0)
-#define PH_DUMP do { } while (0)
-#endif
-#ifdef FPKV_FINE
-// Development aid: cycle stamps of one CTA for two consecutive key tiles, [tile - 3][slot].
-__device__ long long g_fine[2][64];
-#define FT(j, slot) do { if (((j) == 3 || (j) == 4) && blockIdx.y == 3 && blockIdx.x == 2) g_fine[(j) - 3][slot] = clock64(); } while (0)
-#else
-#define FT(j, slot) do { } while (0)
-#endif
 
 // S = Q K^T: eight K = 16 steps (32 bytes along the 128-byte swizzled rows, second 64-element half 16 KiB on), then
 // the commit that tells the softmax group.
@@ -365,10 +341,6 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_consta
     const int hkv = hq0 / (prm.Hq / prm.Hkv);
     const bool is_softmax = warp < 2 * kSoftmaxWarps;
 
-#if defined(FPKV_CTA_SUMS)
-    const unsigned long long cta_t0 = gtime_ns();
-    __shared__ unsigned long long cta_marks[6];           // [2] softmax loop done, [3] first epilogue done, [4] second epilogue done
-#endif
     // ---- prologue ----------------------------------------------------------
     if (tid == 0) {
         bar_init(q_full, 1);
@@ -428,9 +400,12 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_consta
         if (lane == 0 && warp < kSoftmaxWarps) warp_red[4 + warp] = ex;
     }
     __syncthreads();
-    int n_tiles = (max(max(warp_red[4], warp_red[5]), max(warp_red[6], warp_red[7])) + kTileN - 1) / kTileN;
+    const int max_extent = max(max(warp_red[4], warp_red[5]), max(warp_red[6], warp_red[7]));
+    int n_tiles = (max_extent + kTileN - 1) / kTileN;
     if (n_tiles > kMaxKeyTiles) { if (tid == 0) raise_status(prm.status, FPKV_STATUS_BAD_POS); n_tiles = kMaxKeyTiles; }
+    int k_requested = 0, v_requested = 0;                  // key / value tiles the copy thread has requested so far
     if (early && n_tiles > 0) {                            // first K and V tile (an unmapped first page is masked later)
+        k_requested = v_requested = 1;
         const int row0 = hkv * prm.rows_per_plane + ((early_pg >= 0 && early_pg < prm.n_pages) ? (int)early_pg : 0) * kPage;
         bar_expect_tx(k_full0, kTileBytes);
         tma_3d(s32(k_s), &kv_map, 0, row0, 0, k_full0);
@@ -465,9 +440,11 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_consta
                 if (!bar_wait(k_empty0 + 8 * st, ph ^ 1u, abort_flag)) { alive = false; break; }
                 bar_expect_tx(k_full0 + 8 * st, kTileBytes);
                 tma_3d(s32(k_s + st * kTileBytes), &kv_map, 0, page_row[j], 0, k_full0 + 8 * st);
+                k_requested = j + 1;
                 if (!bar_wait(v_empty0 + 8 * st, ph ^ 1u, abort_flag)) { alive = false; break; }
                 bar_expect_tx(v_full0 + 8 * st, kTileBytes);
                 tma_3d(s32(v_s + st * kTileBytes), &kv_map, 0, page_row[j] + prm.Hkv * prm.rows_per_plane, 0, v_full0 + 8 * st);
+                v_requested = j + 1;
             }
         }
     } else if (warp >= kMmaWarp && warp < kMmaWarp + heads) {
@@ -486,9 +463,6 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_consta
             const uint32_t v_lo = ((s32(v_s) & 0x3FFFF) >> 4) | (uint32_t)umma_desc(0, kHalfBytes, 1024);
             const uint32_t t_s = tmem + g * kTileN, t_o = tmem + 256 + g * kTileN;
             const uint32_t s_full = s_full0 + 8 * g, p_full = p_full0 + 8 * g;
-#if defined(FPKV_CTA_SUMS)
-            if (g == 0) cta_marks[0] = gtime_ns();
-#endif
             alive = bar_wait(q_full, 0, abort_flag) && bar_wait(k_full0, 0, abort_flag);
             if (alive) {
                 tc_fence_after();
@@ -511,10 +485,12 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_consta
                     umma_commit(k_empty0 + 8 * sn);
                 }
             }
-            if (alive) umma_commit(all_done0 + 8 * g);
-#if defined(FPKV_CTA_SUMS)
-            if (g == 0) cta_marks[1] = gtime_ns();
-#endif
+            umma_commit(all_done0 + 8 * g);                // arrives when every MMA this thread issued has completed
+            if (!alive) {
+                // Gave up: tensor memory is freed and the CTA's shared memory handed on after the last barrier
+                // below, so wait (bounded, ignoring the abort flag) for the MMAs already in the pipe.
+                for (uint32_t k = 0; k < kSpin && !bar_try(all_done0 + 8 * g, 0); ++k) {}
+            }
         }
     } else if (is_softmax) {
         // ============================== softmax warps =======================
@@ -538,8 +514,22 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_consta
             ++xslot;
             return fmaxf(mine, other);
         };
-        PH_DECL;
         for (int j = 0; j < n_tiles; ++j) {
+            // Value rows past the last key any row of this tile sees (the tail of the last key tile, or all of
+            // an unmapped page's stand-in) were fetched but possibly never appended: the pool may hold anything
+            // there, and 0 x NaN would poison O.  Clear them in shared memory before the first P.V of the tile
+            // (the tensor cores read shared memory through the async proxy, hence the proxy fence).
+            const int tile_rows = page_ok[j] ? min(kTileN, max_extent - j * kTileN) : 0;
+            if (tile_rows < kTileN) {
+                const int st = j % kStages;
+                if (alive && !bar_wait(v_full0 + 8 * st, (j / kStages) & 1u, abort_flag)) alive = false;
+                for (int i = tid; i < (kTileN - tile_rows) * 16; i += 2 * kSoftmaxWarps * 32) {
+                    const int r = tile_rows + (i >> 4), c = i & 15;         // token row, 16-byte piece of its 256 bytes
+                    *reinterpret_cast<uint4*>(v_s + st * kTileBytes + (c >> 3) * kHalfBytes + r * 128 + ((c & 7) << 4)) =
+                        make_uint4(0u, 0u, 0u, 0u);
+                }
+                asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+            }
             const int valid_row = page_ok[j] ? min(kTileN, my_extent - j * kTileN) : 0;   // visible keys of this row in the tile
             const int valid_cols = valid_row - colhalf * 64;                               // ... among this thread's 64 columns
             const bool full = __all_sync(0xffffffffu, valid_cols >= 64);
@@ -548,15 +538,12 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_consta
                 const uint32_t to = tmem + 256 + h * kTileN + lane_base + colhalf * 64;   // this thread's half of the O row
                 // s_full also tells that P.V of tile j-1 is complete: O is stable and the P columns are free.
                 // A wait that runs out does not leave the loop: every thread must reach the named barrier below.
-                PH(0);                                     // loop overhead, arrive of the previous tile
                 if (alive && !bar_wait(s_full0 + 8 * h, j & 1u, abort_flag)) alive = false;
                 tc_fence_after();
-                if (j == 0) PH(7); else PH(1);             // wait for the scores (first tile apart: it waits for the first copies)
                 uint32_t sv[2][32];
                 tmem_ld32_nowait(ts + colhalf * 64, sv[0]);
                 tmem_ld32_nowait(ts + colhalf * 64 + 32, sv[1]);
                 tmem_wait_ld();
-                PH(2);                                     // tensor-memory load
                 float mx;
                 if (full) {
                     float m2[2];
@@ -578,9 +565,7 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_consta
                 }
                 // after this barrier both threads of the row hold all their scores in registers, so the packed
                 // P columns may overwrite either thread's score columns
-                PH(3);                                     // local maximum
                 mx = exchange_max(mx) * prm.scale_log2;    // scale > 0: max commutes with it
-                PH(4);                                     // exchange with the partner thread
                 // raise the reference maximum only when this tile is far above it (both threads of a row decide alike)
                 const bool raise = mx > m_ref[h] + kRescaleThreshold || (m_ref[h] == -INFINITY && mx > -INFINITY);
                 if (__any_sync(0xffffffffu, raise)) {      // tensor-memory access is a whole-warp operation
@@ -629,20 +614,14 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_consta
                     }
                 };
                 if (full) probabilities(std::true_type{}); else probabilities(std::false_type{});
-                PH(5);                                     // raise check and exponentials
                 tmem_st32_nowait(ts + colhalf * 32, pk);
                 l[h] += (r4[0] + r4[1]) + (r4[2] + r4[3]);
                 asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
                 tc_fence_before();
                 __syncwarp();
                 if (lane == 0) bar_arrive(p_full0 + 8 * h);
-                PH(6);                                     // store, wait, fence, arrive
             }
         }
-        PH_DUMP;
-#if defined(FPKV_CTA_SUMS)
-        if (tid == 0) cta_marks[2] = gtime_ns();
-#endif
         // ---- epilogue: O / l -> out, lse --------------------------------------
         // Each thread holds 64 of the 128 output values of its row.  Storing them straight from registers
         // would touch 32 different lines per warp instruction; the two warps of a row quarter stage their 32
@@ -695,9 +674,6 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_consta
                 }
             }
             if (colhalf == 0 && t0 + row < prm.L) prm.lse[(size_t)hq * prm.L + t0 + row] = lse_nat;
-#if defined(FPKV_CTA_SUMS)
-            if (tid == 0) cta_marks[3 + h] = gtime_ns();
-#endif
         }
     }
     if (!alive && lane == 0) {
@@ -711,19 +687,16 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_consta
         for (uint32_t k = 0; k < (1u << 20) && !bar_try(q_full, 0); ++k) {}
     }
     if (warp == kLoadWarp && lane == 0 && *abort_flag) {
-        // copies still in flight target this CTA's shared memory: give them a bounded time to land
-        for (int s = 0; s < kStages; ++s)
-            for (uint32_t k = 0; k < (1u << 16) && !bar_try(k_full0 + 8 * s, 0) && !bar_try(k_full0 + 8 * s, 1); ++k) {}
+        // Copies still in flight target this CTA's shared memory, which the next CTA on this SM gets: wait
+        // (bounded) for the last copy requested into every stage, on the phase that copy completes.
+        if (n_tiles > 0) for (uint32_t k = 0; k < kSpin && !bar_try(q_full, 0); ++k) {}
+        for (int s = 0; s < kStages; ++s) {
+            const int jk = ((k_requested - 1 - s) / kStages) * kStages + s;       // last key tile requested into stage s
+            if (k_requested > s) for (uint32_t k = 0; k < kSpin && !bar_try(k_full0 + 8 * s, (jk / kStages) & 1u); ++k) {}
+            const int jv = ((v_requested - 1 - s) / kStages) * kStages + s;
+            if (v_requested > s) for (uint32_t k = 0; k < kSpin && !bar_try(v_full0 + 8 * s, (jv / kStages) & 1u); ++k) {}
+        }
     }
-#if defined(FPKV_CTA_SUMS)
-    if (tid == 0 && n_tiles > 0) {
-        const unsigned long long t3 = gtime_ns();
-        atomicAdd(&g_cta_sums[0], cta_marks[0] - cta_t0); atomicAdd(&g_cta_sums[1], cta_marks[1] - cta_marks[0]);
-        atomicAdd(&g_cta_sums[2], t3 - cta_marks[1]); atomicAdd(&g_cta_sums[3], 1ull);
-        atomicAdd(&g_cta_sums[5], cta_marks[2] - cta_marks[1]); atomicAdd(&g_cta_sums[6], cta_marks[3] - cta_marks[2]);
-        atomicAdd(&g_cta_sums[7], cta_marks[3 + prm.heads_per_cta - 1] - cta_marks[3]); atomicAdd(&g_cta_sums[4], (unsigned long long)n_tiles);
-    }
-#endif
     if (warp == kMmaWarp) {
         tc_fence_after();
         asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(kTmemCols) : "memory");
@@ -749,23 +722,6 @@ constexpr int kPrefillSmem = 1024 + (2 + 2 * kStages) * kTileBytes + 24 * 8 + 16
 
 }  // namespace
 
-#if defined(FPKV_CTA_SUMS)
-extern "C" __attribute__((visibility("default"))) int fpkv_debug_cta_sums(unsigned long long* host_out, int reset) {
-    if (reset) { unsigned long long z[8] = {0}; return (int)cudaMemcpyToSymbol(g_cta_sums, z, sizeof(z)); }
-    return (int)cudaMemcpyFromSymbol(host_out, g_cta_sums, sizeof(unsigned long long) * 8);
-}
-#endif
-#ifdef FPKV_PHASES
-extern "C" __attribute__((visibility("default"))) int fpkv_debug_phases(unsigned long long* host_out, int reset) {
-    if (reset) { unsigned long long z[16] = {0}; return (int)cudaMemcpyToSymbol(g_phase_sums, z, sizeof(z)); }
-    return (int)cudaMemcpyFromSymbol(host_out, g_phase_sums, sizeof(unsigned long long) * 16);
-}
-#endif
-#ifdef FPKV_FINE
-extern "C" __attribute__((visibility("default"))) int fpkv_debug_fine(long long* host_out) {
-    return (int)cudaMemcpyFromSymbol(host_out, g_fine, sizeof(long long) * 128);
-}
-#endif
 
 bool prefill_tc_supported(const PoolView& pv, int Hq)
 {

@@ -83,13 +83,10 @@ class PagedKVCache(KVCacheBase):
         self._page_table[0, :] = 0
         self.page_table_cpu = [[] for _ in range(max_batch_size)]
         self.capacity = [0 for _ in range(max_batch_size)]
-        self.free_pages = list(reversed(range(1, n_pages)))
-        self.free_batch_idx = list(reversed(range(1, max_batch_size)))
+        self._free_pages = list(reversed(range(1, n_pages)))
+        self._free_batch_idx = list(reversed(range(1, max_batch_size)))
         # [slot, physical page] -> logical page
         self._physical_to_logical = torch.full((max_batch_size, n_pages), -1, dtype=torch.int64, device=device)
-        # On a CUDA cache the table edits of allocate / reserve / erase are queued here and applied by one
-        # kernel launch before the tables are next used (by a kernel of this class or through the attributes).
-        self._pending = []
 
         self.kv_shape = (num_layers, 2, 1, n_heads, n_pages * page_size, head_dim)
         self.kv_cache = torch.zeros(self.kv_shape, dtype=dtype, device=device)
@@ -101,6 +98,26 @@ class PagedKVCache(KVCacheBase):
         self._workspace = None
         self.decode_kernel = _lib.DECODE_AUTO       # DECODE_PORTABLE / DECODE_TMA force one kernel
         self.prefill_kernel = _lib.PREFILL_AUTO     # PREFILL_PORTABLE / PREFILL_TC force one kernel
+
+        # On a CUDA cache the free lists also live on the device (stacks in list order) and allocate /
+        # reserve / erase queue one record each; one kernel launch applies the queue, in order, before the
+        # tables are next used (by a kernel of this class or through the attributes).  The lists above stay
+        # the host's mirror: can_reserve and the error of an over-reserve need them without a device read.
+        self._pending = []
+        if self._dev.type == "cuda":
+            self._free_pages_dev = torch.zeros(n_pages, dtype=torch.int32, device=device)
+            self._free_slots_dev = torch.zeros(max_batch_size, dtype=torch.int32, device=device)
+            self._alloc_counts = torch.zeros(2, dtype=torch.int32, device=device)
+            self._alloc = _lib.FpkvAllocState(self._free_pages_dev.data_ptr(), self._free_slots_dev.data_ptr(),
+                                              self._alloc_counts.data_ptr())
+            # two pinned staging buffers, used in turn, so that a flush allocates nothing and never rewrites
+            # host memory that an earlier, still running copy reads
+            self._ops_cap = 1024
+            self._ops_host = [torch.empty((self._ops_cap, 4), dtype=torch.int32).pin_memory() for _ in range(2)]
+            self._ops_done = [None, None]
+            self._ops_dev = torch.empty((self._ops_cap, 4), dtype=torch.int32, device=device)
+            self._ops_turn = 0
+            self._upload_lists()
 
     # ------------------------------------------------------------------ tables
     @property
@@ -115,34 +132,76 @@ class PagedKVCache(KVCacheBase):
         self._flush_tables()
         return self._physical_to_logical
 
-    def _edit_tables(self, ops):
-        """ops: list of (kind, slot, a, b); kind 0 clears the slot's rows, kind 1 maps logical page a to
-        physical page b.  A CPU cache (bookkeeping only) applies them at once; a CUDA cache queues them."""
-        if self._dev.type == "cuda":
-            self._pending.extend(ops)
-            return
-        for kind, slot, a, b in ops:
-            if kind == 0:
-                self._page_table[slot, :] = -1
-                self._physical_to_logical[slot, :] = -1
-            else:
-                self._page_table[slot, a] = b
-                self._physical_to_logical[slot, b] = a
+    @property
+    def free_pages(self) -> list:
+        """Free physical pages, a LIFO list as in the reference (``free_pages[-n:]`` are taken next).
+        Assign a new list to reorder it (tests shuffle it); do not edit the returned list in place, the
+        device copy would not follow."""
+        return self._free_pages
+
+    @free_pages.setter
+    def free_pages(self, pages):
+        self._flush_tables()                        # records queued so far were made against the old order
+        self._free_pages = list(pages)
+        self._upload_lists()
+
+    @property
+    def free_batch_idx(self) -> list:
+        """Free slots, a LIFO list as in the reference; assign to reorder, do not edit in place."""
+        return self._free_batch_idx
+
+    @free_batch_idx.setter
+    def free_batch_idx(self, slots):
+        self._flush_tables()
+        self._free_batch_idx = list(slots)
+        self._upload_lists()
 
     def flush_tables(self):
-        """Apply the queued table edits now (one pinned upload, one kernel launch).  Every data-path
-        method and the table attributes do this on their own; call it yourself before a region that must
-        not allocate (CUDA-graph capture, ``decode_attention_noalloc``)."""
+        """Apply the queued allocator calls now (one copy from a preallocated pinned buffer, one kernel
+        launch; nothing is allocated).  Every data-path method and the table attributes do this on their
+        own; call it yourself before a region that must not touch the tables (CUDA-graph capture,
+        ``decode_attention_noalloc``)."""
         self._flush_tables()
 
-    def _flush_tables(self):
-        if not self._pending:
+    def _upload_lists(self):
+        """The host lists copied whole to the device stacks: at start-up and after the lists were
+        reordered by hand (nothing is queued at either time)."""
+        if self._dev.type != "cuda":
             return
-        ops = torch.tensor(self._pending, dtype=torch.int32).pin_memory().to(self._dev, non_blocking=True)
+        assert not self._pending
+        fp = torch.tensor(self._free_pages, dtype=torch.int32)
+        fs = torch.tensor(self._free_batch_idx, dtype=torch.int32)
+        assert fp.numel() <= self.n_pages and fs.numel() <= self.max_batch_size, "a free list is longer than the pool"
+        self._free_pages_dev[:fp.numel()].copy_(fp)
+        self._free_slots_dev[:fs.numel()].copy_(fs)
+        self._alloc_counts.copy_(torch.tensor([fp.numel(), fs.numel()], dtype=torch.int32))
+
+    def _flush_tables(self):
+        if self._dev.type != "cuda":
+            return
         n = len(self._pending)
+        if n == 0:
+            return
+        if n > self._ops_cap:                       # a step with more calls than ever before: grow (allocates)
+            torch.cuda.current_stream(self._dev).synchronize()
+            self._ops_cap = max(n, 2 * self._ops_cap)
+            self._ops_host = [torch.empty((self._ops_cap, 4), dtype=torch.int32).pin_memory() for _ in range(2)]
+            self._ops_done = [None, None]
+            self._ops_dev = torch.empty((self._ops_cap, 4), dtype=torch.int32, device=self._dev)
+        t = self._ops_turn
+        self._ops_turn ^= 1
+        if self._ops_done[t] is not None:
+            self._ops_done[t].synchronize()         # the copy that last read this buffer (two flushes ago)
+        host = self._ops_host[t]
+        host.numpy()[:n] = self._pending
         self._pending = []
-        _lib.check(_lib.lib.fpkv_table_update(ctypes.byref(self._pool), ops.data_ptr(), n, self._status_ptr(),
-                                              _stream(self._dev)), "fpkv_table_update")
+        self._ops_dev[:n].copy_(host[:n], non_blocking=True)
+        if self._ops_done[t] is None:
+            self._ops_done[t] = torch.cuda.Event()
+        self._ops_done[t].record(torch.cuda.current_stream(self._dev))
+        _lib.check(_lib.lib.fpkv_alloc_step(ctypes.byref(self._pool), ctypes.byref(self._alloc),
+                                            self._ops_dev.data_ptr(), n, self._status_ptr(), _stream(self._dev)),
+                   "fpkv_alloc_step")
 
     # ------------------------------------------------------------------ helpers
     def _require_cuda(self, *tensors, flush: bool = True):
@@ -164,7 +223,9 @@ class PagedKVCache(KVCacheBase):
         if bits:
             self._status.zero_()
             names = [n for b, n in ((1, "bad slot"), (2, "bad position"), (4, "bad page id"),
-                                    (8, "on-chip wait timed out")) if bits & b]
+                                    (8, "on-chip wait timed out"),
+                                    (16, "image span not closed inside its sequence (cut at the sequence's end)"))
+                     if bits & b]
             raise RuntimeError("fpkv kernel status: " + ", ".join(names))
         return bits
 
@@ -183,18 +244,23 @@ class PagedKVCache(KVCacheBase):
     def can_reserve(self, size: int, batch_idx_int: int | None = None) -> bool:
         """Host-only check: room for a new request, or for growing an existing one."""
         if batch_idx_int is None:
-            return self.num_free_pages * self.page_size >= size and len(self.free_batch_idx) > 0
+            return self.num_free_pages * self.page_size >= size and len(self._free_batch_idx) > 0
         return self.reserve(batch_idx_int, None, size, dry_run=True)
 
     def allocate(self) -> int:
-        slot = self.free_batch_idx.pop()
+        slot = self._free_batch_idx.pop()
         self.capacity[slot] = 0
-        self._edit_tables([(0, slot, 0, 0)])
+        if self._dev.type == "cuda":
+            # a free slot's rows are all -1 already (the constructor and erase leave them so)
+            self._pending.append((_lib.OP_ALLOCATE, slot, 0, 0))
+        else:
+            self._physical_to_logical[slot, :] = -1
+            self._page_table[slot, :] = -1
         return slot
 
     @property
     def num_free_pages(self) -> int:
-        return len(self.free_pages)
+        return len(self._free_pages)
 
     def reserve(self, batch_idx_int: int, batch_idx: Tensor | None, seq_len: int, dry_run: bool = False) -> bool:
         """Grow slot ``batch_idx_int`` to hold at least ``seq_len`` tokens.
@@ -212,20 +278,29 @@ class PagedKVCache(KVCacheBase):
                 f"in batch {batch_idx_int}. Only {self.num_free_pages} pages available. "
                 f"Current capacity is {self.capacity[batch_idx_int]} tokens.")
         start = self.capacity[batch_idx_int] // self.page_size
-        end = start + n_new
-        pages = self.free_pages[-n_new:]
-        self._edit_tables([(1, batch_idx_int, start + i, pg) for i, pg in enumerate(pages)])
+        pages = self._free_pages[-n_new:]
+        if self._dev.type == "cuda":
+            self._pending.append((_lib.OP_RESERVE, batch_idx_int, start, n_new))
+        else:
+            for i, pg in enumerate(pages):
+                self._page_table[batch_idx_int, start + i] = pg
+                self._physical_to_logical[batch_idx_int, pg] = start + i
         self.page_table_cpu[batch_idx_int] += pages
-        self.free_pages = self.free_pages[:-n_new]
+        del self._free_pages[-n_new:]
         self.capacity[batch_idx_int] += n_new * self.page_size
         return True
 
     def erase(self, batch_idx: int) -> None:
-        self.free_batch_idx.append(batch_idx)
-        self.free_pages.extend(reversed(self.page_table_cpu[batch_idx]))
-        self.page_table_cpu[batch_idx] = []
+        self._free_batch_idx.append(batch_idx)
+        owned = self.page_table_cpu[batch_idx]
+        self._free_pages.extend(reversed(owned))
         # cleared on the device too, so padding rows and stale slots read "unmapped"
-        self._edit_tables([(0, batch_idx, 0, 0)])
+        if self._dev.type == "cuda":
+            self._pending.append((_lib.OP_ERASE, batch_idx, len(owned), 0))
+        else:
+            self._page_table[batch_idx, :] = -1
+            self._physical_to_logical[batch_idx, :] = -1
+        self.page_table_cpu[batch_idx] = []
         self.capacity[batch_idx] = 0
 
     # ------------------------------------------------------------------- append
@@ -352,8 +427,8 @@ class PagedKVCache(KVCacheBase):
     # --------------------------------------------------------- decode attention
     def _get_workspace(self, B: int, Hq: int) -> Tensor:
         need = ctypes.c_size_t(0)
-        _lib.check(_lib.lib.fpkv_decode_workspace_bytes(ctypes.byref(self._pool), B, Hq, ctypes.byref(need)),
-                   "fpkv_decode_workspace_bytes")
+        _lib.check(_lib.lib.fpkv_decode_workspace_bytes(ctypes.byref(self._pool), B, Hq, int(self.decode_kernel),
+                                                        ctypes.byref(need)), "fpkv_decode_workspace_bytes")
         if self._workspace is None or self._workspace.numel() < need.value:
             # zero-filled once: the head of the workspace holds arrival counters the kernel leaves at zero
             self._workspace = torch.zeros(need.value, dtype=torch.uint8, device=self._dev)
@@ -432,7 +507,7 @@ class PagedKVCache(KVCacheBase):
         if bi.dtype != torch.int64:
             bi = bi.to(torch.int64)
         bi = bi if bi.is_contiguous() else bi.contiguous()
-        ext = mask.extent(input_pos)
+        ext = mask.extent(input_pos, self._status)
         q = self._rows16(q)
         out = torch.empty((1, L, Hq, D) if token_major else (1, Hq, L, D), dtype=q.dtype, device=q.device)
         lse = torch.empty((1, Hq, L), dtype=torch.float32, device=q.device)

@@ -54,6 +54,9 @@ extern "C" {
 #define FPKV_STATUS_BAD_POS    2u   /* position outside the page table         */
 #define FPKV_STATUS_BAD_PAGE   4u   /* page id outside [0, n_pages)            */
 #define FPKV_STATUS_TIMEOUT    8u   /* a bounded on-chip wait ran out          */
+#define FPKV_STATUS_OPEN_SPAN 16u   /* set by the host-side mask builder, not by a
+                                       kernel: an image span was not closed inside
+                                       its sequence and was cut at the sequence's end */
 
 typedef enum { FPKV_F32 = 0, FPKV_BF16 = 1, FPKV_F16 = 2 } fpkv_dtype;
 typedef enum { FPKV_I32 = 0, FPKV_I64 = 1 } fpkv_itype;
@@ -64,6 +67,14 @@ typedef enum { FPKV_I32 = 0, FPKV_I64 = 1 } fpkv_itype;
  *   data                 device, (num_layers, 2, 1, n_heads, n_pages*page_size,
  *                        head_dim) contiguous, i.e. `kv_cache` (:72-74);
  *                        n_heads is the number of heads STORED (the KV heads).
+ *                        The reference creates it zero-filled (:74).  Here it
+ *                        may hold anything, NaN and Inf bit patterns included,
+ *                        in rows that were never appended: the attention
+ *                        kernels read whole tiles but clear the value rows
+ *                        beyond a sequence's last visible key on chip, so
+ *                        garbage never reaches a result.  Reserved page 0
+ *                        (rows [0, page_size) of every plane) is the landing
+ *                        place of padding rows and is never read.
  *   page_table           device int64 (max_batch_size, n_pages)   (:58-59)
  *   physical_to_logical  device int64 (max_batch_size, n_pages)   (:70)
  */
@@ -102,24 +113,56 @@ typedef struct fpkv_epilogue {
 /* Library version (major*10000 + minor*100 + patch). */
 FPKV_API int fpkv_version(void);
 
+/* Hash of the sources the library was built from (16 hex digits): the build
+ * script compiles it in, the Python loader compares it with the tree and
+ * refuses a library built from something else. */
+FPKV_API const char* fpkv_build_id(void);
+
 /* Text for a return code; never NULL. */
 FPKV_API const char* fpkv_strerror(int code);
 
 /*
- * Apply a batch of page-table edits on the device, in order, with one launch.
- * Replaces the per-call device updates of PagedKVCache.allocate, reserve and
- * erase (paged_attention.py:102-109, 145-158, 166-182), which issue a few
- * tensor operations and one host-to-device tensor each; the free lists and
- * capacities stay on the host as there.  This entry point WRITES
- * pool->page_table and pool->physical_to_logical.
- * ops: device int32 [n_ops][4], 16-byte aligned, each {kind, slot, a, b}:
- *   kind 0  clear both table rows of `slot` to -1              (allocate, erase)
- *   kind 1  page_table[slot, a] = b; physical_to_logical[slot, b] = a   (reserve)
- * Slot 0 and page 0 are reserved and never edited; edits naming them or ids
- * out of range are skipped and raise FPKV_STATUS_BAD_SLOT / _BAD_PAGE.
+ * The allocator's free lists on the device: the reference's `free_pages` and
+ * `free_batch_idx` Python lists (paged_attention.py:62-68) as stacks with the
+ * same order (element 0 at the bottom, the list's last element on top).
+ *   free_pages  device int32 (n_pages);         counts[0] entries are valid
+ *   free_slots  device int32 (max_batch_size);  counts[1] entries are valid
+ *   counts      device int32 [2]
+ * The caller fills them once (the constructor state is free_pages =
+ * [n_pages-1 .. 1], free_slots = [max_batch_size-1 .. 1]) and again whenever
+ * it reorders its own copy of the lists by hand.
  */
-FPKV_API int fpkv_table_update(const fpkv_pool* pool, const int32_t* ops, int32_t n_ops,
-                               int32_t* status, void* stream);
+typedef struct fpkv_alloc_state {
+    int32_t* free_pages;
+    int32_t* free_slots;
+    int32_t* counts;
+} fpkv_alloc_state;
+
+/*
+ * Apply one scheduling step's allocator calls on the device, in order, with
+ * one launch: free stacks, page_table and physical_to_logical.  Replaces the
+ * device side of PagedKVCache.allocate, reserve and erase
+ * (paged_attention.py:102-109, 145-158, 166-182), which issue a few tensor
+ * operations and one host-to-device tensor per call and rewrite whole table
+ * rows; here a call is one 16-byte record and an erase touches only the
+ * entries the slot owns.  The host keeps its own copy of the lists (it needs
+ * them for can_reserve and the RuntimeError of an over-reserve); this entry
+ * point WRITES pool->page_table and pool->physical_to_logical.
+ * ops: device int32 [n_ops][4], 16-byte aligned, each {kind, slot, a, b}:
+ *   kind 0  allocate  pop the slot stack; the popped slot must be `slot`
+ *   kind 1  reserve   take the top b pages, in list order, as logical pages
+ *                     a .. a+b-1 of `slot` (free_pages[-b:] of :147-158)
+ *   kind 2  erase     push the slot's pages (logical 0 .. a-1) back reversed,
+ *                     set those entries of both tables to -1, push the slot
+ *   kind 3  map       page_table[slot, a] = b; physical_to_logical[slot, b] = a
+ *                     (for callers that keep their own free lists)
+ *   kind 4  clear     both table rows of `slot` to -1 in full
+ * Slot 0 and page 0 are reserved and never edited; records naming them, ids
+ * out of range, a pop that does not give `slot`, or a reserve beyond the
+ * stack are skipped and raise FPKV_STATUS_BAD_SLOT / _BAD_PAGE.
+ */
+FPKV_API int fpkv_alloc_step(const fpkv_pool* pool, const fpkv_alloc_state* state,
+                             const int32_t* ops, int32_t n_ops, int32_t* status, void* stream);
 
 /*
  * Decode append: one new K/V row per sequence, written through the page
@@ -197,13 +240,6 @@ FPKV_API int fpkv_gather(const fpkv_pool* pool, int32_t layer, int32_t slot, int
                 void* k_out, void* v_out, int32_t* status, void* stream);
 
 /*
- * Bytes of scratch fpkv_decode_attn needs for a batch of B rows with n_q_heads
- * query heads (an upper bound that does not depend on the context lengths).
- */
-FPKV_API int fpkv_decode_workspace_bytes(const fpkv_pool* pool, int32_t B, int32_t n_q_heads,
-                                size_t* bytes);
-
-/*
  * Paged decode attention: one query token per row against logical keys
  * 0..input_pos[b] of slot batch_idx[b].  Replaces, for S_q == 1, the decode
  * mask pipeline plus FlexAttention call of the reference:
@@ -239,6 +275,16 @@ FPKV_API int fpkv_decode_workspace_bytes(const fpkv_pool* pool, int32_t B, int32
  * Never set it after anything else: the kernel would read batch_idx,
  * input_pos and q before the preceding work is known to be complete. */
 #define FPKV_DECODE_AFTER_APPEND 4
+/*
+ * Bytes of scratch fpkv_decode_attn needs for a batch of B rows with n_q_heads
+ * query heads when called with the same kernel choice in `flags` (an upper
+ * bound that does not depend on the context lengths; the TMA kernel's need
+ * does not depend on B either).  FPKV_ESHAPE when FPKV_DECODE_TMA is forced
+ * outside its range.
+ */
+FPKV_API int fpkv_decode_workspace_bytes(const fpkv_pool* pool, int32_t B, int32_t n_q_heads,
+                                int32_t flags, size_t* bytes);
+
 FPKV_API int fpkv_decode_attn(const fpkv_pool* pool, int32_t layer,
                      void* out, float* lse,
                      const void* q, int64_t q_stride_b, int64_t q_stride_h,

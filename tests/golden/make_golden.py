@@ -21,7 +21,7 @@ agreed on this case".  The reference caches GQA-expanded heads; it is fed
 compared head-group-wise.
 
 Inputs are never stored: tests rebuild them from the seeds in
-fpkv/workloads.py.  Only outputs (attention out / lse, table snapshots, pool
+tests/workloads.py.  Only outputs (attention out / lse, table snapshots, pool
 digests) are written, so the files stay small.
 """
 
@@ -43,6 +43,7 @@ REF = sys.argv[1] if len(sys.argv) > 1 else os.environ.get("FALCON_PERCEPTION_SR
 sys.path.insert(0, REF)
 sys.path.insert(0, os.path.join(ROOT, "falcon-perception_b200"))
 sys.path.insert(0, ROOT)
+sys.path.insert(0, os.path.join(ROOT, "tests"))
 
 # the engine module pulls in post-processing that needs pycocotools (absent)
 _stub = types.ModuleType("pycocotools"); _stub.mask = types.ModuleType("pycocotools.mask")
@@ -54,7 +55,7 @@ from falcon_perception.attention import (compiled_flex_attn_decode,          # n
 from torch.nn.attention.flex_attention import AuxRequest                     # noqa: E402
 
 from oracle import paged_kv_oracle as orc                                    # noqa: E402
-from fpkv import workloads as wl                                             # noqa: E402
+import workloads as wl                                             # noqa: E402
 
 OUT = os.path.join(ROOT, "tests", "golden")
 

@@ -26,6 +26,28 @@ def test_header_symbols_are_exported():
         assert getattr(raw, n) is not None
 
 
+def test_library_matches_the_sources():
+    """The loaded binary carries the hash of the sources it was compiled from; the loader refuses another."""
+    from fpkv._srchash import source_hash
+    assert _lib.build_id() == source_hash() and len(_lib.build_id()) == 16
+
+
+def test_alloc_step_validation():
+    L = _lib.lib
+    p, buf = _pool()
+    ptr = buf.data_ptr()
+    st = _lib.FpkvAllocState(ptr, ptr, ptr)
+    assert L.fpkv_alloc_step(None, ctypes.byref(st), ptr, 1, None, None) == -1
+    assert L.fpkv_alloc_step(ctypes.byref(p), None, ptr, 1, None, None) == -1
+    assert L.fpkv_alloc_step(ctypes.byref(p), ctypes.byref(_lib.FpkvAllocState(0, ptr, ptr)), ptr, 1, None, None) == -1
+    assert L.fpkv_alloc_step(ctypes.byref(p), ctypes.byref(st), ptr, -1, None, None) == -1
+    assert L.fpkv_alloc_step(ctypes.byref(p), ctypes.byref(st), 0, 1, None, None) == -1
+    assert L.fpkv_alloc_step(ctypes.byref(p), ctypes.byref(st), ptr + 4, 1, None, None) == -3
+    assert L.fpkv_alloc_step(ctypes.byref(p), ctypes.byref(st), ptr, 0, None, None) == 0      # nothing queued
+    if not torch.cuda.is_available():
+        assert L.fpkv_alloc_step(ctypes.byref(p), ctypes.byref(st), ptr, 1, None, None) == -4
+
+
 def test_version_and_strerror():
     assert _lib.lib.fpkv_version() >= 100
     assert _lib.strerror(0) == "ok"
@@ -62,8 +84,14 @@ def test_validation_happens_before_any_launch():
     assert call(p, sb=100) == -3                             # stride not a multiple of 16 bytes
     assert call(p, B=0) == 0                                 # empty batch is a no-op
     need = ctypes.c_size_t(0)
-    assert L.fpkv_decode_workspace_bytes(ctypes.byref(p), 4, 3, ctypes.byref(need)) == -2   # 3 % 2 heads
-    assert L.fpkv_decode_workspace_bytes(ctypes.byref(p), 4, 4, ctypes.byref(need)) == 0 and need.value > 0
+    assert L.fpkv_decode_workspace_bytes(ctypes.byref(p), 4, 3, 0, ctypes.byref(need)) == -2   # 3 % 2 heads
+    assert L.fpkv_decode_workspace_bytes(ctypes.byref(p), 4, 4, 0, ctypes.byref(need)) == 0 and need.value > 0
+    # the portable kernel's need follows the batch (its split count shrinks as the batch grows), it is not a fixed maximum
+    small, big = ctypes.c_size_t(0), ctypes.c_size_t(0)
+    assert L.fpkv_decode_workspace_bytes(ctypes.byref(p), 4, 4, _lib.DECODE_PORTABLE, ctypes.byref(small)) == 0
+    assert L.fpkv_decode_workspace_bytes(ctypes.byref(p), 1024, 4, _lib.DECODE_PORTABLE, ctypes.byref(big)) == 0
+    assert big.value < 1024 // 4 * small.value
+    assert L.fpkv_decode_workspace_bytes(ctypes.byref(p), 4, 4, _lib.DECODE_TMA, ctypes.byref(need)) == -2   # page 16
     # decode: workspace too small is caught on the host
     assert L.fpkv_decode_attn(ctypes.byref(p), 0, ptr, ptr, ptr, 256, 64, ptr, ptr, 0, 2, 4, 0.125, ptr, 16, 0,
                               None, None, None) == -6

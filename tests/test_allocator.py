@@ -11,7 +11,7 @@ import torch
 
 from fpkv.paged_attention import PagedKVCache
 from fpkv.attention import CausalDecodeMask, DecodeStepMask, PrefillMask, image_span_ids
-from fpkv import workloads as wl
+import workloads as wl
 from helpers import GOLDEN
 
 
@@ -127,29 +127,71 @@ def test_logical_index_helpers():
 
 
 @pytest.mark.gpu
-def test_table_edits_are_batched_and_ordered():
-    """allocate / reserve / erase on a CUDA cache queue their table edits; one launch applies a whole batch in
-    order (clear, map, clear again, map again on the same slot) and bad ids are reported, not written."""
+def test_allocator_calls_are_batched_and_ordered():
+    """allocate / reserve / erase on a CUDA cache queue one record each; one launch applies a whole batch in
+    order (a slot reserved, erased, allocated and reserved again), the device stacks follow the host lists,
+    and bad records are reported, not applied."""
     import ctypes
     from fpkv import _lib
     c = PagedKVCache(16, 8, 4, 1, 64, 1, torch.float32, "cuda")
     a = c.allocate(); c.reserve(a, None, 20)
-    pages_a = list(c.page_table_cpu[a])
     c.erase(a)
     b = c.allocate(); assert b == a
     c.reserve(b, None, 9)
-    assert len(c._pending) == 2 + 3 + 1 + 2                 # nothing has touched the device yet
+    assert len(c._pending) == 5                             # nothing has touched the device yet
     pt = c.page_table                                       # flushes
     assert not c._pending
     assert pt[b, :2].tolist() == c.page_table_cpu[b] and (pt[b, 2:] == -1).all()
     p2l = c.physical_to_logical[b]
     assert sorted((p2l >= 0).nonzero().view(-1).tolist()) == sorted(c.page_table_cpu[b])
     assert (pt[0] == 0).all()                               # slot 0 is never edited
-    # edits naming slot 0, page 0 or ids out of range are skipped and flagged
-    bad = torch.tensor([[1, 0, 0, 3], [1, 2, 1, 0], [1, 2, 99, 3], [0, 7, 0, 0]], dtype=torch.int32, device="cuda")
-    before = c._page_table.clone()
-    assert _lib.lib.fpkv_table_update(ctypes.byref(c._pool), bad.data_ptr(), 4, c._status.data_ptr(), None) == 0
+    n_pg, n_sl = c._alloc_counts.tolist()
+    assert c._free_pages_dev[:n_pg].tolist() == c.free_pages and c._free_slots_dev[:n_sl].tolist() == c.free_batch_idx
+    # records naming slot 0, page 0, ids out of range, a pop of the wrong slot or more pages than are free are
+    # skipped and flagged
+    bad = torch.tensor([[3, 0, 0, 3], [3, 2, 1, 0], [3, 2, 99, 3], [4, 7, 0, 0], [0, 3, 0, 0], [1, 2, 0, 99]],
+                       dtype=torch.int32, device="cuda")
+    before, counts = c._page_table.clone(), c._alloc_counts.clone()
+    assert _lib.lib.fpkv_alloc_step(ctypes.byref(c._pool), ctypes.byref(c._alloc), bad.data_ptr(), 6,
+                                    c._status.data_ptr(), None) == 0
     torch.cuda.synchronize()
-    assert torch.equal(before, c._page_table)
+    assert torch.equal(before, c._page_table) and torch.equal(counts, c._alloc_counts)
     with pytest.raises(RuntimeError, match="bad slot, bad page id"):
         c.check_status()
+    # direct edits (for callers with their own free lists) and a full clear
+    ok = torch.tensor([[3, 2, 5, 9], [3, 2, 6, 4], [4, 2, 0, 0], [3, 2, 1, 7]], dtype=torch.int32, device="cuda")
+    assert _lib.lib.fpkv_alloc_step(ctypes.byref(c._pool), ctypes.byref(c._alloc), ok.data_ptr(), 4,
+                                    c._status.data_ptr(), None) == 0
+    assert c._page_table[2].tolist() == [-1, 7] + [-1] * 14 and c._physical_to_logical[2, 7].item() == 1
+    c.check_status()
+
+
+@pytest.mark.gpu
+def test_device_stacks_follow_the_host_lists():
+    """Random allocate / reserve / erase traffic, flushed at random moments: the device free stacks and tables
+    always equal the host lists and the oracle's tables."""
+    import random
+    from oracle import paged_kv_oracle as orc
+    rnd = random.Random(7)
+    c = PagedKVCache(200, 16, 12, 1, 64, 1, torch.float32, "cuda")
+    o = orc.OraclePagedKVCache(200, 16, 12, 1, 64, 1, torch.float32)
+    perm = list(range(1, 200)); rnd.shuffle(perm)
+    c.free_pages = list(perm); o.free_pages = list(perm)
+    live = {}
+    for step in range(400):
+        r = rnd.random()
+        if r < 0.25 and c.free_batch_idx:
+            s = c.allocate(); assert o.allocate() == s; live[s] = 0
+        elif r < 0.7 and live:
+            s = rnd.choice(list(live)); want = live[s] + rnd.randint(1, 300)
+            if c.can_reserve(want, s):
+                c.reserve(s, None, want); o.reserve(s, want); live[s] = want
+        elif live:
+            s = rnd.choice(list(live)); del live[s]; c.erase(s); o.erase(s)
+        if rnd.random() < 0.2 or step == 399:
+            assert torch.equal(c.page_table.cpu(), torch.as_tensor(o.page_table))
+            assert torch.equal(c.physical_to_logical.cpu(), torch.as_tensor(o.physical_to_logical))
+            n_pg, n_sl = c._alloc_counts.tolist()
+            assert c._free_pages_dev[:n_pg].tolist() == list(o.free_pages) == c.free_pages
+            assert c._free_slots_dev[:n_sl].tolist() == list(o.free_batch_idx) == c.free_batch_idx
+    c.check_status()

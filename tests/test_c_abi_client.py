@@ -22,14 +22,14 @@ typedef int (*version_fn)(void);
 typedef const char* (*strerror_fn)(int);
 typedef int (*append_fn)(const fpkv_pool*, int32_t, const int64_t*, const void*, int32_t, const void*, int64_t, int64_t,
                          const void*, int64_t, int64_t, int32_t, int32_t*, void*);
-typedef int (*ws_fn)(const fpkv_pool*, int32_t, int32_t, size_t*);
+typedef int (*ws_fn)(const fpkv_pool*, int32_t, int32_t, int32_t, size_t*);
 
 int main(int argc, char** argv) {
     void* h = dlopen(argv[1], RTLD_NOW);
     if (!h) { printf("dlopen failed: %s\n", dlerror()); return 1; }
-    const char* names[] = {"fpkv_version", "fpkv_strerror", "fpkv_append_decode", "fpkv_append_packed", "fpkv_gather",
-                           "fpkv_decode_workspace_bytes", "fpkv_decode_attn", "fpkv_prefill_attn",
-                           "fpkv_decode_attn_static", "fpkv_table_update"};
+    const char* names[] = {"fpkv_version", "fpkv_build_id", "fpkv_strerror", "fpkv_alloc_step", "fpkv_append_decode",
+                           "fpkv_append_packed", "fpkv_pre_append", "fpkv_gather", "fpkv_decode_workspace_bytes",
+                           "fpkv_decode_attn", "fpkv_prefill_attn", "fpkv_decode_attn_static"};
     for (unsigned i = 0; i < sizeof(names) / sizeof(names[0]); ++i)
         if (!dlsym(h, names[i])) { printf("missing %s\n", names[i]); return 2; }
     version_fn version = (version_fn)dlsym(h, "fpkv_version");
@@ -46,8 +46,8 @@ int main(int argc, char** argv) {
     if (append(&pool, 0, (const int64_t*)buf, buf, FPKV_I32, (char*)buf + 4, 1024, 128, buf, 1024, 128, 4, NULL, NULL) != FPKV_EALIGN) return 6;
     if (append(&pool, 0, (const int64_t*)buf, buf, FPKV_I32, buf, 1024, 128, buf, 1024, 128, 0, NULL, NULL) != FPKV_OK) return 7;
     size_t need = 0;
-    if (ws(&pool, 64, 16, &need) != FPKV_OK || need == 0) return 8;
-    if (ws(&pool, 64, 12, &need) != FPKV_ESHAPE) return 9;
+    if (ws(&pool, 64, 16, FPKV_DECODE_AUTO, &need) != FPKV_OK || need == 0) return 8;
+    if (ws(&pool, 64, 12, FPKV_DECODE_AUTO, &need) != FPKV_ESHAPE) return 9;
     printf("c client ok: version %d, decode workspace %zu bytes\n", version(), need);
     return 0;
 }

@@ -2,17 +2,19 @@
 
 config 3  chunked multimodal prefill (8 x [1024 image + 64 text], 512-row query chunks, K/V written to
           pages first) while 56 other sequences decode in the same step -- full size, against the oracle.
-config 4  long-context decode under fragmentation: every few steps a quarter of the sequences finish, are
-          erased, and new ones are admitted into the freed pages -- oracle parity at a reduced size, and at
-          full context lengths (16K-32K) the properties that do not need a CPU pass: allocator state equal
-          to the oracle's, both kernels agreeing, reruns bitwise equal.
+config 4  long-context decode under fragmentation: every 64 of 512 steps a quarter of the sequences finish,
+          are erased, and new ones are admitted into the freed pages -- the full schedule at full context
+          lengths (16K-32K) with the oracle running beside it, plus a reduced-size variant with every step
+          compared.
+config 5  one GPU's share of the 28-layer stack: 64 sequences, 61 GB pool, two layers against the oracle.
 """
 
 import numpy as np
 import pytest
 import torch
 
-from fpkv import _lib, workloads as wl
+from fpkv import _lib
+import workloads as wl
 from fpkv.attention import PrefillMask
 from fpkv.paged_attention import PagedKVCache, paged_attention
 from oracle import paged_kv_oracle as orc
@@ -135,46 +137,106 @@ def test_config4_churn_reduced_size_against_oracle():
     c.check_status()
 
 
-def test_config4_full_context_lengths_properties():
-    """batch 32, context 16K-32K, 2048-token admissions into freed pages; 24 steps with churn every 8."""
-    P, B, n_pages = 128, 32, 10240
+def test_config4_full_schedule_against_the_oracle():
+    """BASELINE config 4 as written: batch 32, context 16K-32K, 512 decode steps; every 64 steps a seeded
+    quarter of the sequences finishes and is erased and new 2048-token sequences are admitted (packed
+    append) into the freed pages.  The oracle runs the whole schedule beside the product on its own
+    full-size pool (every append, every allocator call); attention is compared on all rows at the first
+    and last step, at the first step after each admission and in the middle of each period, and at the end
+    both page tables and the whole pool are compared bit for bit."""
+    P, B, n_pages, H, D = 128, 32, 10240, 8, 128
     rng = np.random.default_rng(4004)
-    c = PagedKVCache(n_pages, P, B + 1, 8, 128, 1, torch.bfloat16, "cuda")
-    o = orc.OraclePagedKVCache(n_pages, P, B + 1, 1, 8, 1, torch.bfloat16)       # allocator only (tiny pool)
+    c = PagedKVCache(n_pages, P, B + 1, H, D, 1, torch.bfloat16, "cuda")
+    o = orc.OraclePagedKVCache(n_pages, P, B + 1, H, D, 1, torch.bfloat16)
     perm = (rng.permutation(n_pages - 1) + 1).tolist()
     c.free_pages = list(perm); o.free_pages = list(perm)
     lens = rng.integers(16384, 32769, size=B).tolist()
     slots = []
     for L in lens:
         s = c.allocate(); assert o.allocate() == s; slots.append(s)
-        c.reserve(s, None, L + 64); o.reserve(s, L + 64)
-    c.kv_cache.normal_(0, 128 ** -0.5)                       # every reserved page holds plausible values
+        c.reserve(s, None, L + 1); o.reserve(s, L + 1)
+    # the initial contexts: random values in every page, the same bytes on both sides
+    c.kv_cache.normal_(0, D ** -0.5)
+    o.kv_cache.copy_(c.kv_cache.cpu())
     g = torch.Generator(device="cuda").manual_seed(3)
-    for step in range(24):
-        if step and step % 8 == 0:
+    checked = 0
+    for step in range(512):
+        if step and step % 64 == 0:
             gone = rng.permutation(B)[:B // 4].tolist()
             for i in gone:
                 c.erase(slots[i]); o.erase(slots[i])
             for i in gone:
                 s = c.allocate(); assert o.allocate() == s
-                c.reserve(s, None, 2048 + 64); o.reserve(s, 2048 + 64)
+                c.reserve(s, None, 2048 + 1); o.reserve(s, 2048 + 1)
+                kh = (torch.randn((1, H, 2048, D), device="cuda", generator=g) * D ** -0.5).bfloat16()
+                vh = (torch.randn((1, H, 2048, D), device="cuda", generator=g) * D ** -0.5).bfloat16()
+                ip, bi = torch.arange(2048, device="cuda").view(1, -1), torch.full((1, 2048), s, device="cuda")
+                c.insert_kv(0, kh, vh, input_pos=ip, batch_idx=bi)
+                o.append_packed(0, bi.cpu(), ip.cpu(), kh.cpu(), vh.cpu())
                 slots[i], lens[i] = s, 2048
             assert c.page_table_cpu == o.page_table_cpu and c.free_pages == o.free_pages
             for i in gone:                               # freed pages are reused and the new tables are scattered
                 pages = c.page_table_cpu[slots[i]]
                 assert len(pages) == 17 and max(pages) - min(pages) > 17
-        bi = torch.tensor(slots, device="cuda"); pos = torch.tensor(lens, dtype=torch.int32, device="cuda")
-        kn, vn, qn = ((torch.randn(B, n, 1, 128, device="cuda", generator=g) * 128 ** -0.5).bfloat16() for n in (8, 8, 16))
-        c.decode_kernel = _lib.DECODE_TMA
-        out, lse = c.decode_step(0, qn, kn, vn, bi, pos)
-        if step % 8 == 7 or step == 8:
-            out2, lse2 = c.decode_attention(0, qn, bi, pos)
-            assert torch.equal(out, out2) and torch.equal(lse, lse2)                      # rerun is bitwise equal
-            c.decode_kernel = _lib.DECODE_PORTABLE
-            outp, lsep = c.decode_attention(0, qn, bi, pos)
-            assert_attention_close(out, lse, outp.float().cpu(), lsep.cpu(), f"tma vs portable, step {step}")
-            gk, gv = c.gather(0, slots[0], lens[0] + 1)                                   # appended row is where it belongs
-            assert torch.equal(gk[:, -1], kn[0, :, 0]) and torch.equal(gv[:, -1], vn[0, :, 0])
+        for i, s in enumerate(slots):                     # grow by a page when the next token needs one
+            c.reserve(s, None, lens[i] + 1); o.reserve(s, lens[i] + 1)
+        bi = torch.tensor(slots); pos = torch.tensor(lens, dtype=torch.int32)
+        kn, vn, qn = ((torch.randn((B, n, 1, D), device="cuda", generator=g) * D ** -0.5).bfloat16() for n in (H, H, 16))
+        out, lse = c.decode_step(0, qn, kn, vn, bi.cuda(), pos.cuda())
+        o.append_decode(0, bi, pos, kn.cpu(), vn.cpu())
+        if step in (0, 511) or step % 64 in (0, 32):
+            ref_out, ref_lse = orc.decode_attention(o, 0, qn.cpu().float(), bi, pos)
+            assert_attention_close(out, lse, ref_out, ref_lse, f"config 4, step {step}")
+            checked += 1
         lens = [L + 1 for L in lens]
+    assert checked == 17
     assert torch.equal(c.page_table.cpu(), torch.from_numpy(o.page_table))
+    assert torch.equal(c.physical_to_logical.cpu(), torch.from_numpy(o.physical_to_logical))
+    assert torch.equal(c.kv_cache[..., P:, :].cpu(), o.kv_cache[..., P:, :])
+    c.check_status()
+
+
+def test_config5_one_gpu_share_of_the_stack_against_the_oracle():
+    """BASELINE config 5, one GPU's share: 64 sequences with context 2K-8K in a 28-layer pool (61 GB); one
+    decode step appends and attends in every layer.  Two layers hold real contexts (written through the
+    packed append on both sides) and are compared with the oracle on every row; the layers in between must
+    come out holding nothing but their own appended rows, i.e. the layer planes are independent."""
+    NL, B, H, Hq, D, P, n_pages = 28, 64, 8, 16, 128, 128, 4352
+    case = wl.make_decode_case(5005, B=B, Hq=Hq, Hkv=H, D=D, P=P, n_pages=n_pages, max_batch_size=B + 1,
+                               len_lo=2048, len_hi=8192, dtype=torch.bfloat16, value_scale=D ** -0.5, with_history=False)
+    c = PagedKVCache(n_pages, P, B + 1, H, D, NL, torch.bfloat16, "cuda")
+    c.free_pages = list(case.free_pages)
+    used = sum((L + 1 + P - 1) // P for L in case.lens)
+    full_layers = (5, 27)
+    oracles = {l: orc.OraclePagedKVCache(used + 1, P, B + 1, H, D, 1, torch.bfloat16) for l in full_layers}
+    g = torch.Generator(device="cuda").manual_seed(55)
+    slots = []
+    for L in case.lens:
+        s = c.allocate(); slots.append(s); c.reserve(s, None, L + 1)
+        ip, bi = torch.arange(L, device="cuda").view(1, L), torch.full((1, L), s, device="cuda")
+        for l in full_layers:
+            o = oracles[l]
+            assert o.allocate() == s; o.reserve(s, L + 1)
+            kh = (torch.randn((1, H, L, D), device="cuda", generator=g) * D ** -0.5).bfloat16()
+            vh = (torch.randn((1, H, L, D), device="cuda", generator=g) * D ** -0.5).bfloat16()
+            c.insert_kv(l, kh, vh, input_pos=ip, batch_idx=bi)
+            o.append_packed(0, bi.cpu(), ip.cpu(), kh.cpu(), vh.cpu())
+    bidx = torch.tensor(slots); pos = torch.tensor(case.lens, dtype=torch.int32)
+    outs = {}
+    step_in = {}
+    for l in range(NL):                                   # the decode step of the whole stack, layer after layer
+        kn, vn, qn = ((torch.randn((B, n, 1, D), device="cuda", generator=g) * D ** -0.5).bfloat16() for n in (H, H, Hq))
+        outs[l] = c.decode_step(l, qn, kn, vn, bidx.cuda(), pos.cuda())
+        step_in[l] = (kn, vn, qn)
+    for l in full_layers:
+        kn, vn, qn = step_in[l]
+        oracles[l].append_decode(0, bidx, pos, kn.cpu(), vn.cpu())
+        ref_out, ref_lse = orc.decode_attention(oracles[l], 0, qn.cpu().float(), bidx, pos)
+        assert_attention_close(outs[l][0], outs[l][1], ref_out, ref_lse, f"config 5, layer {l}, all 64 rows")
+    for l in (0, 4, 6, 26):                               # neighbours of the full layers: only this step's rows
+        kn, vn, qn = step_in[l]
+        plane = c.kv_cache[l][..., P:, :]
+        assert int((plane != 0).sum().item()) == int((kn != 0).sum().item()) + int((vn != 0).sum().item())
+        out, lse = outs[l]                                # one non-zero key per row: out is its value, among zeros
+        assert torch.isfinite(lse).all()
     c.check_status()

@@ -5,7 +5,8 @@ import numpy as np
 import pytest
 import torch
 
-from fpkv import _lib, workloads as wl
+from fpkv import _lib
+import workloads as wl
 from fpkv.paged_attention import PagedKVCache, paged_attention
 from oracle import paged_kv_oracle as orc
 from helpers import assert_attention_close, golden, oracle_from_case, product_from_case
@@ -139,39 +140,75 @@ def test_multi_layer_and_reused_pages():
     c.check_status()
 
 
-def test_kernels_agree_at_config2_size_and_are_deterministic():
-    """Full batch-64, 1K-8K context, permuted pool: too large for the CPU oracle
-    in seconds, so the two independent kernels check each other, a sample of
-    rows is checked against the oracle, and a rerun must be bitwise equal."""
-    case = wl.config2_case(n_pages=8192 * 2, with_history=False)
+def test_config2_full_size_every_row_against_the_oracle():
+    """BASELINE config 2 at full size: batch 64, context 1K-8K, page ids permuted over the 65 536-page pool
+    (32 GiB).  The context K/V is written through the packed append on the device and through the oracle's
+    append on the host (its pool holds only the pages in use; it runs its own allocator, so its page ids
+    differ and only the logical content is shared), then one decode step: every row of both kernels against
+    the oracle's attention, the appended pool read back bit for bit, and a rerun bitwise equal."""
+    case = wl.config2_case(with_history=False)
+    assert case.n_pages == 65536 and case.B == 64
     c = PagedKVCache(case.n_pages, case.P, case.max_batch_size, case.Hkv, case.D, 1, torch.bfloat16, "cuda")
     c.free_pages = list(case.free_pages)
+    used = sum((L + 1 + case.P - 1) // case.P for L in case.lens)
+    o = orc.OraclePagedKVCache(used + 1, case.P, case.max_batch_size, case.Hkv, case.D, 1, torch.bfloat16)
     g = torch.Generator(device="cuda").manual_seed(5)
     slots = []
     for L in case.lens:
-        s = c.allocate(); c.reserve(s, None, L + 1); slots.append(s)
-    # fill every reserved page with N(0,1)/sqrt(D) values directly (the append path is tested elsewhere)
-    used = torch.tensor(sorted(p for s in slots for p in c.page_table_cpu[s]), device="cuda")
-    view = c.kv_cache.view(2, case.Hkv, case.n_pages, case.P, case.D)
-    view[:, :, used] = (torch.randn((2, case.Hkv, used.numel(), case.P, case.D), device="cuda", generator=g)
-                        * case.D ** -0.5).bfloat16()
-    bidx = torch.tensor(slots, device="cuda"); pos = torch.tensor(case.lens, dtype=torch.int32, device="cuda")
+        s = c.allocate(); assert o.allocate() == s; slots.append(s)
+        c.reserve(s, None, L + 1); o.reserve(s, L + 1)
+        kh = (torch.randn((1, case.Hkv, L, case.D), device="cuda", generator=g) * case.D ** -0.5).bfloat16()
+        vh = (torch.randn((1, case.Hkv, L, case.D), device="cuda", generator=g) * case.D ** -0.5).bfloat16()
+        ip, bi = torch.arange(L, device="cuda").view(1, L), torch.full((1, L), s, device="cuda")
+        c.insert_kv(0, kh, vh, input_pos=ip, batch_idx=bi)
+        o.append_packed(0, bi.cpu(), ip.cpu(), kh.cpu(), vh.cpu())
+    # scattered over the whole pool, not a compact prefix of it
+    pages = [p for s in slots for p in c.page_table_cpu[s]]
+    assert len(pages) == used and max(pages) > 60000 and min(pages) < 5000
+    bidx = torch.tensor(slots); pos = torch.tensor(case.lens, dtype=torch.int32)
     k, v, q = case.k_new.cuda(), case.v_new.cuda(), case.q.cuda()
-    c.insert_kv(0, k, v, input_pos=pos.view(-1, 1), batch_idx=bidx)
-    c.decode_kernel = _lib.DECODE_TMA
-    out_t, lse_t = c.decode_attention(0, q, bidx, pos)
-    out_t2, lse_t2 = c.decode_attention(0, q, bidx, pos)
-    assert torch.equal(out_t, out_t2) and torch.equal(lse_t, lse_t2)
-    c.decode_kernel = _lib.DECODE_PORTABLE
-    out_p, lse_p = c.decode_attention(0, q, bidx, pos)
-    assert_attention_close(out_t, lse_t, out_p.float().cpu(), lse_p.cpu(), "tma vs portable")
-    # oracle on three rows (gathered through the product's own gather, itself bit-exact-tested)
-    for i in (0, 31, 63):
+    c.insert_kv(0, k, v, input_pos=pos.cuda().view(-1, 1), batch_idx=bidx.cuda())
+    o.append_decode(0, bidx, pos, case.k_new, case.v_new)
+    ref_out, ref_lse = orc.decode_attention(o, 0, case.q.float(), bidx, pos)
+    for name, kern in KERNELS.items():
+        c.decode_kernel = kern
+        out, lse = c.decode_attention(0, q, bidx.cuda(), pos.cuda())
+        assert_attention_close(out, lse, ref_out, ref_lse, f"config 2, all 64 rows, {name}")
+        out2, lse2 = c.decode_attention(0, q, bidx.cuda(), pos.cuda())
+        assert torch.equal(out, out2) and torch.equal(lse, lse2), name
+    # the pool, read back through the page table, holds exactly what the oracle's pool holds
+    for i in (0, 17, 40, 63):
         gk, gv = c.gather(0, slots[i], case.lens[i] + 1)
-        s = torch.einsum("hrd,hnd->hrn", q[i, :, 0].float().view(8, 2, 128), gk.float()) * 128 ** -0.5
-        ref = torch.einsum("hrn,hnd->hrd", torch.softmax(s, -1), gv.float()).reshape(16, 128)
-        assert_attention_close(out_t[i, :, 0], lse_t[i, :, 0], ref.cpu(), torch.logsumexp(s, -1).reshape(16).cpu(),
-                               f"row {i}")
+        addr, valid = o.key_addresses(slots[i], case.lens[i] + 1)
+        assert valid.all()
+        assert torch.equal(gk.cpu(), o.kv_cache[0, 0, 0][:, torch.from_numpy(addr)])
+        assert torch.equal(gv.cpu(), o.kv_cache[0, 1, 0][:, torch.from_numpy(addr)])
+    c.check_status()
+
+
+def test_rows_never_appended_may_hold_anything():
+    """The pool a caller hands over through the C ABI need not be zero-filled: rows behind a sequence's last
+    key (the tail of its last page, fetched with the page) may hold NaN or Inf bit patterns without reaching
+    any result."""
+    case = _random_case(626, B=7, lens=[1, 15, 16, 17, 130, 255, 300], n_pages=40, max_batch_size=9)
+    o, _, obidx, opos, ok, ov, oq = oracle_from_case(case)
+    ref_out, ref_lse = orc.decode_attention(o, 0, oq.float(), obidx, opos)
+    from fpkv.paged_attention import PagedKVCache as Cache
+    c = Cache(case.n_pages, case.P, case.max_batch_size, case.Hkv, case.D, 1, case.dtype, "cuda")
+    c.kv_cache.view(torch.int16).fill_(-1)                       # 0xFFFF: a NaN in bf16 and fp16
+    c.free_pages = list(case.free_pages)
+    slots = []
+    for L, kh, vh in zip(case.lens, case.k_hist, case.v_hist):
+        s = c.allocate(); slots.append(s); c.reserve(s, None, L + 1)
+        c.insert_kv(0, kh.cuda(), vh.cuda(), input_pos=torch.arange(L, device="cuda").view(1, L),
+                    batch_idx=torch.full((1, L), s, device="cuda"))
+    bidx = torch.tensor(slots, device="cuda"); pos = torch.tensor(case.lens, dtype=torch.int32, device="cuda")
+    c.insert_kv(0, case.k_new.cuda(), case.v_new.cuda(), input_pos=pos.view(-1, 1), batch_idx=bidx)
+    for name, kern in KERNELS.items():
+        c.decode_kernel = kern
+        out, lse = c.decode_attention(0, case.q.cuda(), bidx, pos)
+        assert torch.isfinite(out.float()).all(), name
+        assert_attention_close(out, lse, ref_out, ref_lse, f"NaN-filled pool, {name}")
     c.check_status()
 
 

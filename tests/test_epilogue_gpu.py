@@ -5,7 +5,8 @@ applied to the un-fused results."""
 import pytest
 import torch
 
-from fpkv import _lib, workloads as wl
+from fpkv import _lib
+import workloads as wl
 from fpkv.paged_attention import PagedKVCache, paged_attention
 from oracle import paged_kv_oracle as orc
 from helpers import product_from_case

@@ -5,7 +5,7 @@ replay with new positions equals the eager result."""
 import pytest
 import torch
 
-from fpkv import workloads as wl
+import workloads as wl
 from helpers import product_from_case
 
 pytestmark = pytest.mark.gpu

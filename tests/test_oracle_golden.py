@@ -8,7 +8,7 @@ import numpy as np
 import pytest
 import torch
 
-from fpkv import workloads as wl
+import workloads as wl
 from oracle import paged_kv_oracle as orc
 from helpers import GOLDEN, golden, oracle_from_case
 

@@ -8,7 +8,7 @@ import numpy as np
 import pytest
 import torch
 
-from fpkv import workloads as wl
+import workloads as wl
 from fpkv.paged_attention import PagedKVCache
 from oracle import paged_kv_oracle as orc
 from test_oracle_golden import pre_attention_case

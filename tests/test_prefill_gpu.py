@@ -5,7 +5,8 @@ import numpy as np
 import pytest
 import torch
 
-from fpkv import _lib, workloads as wl
+from fpkv import _lib
+import workloads as wl
 from fpkv.paged_attention import PagedKVCache, paged_attention
 from oracle import paged_kv_oracle as orc
 from helpers import assert_attention_close, golden
@@ -15,8 +16,10 @@ pytestmark = pytest.mark.gpu
 T = wl.image_text_tokens
 
 
-def run_product(case, n_pages, max_batch, dtype=torch.bfloat16, kernel=0):
+def run_product(case, n_pages, max_batch, dtype=torch.bfloat16, kernel=0, poison=False):
     c = PagedKVCache(n_pages, case.P, max_batch, case.Hkv, case.D, 1, dtype, "cuda")
+    if poison:                                     # every row that is never appended holds NaN bit patterns
+        c.kv_cache.view(torch.int16).fill_(-1)
     c.prefill_kernel = kernel
     slots = []
     for toks in case.seq_tokens:
@@ -150,3 +153,17 @@ def test_random_prompt_layouts(seed):
         ref_out, ref_lse = oracle_prefill(case, slots)
         compare_live_rows(case, out, lse, ref_out, ref_lse, f"random layout {seed}, kernel {kernel}")
         c.check_status()
+
+
+@pytest.mark.parametrize("kernel", [_lib.PREFILL_TC, _lib.PREFILL_PORTABLE])
+def test_rows_never_appended_may_hold_anything(kernel):
+    """A pool that was not zero-filled: the tails of the sequences' last pages (fetched with the page) and
+    reserved page 0 hold NaN bit patterns; no result is touched by them."""
+    seqs = [T(0, 100, 30), T(0, 0, 129), T(3, 250, 1), T(0, 0, 5)]
+    case = wl.make_prefill_case(4141, seqs, Hq=8, Hkv=4, D=128, dtype=torch.bfloat16)
+    c, slots, bidx, ipos, mask, out, lse = run_product(case, 12, 6, kernel=kernel, poison=True)
+    ref_out, ref_lse = oracle_prefill(case, slots)
+    live = case.seq_index.view(-1) > 0
+    assert torch.isfinite(out[0][:, live].float()).all()
+    compare_live_rows(case, out, lse, ref_out, ref_lse, f"NaN-filled pool, kernel {kernel}")
+    c.check_status()

@@ -12,7 +12,7 @@ import pytest
 import torch
 import torch.nn.functional as F
 
-from fpkv import workloads as wl
+import workloads as wl
 from fpkv.paged_attention import PagedKVCache
 from oracle import paged_kv_oracle as orc
 

@@ -12,7 +12,8 @@ import math
 import pytest
 import torch
 
-from fpkv import _lib, workloads as wl
+from fpkv import _lib
+import workloads as wl
 from helpers import MAX_ABS, LSE_ABS, product_from_case
 
 pytestmark = pytest.mark.gpu
