@@ -858,6 +858,7 @@ def run_fpkv(args):
         line["build_id"] = _lib.build_id()
         if rk.world == 1 and not args.kernels_only and args.only == "all":
             line["cpu_baseline"] = cpu_baseline_sample()
+            line["gpu_competitor"] = gpu_competitor_sample()
         print(json.dumps(line), flush=True)
     rk.close()
 
@@ -982,6 +983,104 @@ def cpu_baseline_sample():
         return {"value": None, "unit": "GB/s", "cores": None, "kind": "reference", "sample": "failed: " + repr(e)[:200]}
 
 
+def gpu_competitor_sample():
+    """The reference's own GPU path on this box, in its own process (it compiles FlexAttention with
+    torch.compile; a failure or a slow first compile must not take the benchmark down)."""
+    try:
+        env = {k: v for k, v in os.environ.items() if k not in ("RANK", "WORLD_SIZE", "LOCAL_RANK", "TORCHDYNAMO_DISABLE")}
+        res = subprocess.run([sys.executable, os.path.abspath(__file__), "--impl", "reference-gpu", "--steps", "50", "--warmup", "3"],
+                             capture_output=True, text=True, timeout=300, env=env)
+        return json.loads(res.stdout.strip().splitlines()[-1])
+    except Exception as e:
+        return {"impl": "reference-gpu", "unavailable": repr(e)[:200]}
+
+
+def run_reference_gpu(args):
+    """--impl reference-gpu: the reference's own GPU path for the same step, for context (not the target and not
+    the reference arm): its PagedKVCache on the device with 16 expanded heads, its per-step mask slicing and
+    conversion, its append and its compiled FlexAttention decode call, on the 64 seeded sequences in a pool
+    compacted to the pages in use (the reference's mask conversion allocates batch x n_pages index tensors, and
+    its kernel walks them, so the pool size is part of its cost)."""
+    import types
+    import workloads as wl
+    root = reference_root()
+    if root is None:
+        print(json.dumps({"impl": "reference-gpu", "unavailable": "the reference project is not installed under baseline/_ref"}))
+        return
+    assert torch.cuda.is_available()
+    sys.path.insert(0, root)
+    stub = types.ModuleType("pycocotools"); stub.mask = types.ModuleType("pycocotools.mask")
+    sys.modules.setdefault("pycocotools", stub); sys.modules.setdefault("pycocotools.mask", stub.mask)
+    from torch.nn.attention.flex_attention import AuxRequest
+    from falcon_perception.attention import compiled_flex_attn_decode
+    from falcon_perception.paged_attention import PagedKVCache as RefCache
+    from falcon_perception.paged_inference import PagedInferenceEngine
+    device = torch.device("cuda", 0)
+    torch.cuda.set_device(device)
+    case = wl.config2_case(B=BATCH, n_pages=N_PAGES, len_lo=LEN_LO, len_hi=LEN_HI, seed=2002)
+    lens, n = case.lens, BATCH
+    n_pages = sum((L + 1 + WINDOW + P - 1) // P for L in lens) + 1
+    c = RefCache(n_pages, P, n + 1, HQ, D, 1, torch.bfloat16, device)
+    c.free_pages = (torch.randperm(n_pages - 1, generator=torch.Generator().manual_seed(1)) + 1).tolist()
+    slots = []
+    for L in lens:
+        s = c.allocate(); c.reserve(s, torch.tensor([s], device=device), L + 1 + WINDOW); slots.append(s)
+    c.kv_cache.normal_(0, D ** -0.5)
+    g = torch.Generator(device=device).manual_seed(2)
+    q = (torch.randn((n, HQ, 1, D), device=device, generator=g) * D ** -0.5).bfloat16()
+    k = (torch.randn((n, HQ, 1, D), device=device, generator=g) * D ** -0.5).bfloat16()
+    v = (torch.randn((n, HQ, 1, D), device=device, generator=g) * D ** -0.5).bfloat16()
+    engine = types.SimpleNamespace(block_mask=c.create_causal_blockmask(B=n + 1, L=(LEN_HI // P + 2) * P))
+    bidx = torch.tensor(slots, device=device)
+    pos_all = (torch.tensor(lens, dtype=torch.int32).view(1, n) + torch.arange(WINDOW, dtype=torch.int32).view(-1, 1)).to(device)
+
+    def step(i):
+        pos = pos_all[i % WINDOW]
+        mask = PagedInferenceEngine.get_decoding_block_mask(engine, bidx, pos)
+        mask = c.convert_logical_block_mask(mask, bidx)
+        xk, xv = c.insert_kv(0, k, v, input_pos=pos.view(-1, 1), batch_idx=bidx)
+        return compiled_flex_attn_decode(q, xk, xv, block_mask=mask, return_aux=AuxRequest(lse=True))
+    t0 = time.perf_counter()
+    for i in range(max(args.warmup, 3)):
+        step(i)
+    torch.cuda.synchronize()
+    compile_s = time.perf_counter() - t0
+    K = args.steps
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for i in range(K):
+        step(i)
+    e1.record()
+    torch.cuda.synchronize()
+    ms = e0.elapsed_time(e1) / K
+    # the same step replayed from a CUDA graph, as the reference engine runs decode (paged_inference.py:865-952)
+    ms_graph = None
+    try:
+        side = torch.cuda.Stream()
+        side.wait_stream(torch.cuda.current_stream())
+        gr = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(gr, stream=side):
+            step(0)
+        torch.cuda.synchronize()
+        e0.record()
+        for i in range(K):
+            gr.replay()
+        e1.record()
+        torch.cuda.synchronize()
+        ms_graph = e0.elapsed_time(e1) / K
+    except Exception as e:
+        ms_graph = "capture failed: " + repr(e)[:120]
+    nbytes = sum(step_bytes([L + i % WINDOW for L in lens]) for i in range(K)) / K
+    best = ms_graph if isinstance(ms_graph, float) else ms
+    print(json.dumps({
+        "impl": "reference-gpu", "metric": "paged_decode_attn_kv_gbps", "value": nbytes / (best * 1e-3) / 1e9, "unit": "GB/s",
+        "ms_per_step": ms, "ms_per_step_graph_replay": ms_graph, "steps": K, "first_calls_s": round(compile_s, 1),
+        "config": {"workload": WORKLOAD, "pool": f"{n_pages}-page pool (compacted to the pages in use), 16 expanded heads"},
+        "what": "the reference's own GPU path: mask slicing + conversion, append (PagedKVCache.assign), compiled FlexAttention "
+                "decode; bytes counted as for fpkv (8 real KV heads), so the figure is comparable with `value`; it reads "
+                "twice those bytes"}), flush=True)
+
+
 def run_reference(args):
     """--impl reference: the reference's own CPU implementation of the path on the host cores, same metric and
     workload string as the GPU arm.  Rank 0 alone runs it; its throughput does not depend on how many GPU
@@ -1022,7 +1121,7 @@ def main():
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=200)
     ap.add_argument("--warmup", type=int, default=20)
-    ap.add_argument("--impl", default="fpkv", choices=["fpkv", "reference"])
+    ap.add_argument("--impl", default="fpkv", choices=["fpkv", "reference", "reference-gpu"])
     ap.add_argument("--pool-pages", type=int, default=N_PAGES,
                     help="pages in the pool (default 65536 = 32 GiB; profiling captures use a small pool)")
     ap.add_argument("--batch", type=int, default=BATCH, help="sequences per GPU (default 64: the headline workload)")
@@ -1036,6 +1135,8 @@ def main():
     args.warmup = max(args.warmup, 3)
     if args.impl == "reference":
         run_reference(args)
+    elif args.impl == "reference-gpu":
+        run_reference_gpu(args)
     else:
         run_fpkv(args)
 
