@@ -18,36 +18,40 @@
 // been appended before its queries run), so the same kernel serves a whole
 // prompt, a chunk of one, or a step that mixes both.
 //
-// One CTA = one 128-row query tile of a PAIR of query heads that share a stored
+// Work item = one 128-row query tile of a PAIR of query heads that share a stored
 // head (a single head when the GQA ratio is odd): the K/V tile staged in shared
-// memory feeds both heads, which halves the L2 traffic per FLOP.  Per key tile
-// and head:
-//     S = Q K^T    128x128x128, A = Q (shared, K-major), B = K tile (shared, K-major) -> TMEM
-//     O += P V     128x128x128, A = P (TMEM, written in place over S), B = V tile (shared, MN-major) -> TMEM
-// Tensor memory holds S/P and O of both heads (4 x 128 columns = all 512), so
-// each head is one dependent chain  S -> softmax -> P.V -> next S  and only two
-// chains are in flight.  Two resources bound a (tile, head pair) at 2048 clocks
-// each: the tensor pipe (32 MMAs of 64 clocks) and the exponential unit (2 x
-// 128 x 128 results at 16 per clock per SM); the kernel is about keeping both
-// busy at once.
-//   * Warps 0-7 do the softmax, all eight on ONE head's tile at a time, two
-//     threads per query row (warps w and w + 4 reach the same 32 TMEM lanes and
-//     take 64 key columns each).  Two warps per scheduler keep the exponential
-//     unit saturated; a quarter of the exponentials run as a polynomial on the
-//     FMA pipe instead.  While they work on one head, the other head's MMAs run.
-//   * Warp 8 is the TMA producer (2-stage K and V rings).
+// memory feeds both heads, which halves the L2 traffic per FLOP.  A key tile is
+// worked through in two halves of 64 keys; per half and head:
+//     S = Q K^T    128x64x128,  A = Q (shared, K-major), B = 64 rows of the K tile (shared, K-major) -> TMEM
+//     O += P V     128x128x64,  A = P (TMEM, written over the first half of the S columns), B = 64 rows of the V
+//                               tile (shared, MN-major) -> TMEM
+// Tensor memory holds S/P and O of both heads (4 x 128 columns = all 512).  The
+// two halves of a head's score columns are independent buffers: as soon as the
+// P.V of one half is issued, the next key tile's Q.K^T over the same 64 keys is
+// issued behind it, so the scores of a half are ready again by the time the
+// softmax threads have dealt with the other half.  Four chains  S -> softmax ->
+// P.V -> next S  are in flight per SM (two heads x two halves).
+//   * The CTAs are persistent: one per SM, each walking its share of the items
+//     (longest first, dealt out boustrophedon).  Every barrier carries its phase
+//     across items, so the copies and the first Q.K^T of the next item run while
+//     the softmax warps still write the previous item's output.
+//   * Warps 0-3 are the softmax group of head 0, warps 4-7 of head 1: one thread
+//     per query row, 64 scores per step (load, row maximum, exponentials, packed
+//     P store, hand-over).  The groups run independently, so that one group's
+//     loads and barrier traffic overlap the other group's exponentials.
+//   * Warp 8 is the TMA producer (2-stage K and V rings running across items).
 //   * Warps 9 and 10 issue the MMAs, one warp per head: the tensor pipe takes the
 //     MMAs of a thread one after the other and idles through whatever else that
-//     thread does (a barrier wait costs it ~30-100 clocks), so each head gets its
-//     own issuer and waits for operand tiles before it waits for P.
-// The running maximum is only raised when a tile exceeds it by more than 2^8
+//     thread does, so each head gets its own issuer.
+//   * Warp 11 prepares the next item while the current one runs: slot, visible
+//     extent of every row, page ids of all key tiles (two descriptor buffers).
+// The running maximum is only raised when a half exceeds it by more than 2^8
 // (probabilities stay below 256, exact in fp32 and harmless in bf16), so O in
-// TMEM is rarely rescaled.  The output tile is staged through the idle query
-// buffer so that rows leave in whole lines.
+// TMEM is rarely rescaled.  Each thread owns a whole output row and writes it
+// straight from registers (256 contiguous bytes).
 // Every wait is a bounded mbarrier wait; on expiry the CTA raises
-// FPKV_STATUS_TIMEOUT, the MMA and copy warps leave their loops, the softmax
-// warps run theirs to the end without waiting (they meet at named barriers),
-// TMEM is freed and the kernel returns.
+// FPKV_STATUS_TIMEOUT, every role leaves its loops, the copies and MMAs in
+// flight are drained (bounded), TMEM is freed and the kernel returns.
 
 #include <cuda.h>
 #include <type_traits>
@@ -60,17 +64,14 @@ constexpr int kTileM = 128, kTileN = 128, kHeadDim = 128, kPage = 128;
 constexpr int kTileBytes = 128 * 128 * 2;              // any 128 x 128 16-bit tile
 constexpr int kHalfBytes = kTileBytes / 2;             // 64 columns (128 bytes) x 128 rows
 constexpr int kStages = 2;
-constexpr int kSoftmaxWarps = 4;                       // per key-column half: warps 0-3 take columns [0,64), warps 4-7 [64,128)
+constexpr int kSoftmaxWarps = 4;                       // per head: warps 0-3 are head 0's softmax group, warps 4-7 head 1's
 constexpr int kLoadWarp = 8, kMmaWarp = 9;              // warps 9 and 10 issue the MMAs of head 0 and head 1 of the pair
-constexpr int kPrefillThreads = 12 * 32;               // warp 11 idles: registers are granted per four warps anyway
+constexpr int kScoutWarp = 11;                         // prepares the next item's descriptor
+constexpr int kPrefillThreads = 12 * 32;
 constexpr int kMaxKeyTiles = 512;                      // 65 536 keys per sequence
 constexpr uint32_t kSpin = 1u << 22;
 constexpr uint32_t kTmemCols = 512;                    // S/P head 0, S/P head 1, O head 0, O head 1: 128 columns each
 constexpr float kRescaleThreshold = 8.f;
-#ifndef FPKV_POLY_EVERY
-#define FPKV_POLY_EVERY 4
-#endif
-constexpr int kPolyEvery = FPKV_POLY_EVERY;            // one pair in this many takes the polynomial 2^x (0x7fffffff: none)
 
 __device__ __forceinline__ uint32_t s32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
 __device__ __forceinline__ void bar_init(uint32_t bar, uint32_t count) {
@@ -120,13 +121,13 @@ __device__ __forceinline__ uint64_t umma_desc(uint32_t smem_addr, uint32_t lbo_b
     return d;
 }
 // Instruction descriptor for kind::f16: D = f32, A/B = bf16 or f16, M = 128, N = 128.
-__device__ __forceinline__ uint32_t umma_idesc(bool bf16, bool b_mn_major) {
+__device__ __forceinline__ uint32_t umma_idesc(bool bf16, bool b_mn_major, int n = kTileN) {
     uint32_t d = 0;
     d |= 1u << 4;                                      // accumulator format f32
     d |= (bf16 ? 1u : 0u) << 7;                        // A format
     d |= (bf16 ? 1u : 0u) << 10;                       // B format
     d |= (b_mn_major ? 1u : 0u) << 16;                 // B major: 0 = K, 1 = MN
-    d |= (uint32_t)(kTileN >> 3) << 17;
+    d |= (uint32_t)(n >> 3) << 17;
     d |= (uint32_t)(kTileM >> 4) << 24;
     return d;
 }
@@ -236,11 +237,7 @@ __device__ __forceinline__ float ex2(float x) {
     return y;
 }
 
-// 2^x for a pair of arguments on the FMA and integer pipes instead of the exponential unit, which is the narrow
-// resource of the softmax phase (16 results per clock per SM): round to the nearest integer with the
-// 1.5 * 2^23 trick, a degree-3 polynomial on the remainder in [-0.5, 0.5] (maximum relative error 7.5e-5, far
-// below the 16-bit rounding of the probabilities), the integer added into the exponent bits.  Arguments
-// are clamped below at -126; they never exceed 8 here.  Packed f32x2 arithmetic halves the instruction count.
+// Packed fp32 pairs: one instruction scales two scores or adds two probabilities into the row sums.
 struct F2 { float x, y; };
 __device__ __forceinline__ F2 fma2(F2 a, F2 b, F2 c) {
     F2 d;
@@ -255,57 +252,101 @@ __device__ __forceinline__ F2 add2(F2 a, F2 b) {
         : "=f"(d.x), "=f"(d.y) : "f"(a.x), "f"(a.y), "f"(b.x), "f"(b.y));
     return d;
 }
-__device__ __forceinline__ F2 ex2_poly2(F2 x) {
-    x.x = fmaxf(x.x, -126.f); x.y = fmaxf(x.y, -126.f);
-    const F2 fl = add2(x, F2{12582912.f, 12582912.f});
-    const F2 n = add2(fl, F2{-12582912.f, -12582912.f});
-    const F2 f = add2(x, F2{-n.x, -n.y});
-    F2 p = fma2(f, F2{0.05517164617776871f, 0.05517164617776871f}, F2{0.2426111251115799f, 0.2426111251115799f});
-    p = fma2(p, f, F2{0.6932609677314758f, 0.6932609677314758f});
-    p = fma2(p, f, F2{0.9999280571937561f, 0.9999280571937561f});
-    F2 r;
-    r.x = __int_as_float(__float_as_int(p.x) + (__float_as_int(fl.x) << 23));
-    r.y = __int_as_float(__float_as_int(p.y) + (__float_as_int(fl.y) << 23));
-    return r;
+
+
+// O += P V over one half of a key tile (64 keys, four K = 16 steps): P from tensor memory (8 packed columns per 16
+// keys, starting at `a`), V rows from shared memory (MN-major, 16 rows = 2 KiB per step, starting at row 64 * kHalf).
+// `acc_first` is the accumulate flag of the first MMA.
+template <int kHalf>
+__device__ __forceinline__ void issue_pv_half(uint32_t d, uint32_t a, uint32_t b_lo, uint32_t hi, uint32_t idesc, uint32_t acc_first) {
+#pragma unroll
+    for (int k = 0; k < 4; ++k)
+        umma_ts(d, a + k * 8, b_lo + (kHalf * 4 + k) * ((16 * 128) >> 4), hi, idesc, k > 0 ? 1u : acc_first);
 }
-
-
-// S = Q K^T: eight K = 16 steps (32 bytes along the 128-byte swizzled rows, second 64-element half 16 KiB on), then
-// the commit that tells the softmax group.
-__device__ __forceinline__ void issue_qk_gemm(uint32_t d, uint32_t a_lo, uint32_t b_lo, uint32_t hi, uint32_t idesc, uint32_t bar) {
+// S half = Q K^T over 64 keys (N = 64): the K tile's rows [64 * kHalf, +64), i.e. 8 KiB into each 64-element column block.
+template <int kHalf>
+__device__ __forceinline__ void issue_qk_half(uint32_t d, uint32_t a_lo, uint32_t b_lo, uint32_t hi, uint32_t idesc, uint32_t bar) {
 #pragma unroll
     for (int k = 0; k < kHeadDim / 16; ++k) {
         const uint32_t off = ((k >> 2) * kHalfBytes + (k & 3) * 32) >> 4;
-        umma(d, a_lo + off, hi, b_lo + off, hi, idesc, k > 0);
+        umma(d, a_lo + off, hi, b_lo + off + ((kHalf * 64 * 128) >> 4), hi, idesc, k > 0);
     }
     umma_commit(bar);
 }
-// O += P V: P from tensor memory (8 packed columns per 16 keys), V rows from shared memory (MN-major, 16 rows = 2 KiB per step).
-// Issued in two halves of four steps (keys 0-63, 64-127) so that the first can run while the softmax group still
-// exponentiates the second half of the tile.
-template <int kHalf>
-__device__ __forceinline__ void issue_pv_gemm(uint32_t d, uint32_t a, uint32_t b_lo, uint32_t hi, uint32_t idesc, uint32_t acc0) {
-#pragma unroll
-    for (int k = kHalf * 4; k < kHalf * 4 + 4; ++k)
-        umma_ts(d, a + k * 8, b_lo + k * ((16 * 128) >> 4), hi, idesc, k > 0 ? 1u : acc0);
-}
-
 
 struct PrefillParams {
     const int64_t* page_table;
     const int64_t* p2l;
     const int64_t* batch_idx;   // [L] slot of each packed token (0 = pad)
     const int32_t* extent;      // [L] number of visible keys of each packed token
-    void* out;                  // (Hq, L, D) contiguous
+    void* out;                  // (Hq, L, D) contiguous, or (L, Hq, D) when token-major
     float* lse;                 // (Hq, L)
     int32_t* status;
     int L, Hq, Hkv, n_pages, max_batch;
     int rows_per_plane;         // n_pages * page_size
     float scale_log2;
-    int is_bf16;
-    int heads_per_cta;          // 2: both query heads of a GQA pair share the staged K/V tiles; 1 otherwise
+    int heads_per_item;         // 2: both query heads of a GQA pair share the staged K/V tiles; 1 otherwise
+    int n_qtiles, n_pairs, n_items;
     Epilogue epi;
 };
+
+// What every role needs to know about a work item, prepared one item ahead by the scout warp.
+struct ItemDesc {
+    int valid;                  // 0: no more work for this CTA
+    int t0;                     // first packed token of the query tile
+    int hq0;                    // first query head of the item
+    int n_tiles;                // key tiles any row of the tile sees
+    int max_extent;             // largest visible-prefix length among the rows
+    int first_bad;              // first key tile whose page is unmapped (n_tiles when all are mapped)
+    int pad_[2];
+    int extent[kTileM];         // visible keys of each row (0: pad, or a row the tile may not hold)
+    int page_row[kMaxKeyTiles]; // pool row of the K tile of key tile j (reserved page 0 when unmapped)
+    unsigned char page_ok[kMaxKeyTiles];
+};
+
+// 64 scores (two 32-column pieces) -> 32 packed probability words, row sum into rs.  valid_cols: how many of the 64
+// columns exist for this row (all of them on the fast path).
+template <typename T, bool kFull>
+__device__ __forceinline__ void probabilities64(const uint32_t (&sv)[2][32], uint32_t (&pk)[32], F2 (&rs)[2], float scale_log2,
+                                                float neg_m, int valid_cols) {
+#pragma unroll
+    for (int c2 = 0; c2 < 2; ++c2) {
+#pragma unroll
+        for (int c = 0; c < 32; c += 2) {
+            // scale and reference maximum for both scores of the pair in one packed FMA
+            const F2 x = fma2(F2{__uint_as_float(sv[c2][c]), __uint_as_float(sv[c2][c + 1])}, F2{scale_log2, scale_log2},
+                              F2{neg_m, neg_m});
+            F2 p;
+            p.x = ex2(x.x); p.y = ex2(x.y);
+            if (!kFull) {
+                if (c2 * 32 + c >= valid_cols) p.x = 0.f;
+                if (c2 * 32 + c + 1 >= valid_cols) p.y = 0.f;
+            }
+            rs[(c >> 1) & 1] = add2(rs[(c >> 1) & 1], p);                      // packed row sums, two accumulators
+            pk[c2 * 16 + c / 2] = pack2<T>(p.x, p.y);
+        }
+    }
+}
+template <bool kFull>
+__device__ __forceinline__ float max64(const uint32_t (&sv)[2][32], int valid_cols) {
+    if (kFull) {
+        float m2[2];
+#pragma unroll
+        for (int c2 = 0; c2 < 2; ++c2) {
+            m2[c2] = max3f(__uint_as_float(sv[c2][0]), __uint_as_float(sv[c2][1]), __uint_as_float(sv[c2][2]));
+#pragma unroll
+            for (int c = 3; c + 1 < 32; c += 2) m2[c2] = max3f(m2[c2], __uint_as_float(sv[c2][c]), __uint_as_float(sv[c2][c + 1]));
+            m2[c2] = fmaxf(m2[c2], __uint_as_float(sv[c2][31]));
+        }
+        return fmaxf(m2[0], m2[1]);
+    }
+    float mx = -INFINITY;
+#pragma unroll
+    for (int c2 = 0; c2 < 2; ++c2)
+#pragma unroll
+        for (int c = 0; c < 32; ++c) if (c2 * 32 + c < valid_cols) mx = fmaxf(mx, __uint_as_float(sv[c2][c]));
+    return mx;
+}
 
 template <typename T>
 __global__ void __launch_bounds__(kPrefillThreads, 1)
@@ -318,38 +359,39 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_consta
     uint8_t* k_s = q_s + 2 * kTileBytes;                   // kStages x 32 KiB
     uint8_t* v_s = k_s + kStages * kTileBytes;             // kStages x 32 KiB
     uint64_t* bars = reinterpret_cast<uint64_t*>(v_s + kStages * kTileBytes);
-    int* ints = reinterpret_cast<int*>(bars + 24);
+    int* ints = reinterpret_cast<int*>(bars + 48);
     volatile int* abort_flag = ints;                       // [0] abort, [1] TMEM base
     int* tmem_slot = ints + 1;
-    int* warp_red = ints + 4;                              // [8] per-warp reductions of the prologue
-    int* page_row = ints + 16;                             // [kMaxKeyTiles] pool row of key tile j (page 0 when unmapped)
-    unsigned char* page_ok = reinterpret_cast<unsigned char*>(page_row + kMaxKeyTiles);   // [kMaxKeyTiles]
-    float* xch = reinterpret_cast<float*>(page_ok + kMaxKeyTiles);                         // [2][2][128] row max / row sum exchange
+    ItemDesc* desc = reinterpret_cast<ItemDesc*>(ints + 16);   // [2]
 
-    const uint32_t q_full = s32(bars + 0);
-    const uint32_t k_full0 = s32(bars + 1), v_full0 = s32(bars + 3), k_empty0 = s32(bars + 5), v_empty0 = s32(bars + 7);
-    const uint32_t s_full0 = s32(bars + 9);                // [2] one per head of the pair
-    const uint32_t p_full0 = s32(bars + 11);               // [2] P of the tile written (all eight softmax warps arrive)
-    const uint32_t all_done0 = s32(bars + 13);             // [2] one per head
+    // mbarriers; every one keeps its phase across items
+    const uint32_t desc_full0 = s32(bars + 0), desc_empty0 = s32(bars + 2);            // [2] descriptor buffers
+    const uint32_t q_full0 = s32(bars + 4), q_empty0 = s32(bars + 6);                  // [2] per head
+    const uint32_t k_full0 = s32(bars + 8), v_full0 = s32(bars + 8 + kStages);
+    const uint32_t k_empty0 = s32(bars + 8 + 2 * kStages), v_empty0 = s32(bars + 8 + 3 * kStages);
+    const uint32_t s_half0 = s32(bars + 8 + 4 * kStages);                              // [head][half] scores of 64 keys are in TMEM
+    const uint32_t p_half0 = s_half0 + 32;                                             // [head][half] P of 64 keys written
+    const uint32_t pv_done0 = s_half0 + 64;                                            // [2] a half's P.V has completed (one phase per half)
+    const uint32_t all_done0 = s_half0 + 80, o_free0 = s_half0 + 96;                   // [2] last P.V complete / O read by the epilogue
+    const uint32_t drain0 = s_half0 + 112;                                             // [2] give-up path: a head's MMAs have completed
 
     const int tid = threadIdx.x, warp = tid / 32, lane = tid % 32;
-    // Query tiles are taken from the end of the packed row backwards, all head pairs of a tile before the next tile:
-    // under a causal mask the later tiles of a sequence see more keys, and the long CTAs should start first.
-    const int t0 = (int)(gridDim.y - 1 - blockIdx.y) * kTileM;   // first packed token of the query tile
-    const int heads = prm.heads_per_cta;                   // 1 or 2 query heads of one stored head
-    const int hq0 = blockIdx.x * heads;
-    const int hkv = hq0 / (prm.Hq / prm.Hkv);
-    const bool is_softmax = warp < 2 * kSoftmaxWarps;
+    const int heads = prm.heads_per_item;                  // 1 or 2 query heads of one stored head
+    const int n_rep = prm.Hq / prm.Hkv;
 
-    // ---- prologue ----------------------------------------------------------
+    // ---- set-up, once per CTA ------------------------------------------------
     if (tid == 0) {
-        bar_init(q_full, 1);
+        for (int b = 0; b < 2; ++b) {
+            bar_init(desc_full0 + 8 * b, 1); bar_init(desc_empty0 + 8 * b, 1 + 5 * heads);
+            bar_init(q_full0 + 8 * b, 1); bar_init(q_empty0 + 8 * b, 1);
+            for (int hf = 0; hf < 2; ++hf) { bar_init(s_half0 + 16 * b + 8 * hf, 1); bar_init(p_half0 + 16 * b + 8 * hf, kSoftmaxWarps); }
+            bar_init(pv_done0 + 8 * b, 1); bar_init(all_done0 + 8 * b, 1); bar_init(o_free0 + 8 * b, kSoftmaxWarps);
+            bar_init(drain0 + 8 * b, 1);
+        }
         for (int s = 0; s < kStages; ++s) {
             bar_init(k_full0 + 8 * s, 1); bar_init(v_full0 + 8 * s, 1);
             bar_init(k_empty0 + 8 * s, heads); bar_init(v_empty0 + 8 * s, heads);     // one commit per head's MMA warp
         }
-        for (int g = 0; g < 2; ++g) { bar_init(s_full0 + 8 * g, 1); bar_init(p_full0 + 8 * g, 2 * kSoftmaxWarps); }
-        bar_init(all_done0, 1); bar_init(all_done0 + 8, 1);
         *abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
@@ -357,94 +399,114 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_consta
         asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(s32(tmem_slot)), "r"(kTmemCols) : "memory");
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
     }
-    // slot and extent of this thread's row (both softmax groups look at the same 128 rows);
-    // the tile's slot is the largest one (pads are slot 0)
-    const int row = tid % kTileM;
-    int my_slot = 0, my_extent = 0;
-    if (is_softmax && t0 + row < prm.L) {
-        const long long s = prm.batch_idx[t0 + row];
-        const int e = prm.extent[t0 + row];                // both loads in flight together
-        if (s < 0 || s >= prm.max_batch) raise_status(prm.status, FPKV_STATUS_BAD_SLOT);
-        else { my_slot = (int)s; my_extent = s > 0 ? e : 0; }
-        if (my_extent < 0) my_extent = 0;
-    }
-    {
-        int sl = my_slot;
-#pragma unroll
-        for (int o = 16; o > 0; o >>= 1) sl = max(sl, __shfl_xor_sync(0xffffffffu, sl, o));
-        if (lane == 0 && warp < kSoftmaxWarps) warp_red[warp] = sl;
-    }
     tc_fence_before();
     __syncthreads();
     tc_fence_after();
-    const int slot = max(max(warp_red[0], warp_red[1]), max(warp_red[2], warp_red[3]));
-    // The copy warp starts as early as it can: the query tile depends on nothing (issued now), the first K / V
-    // tile only on the sequence's first page id (load started now, used after the next barrier), so that the first
-    // Q.K^T does not wait for the rest of the set-up.
-    const bool early = warp == kLoadWarp && lane == 0 && slot > 0;
-    long long early_pg = -1;
-    if (early) {
-        bar_expect_tx(q_full, heads * kTileBytes);
-        for (int g = 0; g < heads; ++g) tma_4d(s32(q_s + g * kTileBytes), &q_map, 0, t0, 0, hq0 + g, q_full);
-        early_pg = prm.page_table[(long long)slot * prm.n_pages];
-    }
-    if (my_slot != 0 && my_slot != slot) {                 // two live sequences in one query tile: not supported
-        raise_status(prm.status, FPKV_STATUS_BAD_SLOT);
-        my_extent = 0;
-    }
-    if ((long long)my_extent > (long long)prm.n_pages * kPage) { raise_status(prm.status, FPKV_STATUS_BAD_POS); my_extent = 0; }
-    {
-        int ex = my_extent;
-#pragma unroll
-        for (int o = 16; o > 0; o >>= 1) ex = max(ex, __shfl_xor_sync(0xffffffffu, ex, o));
-        if (lane == 0 && warp < kSoftmaxWarps) warp_red[4 + warp] = ex;
-    }
-    __syncthreads();
-    const int max_extent = max(max(warp_red[4], warp_red[5]), max(warp_red[6], warp_red[7]));
-    int n_tiles = (max_extent + kTileN - 1) / kTileN;
-    if (n_tiles > kMaxKeyTiles) { if (tid == 0) raise_status(prm.status, FPKV_STATUS_BAD_POS); n_tiles = kMaxKeyTiles; }
-    int k_requested = 0, v_requested = 0;                  // key / value tiles the copy thread has requested so far
-    if (early && n_tiles > 0) {                            // first K and V tile (an unmapped first page is masked later)
-        k_requested = v_requested = 1;
-        const int row0 = hkv * prm.rows_per_plane + ((early_pg >= 0 && early_pg < prm.n_pages) ? (int)early_pg : 0) * kPage;
-        bar_expect_tx(k_full0, kTileBytes);
-        tma_3d(s32(k_s), &kv_map, 0, row0, 0, k_full0);
-        bar_expect_tx(v_full0, kTileBytes);
-        tma_3d(s32(v_s), &kv_map, 0, row0 + prm.Hkv * prm.rows_per_plane, 0, v_full0);
-    }
-    // page ids of all key tiles, resolved once (coalesced) instead of one dependent load per tile
-    for (int j = tid; j < n_tiles; j += kPrefillThreads) {
-        const long long trow = (long long)slot * prm.n_pages;
-        const long long pg = prm.page_table[trow + j];
-        bool ok = pg >= 0 && pg < prm.n_pages;
-        if (pg >= prm.n_pages) raise_status(prm.status, FPKV_STATUS_BAD_PAGE);
-        if (ok) ok = prm.p2l[trow + pg] >= 0;
-        page_row[j] = hkv * prm.rows_per_plane + (ok ? (int)pg : 0) * kPage;   // unmapped: reserved page 0 (finite junk, masked)
-        page_ok[j] = ok;
-    }
-    __syncthreads();
     const uint32_t tmem = (uint32_t)*tmem_slot;
-    // tensor memory: S/P of head 0 [0,128), S/P of head 1 [128,256), O of head 0 [256,384), O of head 1 [384,512)
+    // tensor memory: S/P of head 0 [0,128), S/P of head 1 [128,256), O of head 0 [256,384), O of head 1 [384,512);
+    // P (packed pairs) goes over the upper half of S: keys 0-63 in columns [64,96), keys 64-127 in [96,128)
     bool alive = true;
+    // copies requested so far by the producer thread (for the give-up path)
+    uint32_t k_requested = 0, v_requested = 0, q_requested[2] = {0, 0};
 
-    if (warp == kLoadWarp) {
-        // ============================== TMA producer ========================
-        if (lane == 0 && n_tiles > 0) {
-            if (!early) {
-                bar_expect_tx(q_full, heads * kTileBytes);
-                for (int g = 0; g < heads; ++g) tma_4d(s32(q_s + g * kTileBytes), &q_map, 0, t0, 0, hq0 + g, q_full);
+    if (warp == kScoutWarp) {
+        // ============================== scout ===================================
+        // Items are numbered longest first (query tiles from the end of the packed row backwards: under a causal
+        // mask the later tiles see more keys; all head pairs of a tile before the next tile) and dealt to the CTAs
+        // in rounds, forwards and backwards alternately, so that every CTA gets a similar mix.
+        const int G = gridDim.x, rounds = (prm.n_items + G - 1) / G;
+        uint32_t it = 0;
+        for (int k = 0; k <= rounds && alive; ++k) {
+            int idx = -1;
+            if (k < rounds) {
+                idx = k * G + ((k & 1) ? G - 1 - (int)blockIdx.x : (int)blockIdx.x);
+                if (idx >= prm.n_items) continue;
             }
-            for (int j = early ? 1 : 0; j < n_tiles; ++j) {
-                const int st = j % kStages;
-                const uint32_t ph = (j / kStages) & 1u;
-                if (!bar_wait(k_empty0 + 8 * st, ph ^ 1u, abort_flag)) { alive = false; break; }
-                bar_expect_tx(k_full0 + 8 * st, kTileBytes);
-                tma_3d(s32(k_s + st * kTileBytes), &kv_map, 0, page_row[j], 0, k_full0 + 8 * st);
-                k_requested = j + 1;
-                if (!bar_wait(v_empty0 + 8 * st, ph ^ 1u, abort_flag)) { alive = false; break; }
-                bar_expect_tx(v_full0 + 8 * st, kTileBytes);
-                tma_3d(s32(v_s + st * kTileBytes), &kv_map, 0, page_row[j] + prm.Hkv * prm.rows_per_plane, 0, v_full0 + 8 * st);
-                v_requested = j + 1;
+            const uint32_t b = it & 1u;
+            if (lane == 0) alive = bar_wait(desc_empty0 + 8 * b, ((it >> 1) & 1u) ^ 1u, abort_flag);
+            alive = __shfl_sync(0xffffffffu, alive, 0);
+            if (!alive) break;
+            ItemDesc* d = desc + b;
+            if (idx < 0) {
+                if (lane == 0) d->valid = 0;
+            } else {
+                const int y = idx / prm.n_pairs, x = idx - y * prm.n_pairs;
+                const int t0 = (prm.n_qtiles - 1 - y) * kTileM, hq0 = x * heads, hkv = hq0 / n_rep;
+                int sl[4], ex[4], smax = 0;
+#pragma unroll
+                for (int r = 0; r < 4; ++r) {
+                    const int tk = t0 + lane + 32 * r;
+                    long long s = 0; int e = 0;
+                    if (tk < prm.L) { s = prm.batch_idx[tk]; e = prm.extent[tk]; }     // both loads in flight together
+                    if (s < 0 || s >= prm.max_batch) { raise_status(prm.status, FPKV_STATUS_BAD_SLOT); s = 0; }
+                    sl[r] = (int)s; ex[r] = (s > 0 && e > 0) ? e : 0;
+                    smax = max(smax, sl[r]);
+                }
+#pragma unroll
+                for (int o = 16; o > 0; o >>= 1) smax = max(smax, __shfl_xor_sync(0xffffffffu, smax, o));   // pads are slot 0
+                int emax = 0;
+#pragma unroll
+                for (int r = 0; r < 4; ++r) {
+                    if (sl[r] != 0 && sl[r] != smax) { raise_status(prm.status, FPKV_STATUS_BAD_SLOT); ex[r] = 0; }   // two live sequences in one tile
+                    if ((long long)ex[r] > (long long)prm.n_pages * kPage) { raise_status(prm.status, FPKV_STATUS_BAD_POS); ex[r] = 0; }
+                    if (ex[r] > kMaxKeyTiles * kTileN) { raise_status(prm.status, FPKV_STATUS_BAD_POS); ex[r] = kMaxKeyTiles * kTileN; }
+                    d->extent[lane + 32 * r] = ex[r];
+                    emax = max(emax, ex[r]);
+                }
+#pragma unroll
+                for (int o = 16; o > 0; o >>= 1) emax = max(emax, __shfl_xor_sync(0xffffffffu, emax, o));
+                const int n_tiles = (emax + kTileN - 1) / kTileN;
+                // page ids of all key tiles, resolved once (coalesced) instead of one dependent load per tile
+                const long long trow = (long long)smax * prm.n_pages;
+                int first_bad = n_tiles;
+                for (int j = lane; j < n_tiles; j += 32) {
+                    const long long pg = prm.page_table[trow + j];
+                    bool ok = pg >= 0 && pg < prm.n_pages;
+                    if (pg >= prm.n_pages) raise_status(prm.status, FPKV_STATUS_BAD_PAGE);
+                    if (ok) ok = prm.p2l[trow + pg] >= 0;
+                    d->page_row[j] = hkv * prm.rows_per_plane + (ok ? (int)pg : 0) * kPage;   // unmapped: reserved page 0, masked
+                    d->page_ok[j] = ok;
+                    if (!ok) first_bad = min(first_bad, j);
+                }
+#pragma unroll
+                for (int o = 16; o > 0; o >>= 1) first_bad = min(first_bad, __shfl_xor_sync(0xffffffffu, first_bad, o));
+                if (lane == 0) { d->valid = 1; d->t0 = t0; d->hq0 = hq0; d->n_tiles = n_tiles; d->max_extent = emax; d->first_bad = first_bad; }
+            }
+            __syncwarp();
+            if (lane == 0) bar_arrive(desc_full0 + 8 * b);
+            ++it;
+        }
+    } else if (warp == kLoadWarp) {
+        // ============================== TMA producer ========================
+        if (lane == 0) {
+            uint32_t gk = 0, wit = 0;                      // key tiles requested, items with work so far
+            for (uint32_t it = 0; alive; ++it) {
+                const uint32_t b = it & 1u;
+                if (!bar_wait(desc_full0 + 8 * b, (it >> 1) & 1u, abort_flag)) { alive = false; break; }
+                const ItemDesc* d = desc + b;
+                if (!d->valid) break;
+                const int n = d->n_tiles;
+                if (n > 0) {
+                    for (int h = 0; h < heads && alive; ++h) {           // the head's query buffer is free once its last Q.K^T is through
+                        if (!bar_wait(q_empty0 + 8 * h, (wit & 1u) ^ 1u, abort_flag)) { alive = false; break; }
+                        bar_expect_tx(q_full0 + 8 * h, kTileBytes);
+                        tma_4d(s32(q_s + h * kTileBytes), &q_map, 0, d->t0, 0, d->hq0 + h, q_full0 + 8 * h);
+                        q_requested[h] = wit + 1;
+                    }
+                    for (int j = 0; j < n && alive; ++j, ++gk) {
+                        const uint32_t st = gk % kStages, ph = (gk / kStages) & 1u;
+                        if (!bar_wait(k_empty0 + 8 * st, ph ^ 1u, abort_flag)) { alive = false; break; }
+                        bar_expect_tx(k_full0 + 8 * st, kTileBytes);
+                        tma_3d(s32(k_s + st * kTileBytes), &kv_map, 0, d->page_row[j], 0, k_full0 + 8 * st);
+                        k_requested = gk + 1;
+                        if (!bar_wait(v_empty0 + 8 * st, ph ^ 1u, abort_flag)) { alive = false; break; }
+                        bar_expect_tx(v_full0 + 8 * st, kTileBytes);
+                        tma_3d(s32(v_s + st * kTileBytes), &kv_map, 0, d->page_row[j] + prm.Hkv * prm.rows_per_plane, 0, v_full0 + 8 * st);
+                        v_requested = gk + 1;
+                    }
+                    ++wit;
+                }
+                if (alive) bar_arrive(desc_empty0 + 8 * b);
             }
         }
     } else if (warp >= kMmaWarp && warp < kMmaWarp + heads) {
@@ -454,226 +516,216 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_consta
         // idles for it; with an issuer per head the other head's MMAs fill those gaps, and each head's
         // chain  S -> softmax -> P.V -> next S  advances on its own.  Both heads read the one staged K / V tile.
         const int g = warp - kMmaWarp;
-        if (lane == 0 && n_tiles > 0) {
-            const uint32_t idesc_qk = umma_idesc(prm.is_bf16 != 0, false);
-            const uint32_t idesc_pv = umma_idesc(prm.is_bf16 != 0, true);
+        if (lane == 0) {
+            const bool is_bf16 = std::is_same<T, __nv_bfloat16>::value;
+            const uint32_t idesc_qk = umma_idesc(is_bf16, false, 64);
+            const uint32_t idesc_pv = umma_idesc(is_bf16, true);
             // descriptor words: low = start address >> 4 (| LBO for MN-major), high = SBO 1024 | version | 128-byte swizzle
             const uint32_t desc_hi = (uint32_t)(umma_desc(0, 0, 1024) >> 32);
             const uint32_t q_lo = ((s32(q_s) & 0x3FFFF) >> 4) + g * (kTileBytes >> 4), k_lo = (s32(k_s) & 0x3FFFF) >> 4;
             const uint32_t v_lo = ((s32(v_s) & 0x3FFFF) >> 4) | (uint32_t)umma_desc(0, kHalfBytes, 1024);
             const uint32_t t_s = tmem + g * kTileN, t_o = tmem + 256 + g * kTileN;
-            const uint32_t s_full = s_full0 + 8 * g, p_full = p_full0 + 8 * g;
-            alive = bar_wait(q_full, 0, abort_flag) && bar_wait(k_full0, 0, abort_flag);
-            if (alive) {
-                tc_fence_after();
-                issue_qk_gemm(t_s, q_lo, k_lo, desc_hi, idesc_qk, s_full);
-                umma_commit(k_empty0);
-            }
-            for (int j = 0; j < n_tiles && alive; ++j) {
-                const int st = j % kStages, sn = (j + 1) % kStages;
-                // the operand tiles first: they arrived long ago, and waiting for them here costs nothing
-                // while the softmax group is still busy
-                if (!bar_wait(v_full0 + 8 * st, (j / kStages) & 1u, abort_flag)) { alive = false; break; }
-                if (j + 1 < n_tiles && !bar_wait(k_full0 + 8 * sn, ((j + 1) / kStages) & 1u, abort_flag)) { alive = false; break; }
-                if (!bar_wait(p_full, j & 1u, abort_flag)) { alive = false; break; }
-                tc_fence_after();
-                issue_pv_gemm<0>(t_o, t_s, v_lo + st * (kTileBytes >> 4), desc_hi, idesc_pv, j > 0);
-                issue_pv_gemm<1>(t_o, t_s, v_lo + st * (kTileBytes >> 4), desc_hi, idesc_pv, 1u);
-                umma_commit(v_empty0 + 8 * st);
-                if (j + 1 < n_tiles) {
-                    issue_qk_gemm(t_s, q_lo, k_lo + sn * (kTileBytes >> 4), desc_hi, idesc_qk, s_full);
-                    umma_commit(k_empty0 + 8 * sn);
+            const uint32_t s_lo = s_half0 + 16 * g, s_hi = s_lo + 8, p_lo = p_half0 + 16 * g, p_hi = p_lo + 8;
+            const uint32_t pv_done = pv_done0 + 8 * g;
+            uint32_t gk = 0, th = 0, wit = 0;              // key tiles, head-tiles and items with work so far
+            for (uint32_t it = 0; alive; ++it) {
+                const uint32_t b = it & 1u;
+                if (!bar_wait(desc_full0 + 8 * b, (it >> 1) & 1u, abort_flag)) { alive = false; break; }
+                const ItemDesc* d = desc + b;
+                if (!d->valid) break;
+                const int n = d->n_tiles;
+                if (n > 0) {
+                    const uint32_t st0 = gk % kStages;
+                    alive = bar_wait(q_full0 + 8 * g, wit & 1u, abort_flag) &&
+                            bar_wait(k_full0 + 8 * st0, (gk / kStages) & 1u, abort_flag);
+                    if (!alive) break;
+                    tc_fence_after();
+                    issue_qk_half<0>(t_s, q_lo, k_lo + st0 * (kTileBytes >> 4), desc_hi, idesc_qk, s_lo);
+                    issue_qk_half<1>(t_s + 64, q_lo, k_lo + st0 * (kTileBytes >> 4), desc_hi, idesc_qk, s_hi);
+                    umma_commit(k_empty0 + 8 * st0);
+                    if (n == 1) umma_commit(q_empty0 + 8 * g);
+                    for (int j = 0; j < n; ++j) {
+                        const uint32_t cur = gk + j, nxt = cur + 1;
+                        const uint32_t st = cur % kStages, sn = nxt % kStages;
+                        // the operand tiles first: they arrived long ago, and waiting for them here costs nothing
+                        // while the softmax group is still busy
+                        if (!bar_wait(v_full0 + 8 * st, (cur / kStages) & 1u, abort_flag)) { alive = false; break; }
+                        if (j + 1 < n && !bar_wait(k_full0 + 8 * sn, (nxt / kStages) & 1u, abort_flag)) { alive = false; break; }
+                        // O of the previous item must have been read by its epilogue before the first P.V overwrites it
+                        if (j == 0 && !bar_wait(o_free0 + 8 * g, (wit & 1u) ^ 1u, abort_flag)) { alive = false; break; }
+                        // keys 0-63: P.V, then at once the next tile's scores of the same half (its columns are free again)
+                        if (!bar_wait(p_lo, th & 1u, abort_flag)) { alive = false; break; }
+                        tc_fence_after();
+                        issue_pv_half<0>(t_o, t_s, v_lo + st * (kTileBytes >> 4), desc_hi, idesc_pv, j > 0);
+                        umma_commit(pv_done);
+                        if (j + 1 < n) issue_qk_half<0>(t_s, q_lo, k_lo + sn * (kTileBytes >> 4), desc_hi, idesc_qk, s_lo);
+                        // keys 64-127
+                        if (!bar_wait(p_hi, th & 1u, abort_flag)) { alive = false; break; }
+                        tc_fence_after();
+                        issue_pv_half<1>(t_o, t_s + 64, v_lo + st * (kTileBytes >> 4), desc_hi, idesc_pv, 1u);
+                        umma_commit(pv_done);
+                        umma_commit(v_empty0 + 8 * st);
+                        ++th;
+                        if (j + 1 < n) {
+                            issue_qk_half<1>(t_s + 64, q_lo, k_lo + sn * (kTileBytes >> 4), desc_hi, idesc_qk, s_hi);
+                            umma_commit(k_empty0 + 8 * sn);
+                            if (j + 2 == n) umma_commit(q_empty0 + 8 * g);     // that was the item's last Q.K^T
+                        }
+                    }
+                    if (!alive) break;
+                    umma_commit(all_done0 + 8 * g);
+                    gk += n; ++wit;
                 }
+                bar_arrive(desc_empty0 + 8 * b);
             }
-            umma_commit(all_done0 + 8 * g);                // arrives when every MMA this thread issued has completed
             if (!alive) {
                 // Gave up: tensor memory is freed and the CTA's shared memory handed on after the last barrier
                 // below, so wait (bounded, ignoring the abort flag) for the MMAs already in the pipe.
-                for (uint32_t k = 0; k < kSpin && !bar_try(all_done0 + 8 * g, 0); ++k) {}
+                umma_commit(drain0 + 8 * g);
+                for (uint32_t k = 0; k < kSpin && !bar_try(drain0 + 8 * g, 0); ++k) {}
             }
         }
-    } else if (is_softmax) {
-        // ============================== softmax warps =======================
-        // All eight warps work on ONE head's score tile at a time, two threads per query row: warps w and
-        // w + 4 reach the same 32 tensor-memory lanes, warp w / 4 takes key columns [0,64) or [64,128).  The
-        // exponential unit (16 results per clock per SM) bounds this phase; with two warps per scheduler
-        // it stays saturated, and a head's tile is through in half the time a single thread per row needs,
-        // which is what the chain  S -> softmax -> P.V -> next S  of each head waits for.  The heads alternate
-        // (tile j of head 0, tile j of head 1, tile j + 1 of head 0, ...) while the other head's MMAs run.
-        const int quarter = warp % 4, colhalf = warp / 4;
+    } else if (warp < kSoftmaxWarps * heads) {
+        // ============================== softmax groups ======================
+        // Group h (warps 4h .. 4h+3) owns head h of the pair: one thread per query row, warp w reaches tensor-
+        // memory lanes [32 (w % 4), +32).  The groups do not synchronise with each other: while one exponentiates,
+        // the other one's score loads, maximum, P store and barrier traffic -- and both heads' MMAs -- run underneath.
+        const int h = warp / kSoftmaxWarps, quarter = warp % kSoftmaxWarps;
+        const int row = quarter * 32 + lane;
         const uint32_t lane_base = (uint32_t)(quarter * 32) << 16;
-        float m_ref[2] = {-INFINITY, -INFINITY}, l[2] = {0.f, 0.f};
-        uint32_t v[32];
-        uint32_t xslot = 0;                                // exchange buffer parity
-        // (the two warps of a row quarter meet at their own named barrier, 1 + quarter)
-        auto exchange_max = [&](float mine) {              // maximum over the two threads of a row
-            float* buf = xch + (xslot & 1u) * 256;
-            buf[colhalf * 128 + row] = mine;
-            asm volatile("bar.sync %0, 64;" ::"r"(1 + quarter) : "memory");
-            const float other = buf[(1 - colhalf) * 128 + row];
-            ++xslot;
-            return fmaxf(mine, other);
-        };
-        for (int j = 0; j < n_tiles; ++j) {
-            // Value rows past the last key any row of this tile sees (the tail of the last key tile, or all of
-            // an unmapped page's stand-in) were fetched but possibly never appended: the pool may hold anything
-            // there, and 0 x NaN would poison O.  Clear them in shared memory before the first P.V of the tile
-            // (the tensor cores read shared memory through the async proxy, hence the proxy fence).
-            const int tile_rows = page_ok[j] ? min(kTileN, max_extent - j * kTileN) : 0;
-            if (tile_rows < kTileN) {
-                const int st = j % kStages;
-                if (alive && !bar_wait(v_full0 + 8 * st, (j / kStages) & 1u, abort_flag)) alive = false;
-                for (int i = tid; i < (kTileN - tile_rows) * 16; i += 2 * kSoftmaxWarps * 32) {
-                    const int r = tile_rows + (i >> 4), c = i & 15;         // token row, 16-byte piece of its 256 bytes
-                    *reinterpret_cast<uint4*>(v_s + st * kTileBytes + (c >> 3) * kHalfBytes + r * 128 + ((c & 7) << 4)) =
-                        make_uint4(0u, 0u, 0u, 0u);
-                }
-                asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
-            }
-            const int valid_row = page_ok[j] ? min(kTileN, my_extent - j * kTileN) : 0;   // visible keys of this row in the tile
-            const int valid_cols = valid_row - colhalf * 64;                               // ... among this thread's 64 columns
-            const bool full = __all_sync(0xffffffffu, valid_cols >= 64);
-            for (int h = 0; h < heads; ++h) {
-                const uint32_t ts = tmem + h * kTileN + lane_base;          // S, then P, of this head
-                const uint32_t to = tmem + 256 + h * kTileN + lane_base + colhalf * 64;   // this thread's half of the O row
-                // s_full also tells that P.V of tile j-1 is complete: O is stable and the P columns are free.
-                // A wait that runs out does not leave the loop: every thread must reach the named barrier below.
-                if (alive && !bar_wait(s_full0 + 8 * h, j & 1u, abort_flag)) alive = false;
-                tc_fence_after();
-                uint32_t sv[2][32];
-                tmem_ld32_nowait(ts + colhalf * 64, sv[0]);
-                tmem_ld32_nowait(ts + colhalf * 64 + 32, sv[1]);
-                tmem_wait_ld();
-                float mx;
-                if (full) {
-                    float m2[2];
-#pragma unroll
-                    for (int c2 = 0; c2 < 2; ++c2) {
-                        m2[c2] = max3f(__uint_as_float(sv[c2][0]), __uint_as_float(sv[c2][1]), __uint_as_float(sv[c2][2]));
-#pragma unroll
-                        for (int c = 3; c + 1 < 32; c += 2)
-                            m2[c2] = max3f(m2[c2], __uint_as_float(sv[c2][c]), __uint_as_float(sv[c2][c + 1]));
-                        m2[c2] = fmaxf(m2[c2], __uint_as_float(sv[c2][31]));
-                    }
-                    mx = fmaxf(m2[0], m2[1]);
-                } else {
-                    mx = -INFINITY;
-#pragma unroll
-                    for (int c2 = 0; c2 < 2; ++c2)
-#pragma unroll
-                        for (int c = 0; c < 32; ++c) if (c2 * 32 + c < valid_cols) mx = fmaxf(mx, __uint_as_float(sv[c2][c]));
-                }
-                // after this barrier both threads of the row hold all their scores in registers, so the packed
-                // P columns may overwrite either thread's score columns
-                mx = exchange_max(mx) * prm.scale_log2;    // scale > 0: max commutes with it
-                // raise the reference maximum only when this tile is far above it (both threads of a row decide alike)
-                const bool raise = mx > m_ref[h] + kRescaleThreshold || (m_ref[h] == -INFINITY && mx > -INFINITY);
-                if (__any_sync(0xffffffffu, raise)) {      // tensor-memory access is a whole-warp operation
-                    const float m_new = raise ? mx : m_ref[h];
-                    const float alpha = (m_ref[h] == -INFINITY) ? 0.f : exp2f(m_ref[h] - m_new);
-                    if (j > 0) {                           // rescale this thread's half of the O row in tensor memory
-#pragma unroll 1
-                        for (int c2 = 0; c2 < 2; ++c2) {
-                            tmem_ld32(to + c2 * 32, v);
-#pragma unroll
-                            for (int c = 0; c < 32; ++c) v[c] = __float_as_uint(__uint_as_float(v[c]) * alpha);
-                            tmem_st32(to + c2 * 32, v);
-                        }
-                    }
-                    l[h] *= alpha;
-                    m_ref[h] = m_new;
-                }
-                // probabilities, packed two per 32-bit column: this thread's 64 scores become packed columns
-                // [colhalf * 32, colhalf * 32 + 32) of the region
-                float r4[4] = {0.f, 0.f, 0.f, 0.f};
-                const float neg_m = (m_ref[h] == -INFINITY) ? 0.f : -m_ref[h];
-                uint32_t pk[32];
-                auto probabilities = [&](auto full_tag) {
-                    constexpr bool kFull = decltype(full_tag)::value;
-#pragma unroll
-                    for (int c2 = 0; c2 < 2; ++c2) {
-#pragma unroll
-                        for (int c = 0; c < 32; c += 2) {
-                            float p0, p1;
-                            if ((c >> 1) % kPolyEvery == kPolyEvery - 1) {     // every fourth pair off the exponential unit
-                                const F2 p = ex2_poly2(fma2(F2{__uint_as_float(sv[c2][c]), __uint_as_float(sv[c2][c + 1])},
-                                                            F2{prm.scale_log2, prm.scale_log2}, F2{neg_m, neg_m}));
-                                p0 = p.x; p1 = p.y;
-                            } else {
-                                p0 = ex2(fmaf(__uint_as_float(sv[c2][c]), prm.scale_log2, neg_m));
-                                p1 = ex2(fmaf(__uint_as_float(sv[c2][c + 1]), prm.scale_log2, neg_m));
-                            }
-                            if (!kFull) {
-                                if (c2 * 32 + c >= valid_cols) p0 = 0.f;
-                                if (c2 * 32 + c + 1 >= valid_cols) p1 = 0.f;
-                            }
-                            r4[(c >> 1) & 1] += p0;
-                            r4[2 + ((c >> 1) & 1)] += p1;
-                            pk[c2 * 16 + c / 2] = pack2<T>(p0, p1);
-                        }
-                    }
-                };
-                if (full) probabilities(std::true_type{}); else probabilities(std::false_type{});
-                tmem_st32_nowait(ts + colhalf * 32, pk);
-                l[h] += (r4[0] + r4[1]) + (r4[2] + r4[3]);
-                asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
-                tc_fence_before();
-                __syncwarp();
-                if (lane == 0) bar_arrive(p_full0 + 8 * h);
-            }
-        }
-        // ---- epilogue: O / l -> out, lse --------------------------------------
-        // Each thread holds 64 of the 128 output values of its row.  Storing them straight from registers
-        // would touch 32 different lines per warp instruction; the two warps of a row quarter stage their 32
-        // rows in the (now idle) query tile of the head, 16-byte chunks XOR-swizzled by row so that neither
-        // side has bank conflicts, and write them out two whole rows per instruction.
+        const uint32_t ts = tmem + h * kTileN + lane_base;            // S of this head: keys 0-63 in columns [0,64), keys 64-127 in [64,128)
+        const uint32_t to = tmem + 256 + h * kTileN + lane_base;      // O of this head
+        const uint32_t pv_done = pv_done0 + 8 * h;
         T* out = reinterpret_cast<T*>(prm.out);
-        for (int h = 0; h < heads; ++h) {
-            const int hq = hq0 + h;
-            const uint32_t to = tmem + 256 + h * kTileN + lane_base + colhalf * 64;
-            if (n_tiles > 0) {
-                if (alive && !bar_wait(all_done0 + 8 * h, 0, abort_flag)) alive = false;
-                tc_fence_after();
+        uint32_t gk = 0, th = 0, wit = 0;                  // key tiles, head-tiles and items with work so far
+        for (uint32_t it = 0; alive; ++it) {
+            const uint32_t b = it & 1u;
+            if (!bar_wait(desc_full0 + 8 * b, (it >> 1) & 1u, abort_flag)) { alive = false; break; }
+            const ItemDesc* d = desc + b;
+            if (!d->valid) break;
+            const int n = d->n_tiles, max_extent = d->max_extent, my_extent = d->extent[row];
+            const int tk = d->t0 + row, hq = d->hq0 + h;
+            float m_ref = -INFINITY, l = 0.f;
+            uint32_t sv[2][32], pk[32];
+            // per-item constants of the tile loop: tiles below `wfull` are fully visible to every row of this warp
+            const int first_bad = d->first_bad;
+            int wfull = my_extent / kTileN;
+#pragma unroll
+            for (int o = 16; o > 0; o >>= 1) wfull = min(wfull, __shfl_xor_sync(0xffffffffu, wfull, o));
+            wfull = min(wfull, first_bad);
+            const int zero_from = min(first_bad, (max_extent % kTileN) ? n - 1 : n);   // first tile with value rows to clear
+            for (int j = 0; j < n && alive; ++j) {
+                const bool page_ok = j < first_bad || d->page_ok[j];
+                // Value rows past the last key any row of this tile sees (the tail of the last key tile, or all of
+                // an unmapped page's stand-in) were fetched but possibly never appended: the pool may hold anything
+                // there, and 0 x NaN would poison O.  Clear them in shared memory before this head's first P.V of
+                // the tile (both groups do, each ahead of its own hand-over; the tensor cores read shared memory
+                // through the async proxy, hence the proxy fence).
+                if (j >= zero_from) {
+                    const int tile_rows = page_ok ? min(kTileN, max_extent - j * kTileN) : 0;
+                    const uint32_t cur = gk + j, st = cur % kStages;
+                    if (!bar_wait(v_full0 + 8 * st, (cur / kStages) & 1u, abort_flag)) { alive = false; break; }
+                    for (int i = row; i < (kTileN - tile_rows) * 16; i += kSoftmaxWarps * 32) {
+                        const int r = tile_rows + (i >> 4), c = i & 15;         // token row, 16-byte piece of its 256 bytes
+                        *reinterpret_cast<uint4*>(v_s + st * kTileBytes + (c >> 3) * kHalfBytes + r * 128 + ((c & 7) << 4)) =
+                            make_uint4(0u, 0u, 0u, 0u);
+                    }
+                    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+                }
+                const bool full = j < wfull;
+                const int valid_row = full ? kTileN : (page_ok ? min(kTileN, my_extent - j * kTileN) : 0);   // visible keys of this row in the tile
+                // The tile is worked through in two halves of 64 keys.  Each half has its own score columns, and the
+                // MMA warp refills a half (next tile's Q.K^T over the same 64 keys) as soon as that half's P.V is
+                // issued: the scores of the next half are there when this group comes back for them.
+#pragma unroll
+                for (int hf = 0; hf < 2; ++hf) {
+                    const uint32_t unit = 2 * th + hf;                          // halves this head has gone through so far
+                    const int valid_cols = valid_row - 64 * hf;
+                    if (!bar_wait(s_half0 + 16 * h + 8 * hf, th & 1u, abort_flag)) { alive = false; break; }
+                    tc_fence_after();
+                    tmem_ld32_nowait(ts + 64 * hf, sv[0]);
+                    tmem_ld32_nowait(ts + 64 * hf + 32, sv[1]);
+                    tmem_wait_ld();
+                    // The reference maximum is raised lazily: only when a score lies more than 2^8 above it (the
+                    // probabilities stay below 256, exact in fp32 and harmless in 16 bits), so that O in tensor memory
+                    // is rarely rescaled.  O is stable only once every P.V issued so far has completed.
+                    const float mx = (full ? max64<true>(sv, 64) : max64<false>(sv, valid_cols)) * prm.scale_log2;   // scale > 0: max commutes with it
+                    const bool raise = mx > m_ref + kRescaleThreshold || (m_ref == -INFINITY && mx > -INFINITY);
+                    if (__any_sync(0xffffffffu, raise)) {  // tensor-memory access is a whole-warp operation
+                        const float m_new = raise ? mx : m_ref;
+                        const float alpha = (m_ref == -INFINITY) ? 0.f : exp2f(m_ref - m_new);
+                        if (j > 0 || hf > 0) {             // rescale this row of O in tensor memory
+                            if (!bar_wait(pv_done, (unit - 1) & 1u, abort_flag)) { alive = false; break; }
+                            tc_fence_after();
+#pragma unroll 1
+                            for (int c4 = 0; c4 < 4; ++c4) {
+                                tmem_ld32(to + c4 * 32, pk);
+#pragma unroll
+                                for (int c = 0; c < 32; ++c) pk[c] = __float_as_uint(__uint_as_float(pk[c]) * alpha);
+                                tmem_st32(to + c4 * 32, pk);
+                            }
+                        }
+                        l *= alpha;
+                        m_ref = m_new;
+                    }
+                    const float neg_m = (m_ref == -INFINITY) ? 0.f : -m_ref;
+                    F2 rs[2] = {F2{0.f, 0.f}, F2{0.f, 0.f}};
+                    if (full) probabilities64<T, true>(sv, pk, rs, prm.scale_log2, neg_m, 64);
+                    else probabilities64<T, false>(sv, pk, rs, prm.scale_log2, neg_m, valid_cols);
+                    tmem_st32_nowait(ts + 64 * hf, pk);    // P of these 64 keys over the first half of their own score columns
+                    l += (rs[0].x + rs[0].y) + (rs[1].x + rs[1].y);
+                    asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
+                    tc_fence_before();
+                    __syncwarp();
+                    if (lane == 0) bar_arrive(p_half0 + 16 * h + 8 * hf);
+                }
+                ++th;
             }
-            // row sum over both threads of the row
-            float* buf = xch + (xslot & 1u) * 256;
-            buf[colhalf * 128 + row] = l[h];
-            asm volatile("bar.sync %0, 64;" ::"r"(1 + quarter) : "memory");
-            const float lsum = l[h] + buf[(1 - colhalf) * 128 + row];
-            ++xslot;
-            const float inv = lsum > 0.f ? 1.f / lsum : 0.f;
-            const float lse_nat = lsum > 0.f ? (m_ref[h] + log2f(lsum)) * kLn2 : -INFINITY;
+            if (!alive) break;
+            gk += n;
+            // ---- epilogue: O / l -> out, lse; every thread owns one row of 256 contiguous bytes ----
+            if (n > 0) {
+                if (!bar_wait(all_done0 + 8 * h, wit & 1u, abort_flag)) { alive = false; break; }
+                tc_fence_after();
+                ++wit;
+            }
+            const float inv = l > 0.f ? 1.f / l : 0.f;
+            const float lse_nat = l > 0.f ? (m_ref + log2f(l)) * kLn2 : -INFINITY;
             const bool gate_on = prm.epi.sinks != nullptr;
             const float gate = sink_gate(prm.epi, hq, lse_nat);
-            uint8_t* slab = q_s + h * kTileBytes + quarter * (32 * 256);
+            T* dst = out + (prm.epi.token_major ? ((size_t)tk * prm.Hq + hq) : ((size_t)hq * prm.L + tk)) * kHeadDim;
 #pragma unroll 1
             for (int c2 = 0; c2 < 2; ++c2) {
-                if (n_tiles > 0) tmem_ld32(to + c2 * 32, v);
-#pragma unroll
-                for (int c = 0; c < 32; c += 8) {
-                    uint32_t w[4];
-#pragma unroll
-                    for (int e = 0; e < 4; ++e) {
-                        const float a = (n_tiles > 0 && lsum > 0.f) ? __uint_as_float(v[c + 2 * e]) * inv : 0.f;
-                        const float b = (n_tiles > 0 && lsum > 0.f) ? __uint_as_float(v[c + 2 * e + 1]) * inv : 0.f;
-                        w[e] = gated_pair<T>(a, b, gate, gate_on);
+                if (n > 0) {
+                    tmem_ld32_nowait(to + c2 * 64, sv[0]);
+                    tmem_ld32_nowait(to + c2 * 64 + 32, sv[1]);
+                    tmem_wait_ld();
+                    if (c2 == 1) {                         // O is in registers: the next item's first P.V may overwrite it
+                        tc_fence_before();
+                        __syncwarp();
+                        if (lane == 0) bar_arrive(o_free0 + 8 * h);
                     }
-                    const int chunk = colhalf * 8 + c2 * 4 + c / 8;
-                    *reinterpret_cast<uint4*>(slab + lane * 256 + ((chunk ^ (lane & 15)) * 16)) = make_uint4(w[0], w[1], w[2], w[3]);
                 }
-            }
-            asm volatile("bar.sync %0, 64;" ::"r"(1 + quarter) : "memory");         // both column halves of every row are staged
-#pragma unroll 4
-            for (int i = 0; i < 8; ++i) {                  // this warp writes out 16 of the quarter's 32 rows
-                const int rr = colhalf * 16 + 2 * i + (lane >> 4), chunk = lane & 15;
-                const uint4 val = *reinterpret_cast<const uint4*>(slab + rr * 256 + ((chunk ^ (rr & 15)) * 16));
-                const int tk = t0 + quarter * 32 + rr;
                 if (tk < prm.L) {
-                    T* dst = out + (prm.epi.token_major ? ((size_t)tk * prm.Hq + hq) : ((size_t)hq * prm.L + tk)) * kHeadDim + chunk * 8;
-                    *reinterpret_cast<uint4*>(dst) = val;
+#pragma unroll
+                    for (int q8 = 0; q8 < 4; ++q8) {
+                        uint32_t w[8];
+#pragma unroll
+                        for (int e = 0; e < 8; ++e) {
+                            const int c = q8 * 16 + 2 * e;
+                            const float a = (n > 0 && l > 0.f) ? __uint_as_float(sv[c >> 5][c & 31]) * inv : 0.f;
+                            const float bb = (n > 0 && l > 0.f) ? __uint_as_float(sv[c >> 5][(c & 31) + 1]) * inv : 0.f;
+                            w[e] = gated_pair<T>(a, bb, gate, gate_on);
+                        }
+                        T* at = dst + c2 * 64 + q8 * 16;   // two adjacent 16-byte stores fill a 32-byte sector
+                        *reinterpret_cast<uint4*>(at) = make_uint4(w[0], w[1], w[2], w[3]);
+                        *reinterpret_cast<uint4*>(at + 8) = make_uint4(w[4], w[5], w[6], w[7]);
+                    }
                 }
             }
-            if (colhalf == 0 && t0 + row < prm.L) prm.lse[(size_t)hq * prm.L + t0 + row] = lse_nat;
+            if (tk < prm.L) prm.lse[(size_t)hq * prm.L + tk] = lse_nat;
+            __syncwarp();
+            if (lane == 0) bar_arrive(desc_empty0 + 8 * b);
         }
     }
     if (!alive && lane == 0) {
@@ -683,20 +735,23 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_consta
     // ---- teardown: everyone meets here, then the allocating warp frees TMEM ---
     tc_fence_before();
     __syncthreads();
-    if (early && n_tiles == 0) {                          // the query tile was requested before it turned out that no row sees a key
-        for (uint32_t k = 0; k < (1u << 20) && !bar_try(q_full, 0); ++k) {}
-    }
     if (warp == kLoadWarp && lane == 0 && *abort_flag) {
         // Copies still in flight target this CTA's shared memory, which the next CTA on this SM gets: wait
-        // (bounded) for the last copy requested into every stage, on the phase that copy completes.
-        if (n_tiles > 0) for (uint32_t k = 0; k < kSpin && !bar_try(q_full, 0); ++k) {}
-        for (int s = 0; s < kStages; ++s) {
-            const int jk = ((k_requested - 1 - s) / kStages) * kStages + s;       // last key tile requested into stage s
-            if (k_requested > s) for (uint32_t k = 0; k < kSpin && !bar_try(k_full0 + 8 * s, (jk / kStages) & 1u); ++k) {}
-            const int jv = ((v_requested - 1 - s) / kStages) * kStages + s;
-            if (v_requested > s) for (uint32_t k = 0; k < kSpin && !bar_try(v_full0 + 8 * s, (jv / kStages) & 1u); ++k) {}
+        // (bounded) for the last copy requested into every buffer, on the phase that copy completes.
+        for (int h = 0; h < 2; ++h)
+            if (q_requested[h] > 0) for (uint32_t k = 0; k < kSpin && !bar_try(q_full0 + 8 * h, (q_requested[h] - 1) & 1u); ++k) {}
+        for (uint32_t s = 0; s < (uint32_t)kStages; ++s) {
+            if (k_requested > s) {
+                const uint32_t last = ((k_requested - 1 - s) / kStages) * kStages + s;    // last key tile requested into stage s
+                for (uint32_t k = 0; k < kSpin && !bar_try(k_full0 + 8 * s, (last / kStages) & 1u); ++k) {}
+            }
+            if (v_requested > s) {
+                const uint32_t last = ((v_requested - 1 - s) / kStages) * kStages + s;
+                for (uint32_t k = 0; k < kSpin && !bar_try(v_full0 + 8 * s, (last / kStages) & 1u); ++k) {}
+            }
         }
     }
+    __syncthreads();
     if (warp == kMmaWarp) {
         tc_fence_after();
         asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(kTmemCols) : "memory");
@@ -718,7 +773,17 @@ EncodeFn encoder() {
     return fn;
 }
 
-constexpr int kPrefillSmem = 1024 + (2 + 2 * kStages) * kTileBytes + 24 * 8 + 16 * 4 + kMaxKeyTiles * 5 + 2 * 2 * 128 * 4 + 64;   // Q x2, K and V x kStages
+int prefill_sm_count() {
+    static int n = [] {
+        int dev = 0, v = 0;
+        cudaGetDevice(&dev);
+        cudaDeviceGetAttribute(&v, cudaDevAttrMultiProcessorCount, dev);
+        return v > 0 ? v : 148;
+    }();
+    return n;
+}
+
+constexpr int kPrefillSmem = 1024 + (2 + 2 * kStages) * kTileBytes + 48 * 8 + 16 * 4 + 2 * (int)sizeof(ItemDesc) + 64;   // Q x2, K and V x kStages
 
 }  // namespace
 
@@ -728,6 +793,7 @@ bool prefill_tc_supported(const PoolView& pv, int Hq)
     if (pv.dtype != FPKV_BF16 && pv.dtype != FPKV_F16) return false;
     if (pv.P != kPage || pv.D != kHeadDim) return false;
     if (Hq % pv.H) return false;
+    // TMA coordinates are 32-bit token rows within one layer's K and V planes (more rows than 180 GB can hold)
     if ((long long)2 * pv.H * pv.n_pages * pv.P >= (1ll << 31)) return false;
     return encoder() != nullptr;
 }
@@ -765,11 +831,14 @@ int launch_prefill_tc(const PoolView& pv, int layer, void* out, float* lse, cons
     prm.L = L; prm.Hq = Hq; prm.Hkv = pv.H; prm.n_pages = pv.n_pages; prm.max_batch = pv.max_batch;
     prm.rows_per_plane = pv.n_pages * pv.P;
     prm.scale_log2 = sm_scale * kLog2e;
-    prm.is_bf16 = pv.dtype == FPKV_BF16;
-    prm.heads_per_cta = ((Hq / pv.H) % 2 == 0) ? 2 : 1;
+    prm.heads_per_item = ((Hq / pv.H) % 2 == 0) ? 2 : 1;
+    prm.n_qtiles = (L + kTileM - 1) / kTileM;
+    prm.n_pairs = Hq / prm.heads_per_item;
+    const long long n_items = (long long)prm.n_qtiles * prm.n_pairs;
+    if (n_items >= (1ll << 30)) return FPKV_ESHAPE;
+    prm.n_items = (int)n_items;
     prm.epi = epi;
-    if ((L + kTileM - 1) / kTileM > 65535) return FPKV_ESHAPE;
-    dim3 grid(Hq / prm.heads_per_cta, (L + kTileM - 1) / kTileM);
+    const int grid = prm.n_items < prefill_sm_count() ? prm.n_items : prefill_sm_count();    // persistent: one CTA per SM
     if (pv.dtype == FPKV_BF16) {
         auto kern = prefill_tc_kernel<__nv_bfloat16>;
         if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, kPrefillSmem) != cudaSuccess) return FPKV_ELAUNCH;
