@@ -493,17 +493,33 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_consta
                         tma_4d(s32(q_s + h * kTileBytes), &q_map, 0, d->t0, 0, d->hq0 + h, q_full0 + 8 * h);
                         q_requested[h] = wit + 1;
                     }
-                    for (int j = 0; j < n && alive; ++j, ++gk) {
-                        const uint32_t st = gk % kStages, ph = (gk / kStages) & 1u;
-                        if (!bar_wait(k_empty0 + 8 * st, ph ^ 1u, abort_flag)) { alive = false; break; }
-                        bar_expect_tx(k_full0 + 8 * st, kTileBytes);
-                        tma_3d(s32(k_s + st * kTileBytes), &kv_map, 0, d->page_row[j], 0, k_full0 + 8 * st);
-                        k_requested = gk + 1;
-                        if (!bar_wait(v_empty0 + 8 * st, ph ^ 1u, abort_flag)) { alive = false; break; }
-                        bar_expect_tx(v_full0 + 8 * st, kTileBytes);
-                        tma_3d(s32(v_s + st * kTileBytes), &kv_map, 0, d->page_row[j] + prm.Hkv * prm.rows_per_plane, 0, v_full0 + 8 * st);
-                        v_requested = gk + 1;
+                    // The K ring and the V ring advance independently: a K stage frees up when the tile's Q.K^T is
+                    // through, long before its V stage does (P.V comes a softmax later), so whichever ring has room
+                    // gets its next copy; waiting for them strictly in turn would hold K copies back behind V.
+                    int jk = 0, jv = 0;
+                    uint32_t idle = 0;
+                    while ((jk < n || jv < n) && alive) {
+                        bool progress = false;
+                        if (jk < n) {
+                            const uint32_t g = gk + jk, st = g % kStages;
+                            if (bar_try(k_empty0 + 8 * st, ((g / kStages) & 1u) ^ 1u)) {
+                                bar_expect_tx(k_full0 + 8 * st, kTileBytes);
+                                tma_3d(s32(k_s + st * kTileBytes), &kv_map, 0, d->page_row[jk], 0, k_full0 + 8 * st);
+                                k_requested = g + 1; ++jk; progress = true;
+                            }
+                        }
+                        if (jv < n) {
+                            const uint32_t g = gk + jv, st = g % kStages;
+                            if (bar_try(v_empty0 + 8 * st, ((g / kStages) & 1u) ^ 1u)) {
+                                bar_expect_tx(v_full0 + 8 * st, kTileBytes);
+                                tma_3d(s32(v_s + st * kTileBytes), &kv_map, 0, d->page_row[jv] + prm.Hkv * prm.rows_per_plane, 0, v_full0 + 8 * st);
+                                v_requested = g + 1; ++jv; progress = true;
+                            }
+                        }
+                        if (progress) idle = 0;
+                        else if (++idle > kSpin || ((idle & 255u) == 255u && *abort_flag)) alive = false;
                     }
+                    gk += n;
                     ++wit;
                 }
                 if (alive) bar_arrive(desc_empty0 + 8 * b);
