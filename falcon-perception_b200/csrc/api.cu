@@ -38,6 +38,8 @@ int make_view(const fpkv_pool* pool, int layer, PoolView* pv) {
     pv->num_layers = pool->num_layers; pv->H = pool->n_heads; pv->n_pages = pool->n_pages;
     pv->P = pool->page_size; pv->D = pool->head_dim; pv->max_batch = pool->max_batch_size;
     pv->dtype = pool->dtype; pv->esize = es;
+    pv->split_hq = pool->split_q_heads;
+    if (pv->split_hq < 0 || (pv->split_hq > 0 && (pv->split_hq % pv->H != 0 || pv->split_hq == pv->H))) return FPKV_ESHAPE;
     return FPKV_OK;
 }
 
@@ -86,6 +88,7 @@ int decode_attn_checked(const fpkv_pool* pool, int32_t layer, void* out, float* 
     if ((rc = make_epilogue(epilogue, n_q_heads, &epi))) return rc;
     if (B < 0 || n_q_heads <= 0 || (pos_type != FPKV_I32 && pos_type != FPKV_I64)) return FPKV_EINVAL;
     if (n_q_heads % pv.H) return FPKV_ESHAPE;
+    if (pv.split_hq && n_q_heads != pv.split_hq) return FPKV_ESHAPE;      // a split pool serves exactly its query heads
     if (B == 0) return FPKV_OK;
     if (out == nullptr || lse == nullptr || batch_idx == nullptr || input_pos == nullptr || workspace == nullptr)
         return FPKV_EINVAL;
@@ -185,7 +188,8 @@ int fpkv_pre_append(const fpkv_pool* pool, int32_t layer, const void* qkv, int64
     if (rc) return rc;
     if (n_tok < 0 || (pos_type != FPKV_I32 && pos_type != FPKV_I64) || n_q_heads <= 0 || n_kv_heads <= 0) return FPKV_EINVAL;
     if (n_q_heads % n_kv_heads) return FPKV_ESHAPE;
-    if (pv.H != n_q_heads && pv.H != n_kv_heads) return FPKV_ESHAPE;     // expanded or compact pool, nothing else
+    if (pv.split_hq ? (pv.split_hq != n_q_heads || pv.H != n_kv_heads)
+                    : (pv.H != n_q_heads && pv.H != n_kv_heads)) return FPKV_ESHAPE;     // expanded, compact or split pool
     if (pv.D != 64 && pv.D != 128) return FPKV_ESHAPE;
     if (qkv_stride_t < (int64_t)(n_q_heads + 2 * n_kv_heads) * pv.D) return FPKV_ESHAPE;
     if (!(eps >= 0.f)) return FPKV_EINVAL;
@@ -274,6 +278,7 @@ int fpkv_prefill_attn(const fpkv_pool* pool, int32_t layer, void* out, float* ls
     if ((rc = make_epilogue(epilogue, n_q_heads, &epi))) return rc;
     if (L < 0 || n_q_heads <= 0) return FPKV_EINVAL;
     if (n_q_heads % pv.H) return FPKV_ESHAPE;
+    if (pv.split_hq && n_q_heads != pv.split_hq) return FPKV_ESHAPE;
     if (L == 0) return FPKV_OK;
     if (out == nullptr || lse == nullptr || batch_idx == nullptr || extent == nullptr) return FPKV_EINVAL;
     if ((rc = check_rows(q, q_stride_h, q_stride_t, pv.esize))) return rc;

@@ -14,15 +14,36 @@ constexpr float kLog2e = 1.4426950408889634f;
 constexpr float kLn2 = 0.6931471805599453f;
 
 // Host-side view of one call's pool arguments after validation.
+//
+// Two pool layouts.  Uniform (split_hq == 0): the reference's (L, 2, 1, H, rows, D), K planes of all heads, then V
+// planes.  Split (split_hq = number of query heads): per layer
+//     K first halves   [H ][rows][D/2]   one per KV head: the half that carries the 1-D rotary embedding
+//     K second halves  [Hq][rows][D/2]   one per QUERY head: the half that carries the per-query-head 2-D embedding
+//     V                [H ][rows][D]     one per KV head
+// which holds exactly what the reference's GQA-expanded cache holds (its copies of a KV head differ only in the
+// second half of K) in (3 H + Hq) D / 2 instead of 2 Hq D elements per token.
 struct PoolView {
     char* base;                       // start of the pool
     const int64_t* page_table;
     const int64_t* p2l;
     int num_layers, H, n_pages, P, D, max_batch, dtype, esize;
-    // bytes between consecutive (layer, k|v, head) planes and helpers
-    __host__ __device__ size_t plane_bytes() const { return (size_t)n_pages * P * D * esize; }
-    __host__ __device__ char* plane(int layer, int kv, int h) const {
+    int split_hq;                     // 0: uniform layout; otherwise the split layout for this many query heads
+    __host__ __device__ size_t rows() const { return (size_t)n_pages * P; }
+    // bytes between consecutive (layer, k|v, head) planes of the uniform layout
+    __host__ __device__ size_t plane_bytes() const { return rows() * D * esize; }
+    __host__ __device__ size_t half_plane_bytes() const { return rows() * (D / 2) * esize; }
+    __host__ __device__ size_t layer_bytes() const {
+        return split_hq ? (size_t)(3 * H + split_hq) * half_plane_bytes() : (size_t)2 * H * plane_bytes();
+    }
+    __host__ __device__ char* layer_base(int layer) const { return base + (size_t)layer * layer_bytes(); }
+    __host__ __device__ char* plane(int layer, int kv, int h) const {          // uniform layout
         return base + ((size_t)(layer * 2 + kv) * H + h) * plane_bytes();
+    }
+    // split layout
+    __host__ __device__ char* kt_plane(int layer, int hkv) const { return layer_base(layer) + (size_t)hkv * half_plane_bytes(); }
+    __host__ __device__ char* khw_plane(int layer, int hq) const { return layer_base(layer) + (size_t)(H + hq) * half_plane_bytes(); }
+    __host__ __device__ char* v_plane(int layer, int hkv) const {
+        return layer_base(layer) + (size_t)(H + split_hq) * half_plane_bytes() + (size_t)hkv * plane_bytes();
     }
 };
 

@@ -38,6 +38,13 @@ __host__ __device__ inline int portable_splits(int B, int Hq) {
 
 // Where row (b, hq) of the result goes: element strides of out and lse over rows and heads.
 struct OutLayout { long long out_row, out_head, lse_row, lse_head; };
+// Split pool layout (common.cuh): first K halves per KV head, second K halves per query head, V per KV head.
+// kt == nullptr: the uniform layout.
+struct SplitPtrs { const char* kt; const char* khw; const char* v; size_t half_plane_bytes; };
+static inline SplitPtrs split_ptrs(const PoolView& pv, int layer) {
+    if (!pv.split_hq) return SplitPtrs{nullptr, nullptr, nullptr, 0};
+    return SplitPtrs{pv.kt_plane(layer, 0), pv.khw_plane(layer, 0), pv.v_plane(layer, 0), pv.half_plane_bytes()};
+}
 
 template <typename T, int D, typename PosT, bool DIRECT>
 __global__ void __launch_bounds__(kPortableWarps * 32)
@@ -48,7 +55,7 @@ decode_portable_kernel(const char* __restrict__ pool_layer, size_t plane_bytes, 
                        const int64_t* __restrict__ batch_idx, const PosT* __restrict__ pos,
                        const int32_t* __restrict__ extent,
                        int Hq, float scale_log2, float* __restrict__ ws, T* __restrict__ out, float* __restrict__ lse,
-                       OutLayout lay, Epilogue epi, int32_t* status)
+                       OutLayout lay, Epilogue epi, int32_t* status, SplitPtrs sp)
 {
     constexpr int E = D / 32;                     // elements per lane
     const int row = blockIdx.x;                   // b * Hq + hq
@@ -89,6 +96,13 @@ decode_portable_kernel(const char* __restrict__ pool_layer, size_t plane_bytes, 
 
     const T* Kp = reinterpret_cast<const T*>(pool_layer + (size_t)h * plane_bytes);
     const T* Vp = reinterpret_cast<const T*>(pool_layer + ((size_t)H + h) * plane_bytes);
+    int k_row = D;                                // elements between consecutive tokens in the K array this lane reads
+    if (sp.kt != nullptr) {                       // a lane's E elements lie in one half of the head
+        k_row = D / 2;
+        Kp = lane * E < D / 2 ? reinterpret_cast<const T*>(sp.kt + (size_t)h * sp.half_plane_bytes)
+                              : reinterpret_cast<const T*>(sp.khw + (size_t)hq * sp.half_plane_bytes) - D / 2;
+        Vp = reinterpret_cast<const T*>(sp.v + (size_t)h * plane_bytes);
+    }
 
     for (int pg = pg0; pg < pg1; ++pg) {
         const long long page = page_table[slot * n_pages + pg];
@@ -99,9 +113,10 @@ decode_portable_kernel(const char* __restrict__ pool_layer, size_t plane_bytes, 
         if (n_here > P) n_here = P;
         for (int t = warp; t < n_here; t += kPortableWarps) {
             const size_t off = ((size_t)page * P + t) * D + lane * E;
+            const size_t koff = ((size_t)page * P + t) * k_row + lane * E;
             float s = 0.f;
 #pragma unroll
-            for (int e = 0; e < E; ++e) s += qv[e] * ElemTraits<T>::to_float(Kp[off + e]);
+            for (int e = 0; e < E; ++e) s += qv[e] * ElemTraits<T>::to_float(Kp[koff + e]);
 #pragma unroll
             for (int o = 16; o > 0; o >>= 1) s += __shfl_xor_sync(0xffffffffu, s, o);
             const float m_new = fmaxf(m, s);
@@ -179,7 +194,7 @@ static int launch_typed(const PoolView& pv, int layer, void* out, float* lse, co
     decode_portable_kernel<T, D, PosT, false><<<grid, kPortableWarps * 32, 0, stream>>>(
         pv.plane(layer, 0, 0), pv.plane_bytes(), pv.H, pv.page_table, pv.p2l, pv.n_pages, pv.max_batch, pv.P,
         (const T*)q, q_stride_b, q_stride_h, batch_idx, (const PosT*)pos, nullptr, Hq, sm_scale * kLog2e,
-        (float*)workspace, nullptr, nullptr, OutLayout{0, 0, 0, 0}, Epilogue{nullptr, 0, 0}, status);
+        (float*)workspace, nullptr, nullptr, OutLayout{0, 0, 0, 0}, Epilogue{nullptr, 0, 0}, status, split_ptrs(pv, layer));
     if (cudaGetLastError() != cudaSuccess) return FPKV_ELAUNCH;
     decode_portable_merge_kernel<T, D><<<B * Hq, D, 0, stream>>>((const float*)workspace, S, (T*)out, lse, Hq, epi);
     return cudaGetLastError() == cudaSuccess ? FPKV_OK : FPKV_ELAUNCH;
@@ -227,7 +242,7 @@ static int launch_prefill_typed(const PoolView& pv, int layer, void* out, float*
         decode_portable_kernel<T, D, int32_t, true><<<grid, kPortableWarps * 32, 0, s>>>(
             pv.plane(layer, 0, 0), pv.plane_bytes(), pv.H, pv.page_table, pv.p2l, pv.n_pages, pv.max_batch, pv.P,
             (const T*)q + (long long)t0 * qst, qst, qsh, bi + t0, nullptr, extent + t0, Hq, sc * kLog2e, nullptr,
-            (T*)out + (long long)t0 * lay.out_row, lse + t0, lay, epi, st);
+            (T*)out + (long long)t0 * lay.out_row, lse + t0, lay, epi, st, split_ptrs(pv, layer));
         if (cudaGetLastError() != cudaSuccess) return FPKV_ELAUNCH;
     }
     return FPKV_OK;

@@ -826,6 +826,7 @@ int launch_shape(int D, int nrep, const CUtensorMap& map, const CUtensorMap& map
 
 bool decode_tma_supported(const PoolView& pv, int Hq)
 {
+    if (pv.split_hq) return false;
     if (pv.dtype != FPKV_BF16 && pv.dtype != FPKV_F16) return false;
     if (pv.P != 128 || (pv.D != 64 && pv.D != 128)) return false;
     if (Hq % pv.H) return false;

@@ -24,7 +24,9 @@
 // h's 2-D table); with n_heads == n_kv_heads it holds each key head once,
 // rotated with the table of the first query head of its group, which equals the
 // reference whenever the 2-D frequencies agree within a group or no 2-D table is
-// in use.  HBM/latency-bound byte work: no shared memory, no tensor cores.
+// in use.  The split layout (common.cuh) stores the first half of each key head once and the second half per query
+// head with that head's table: exactly the reference's content in fewer bytes.
+// HBM/latency-bound byte work: no shared memory, no tensor cores.
 
 #include "common.cuh"
 
@@ -33,6 +35,8 @@ namespace {
 
 struct PreAppendParams {
     char* pool_layer; size_t plane_bytes; int H_out;
+    int split;                          // split layout: keys per query head (shared first half stored once), values per KV head
+    char* kt_base; char* khw_base; char* v_base; size_t half_plane_bytes;
     const int64_t* page_table; int n_pages, max_batch, P;
     const char* qkv; long long qkv_row_bytes;
     int Hq, Hkv;
@@ -82,10 +86,11 @@ pre_append_kernel(const PreAppendParams prm)
     using RowT = Row<T, E>;
     const int lane = threadIdx.x % 32;
     const int sub = lane % kLanesPerRow;                   // position of the lane within its row
-    const int items = prm.Hq + 2 * prm.H_out;              // per token: query heads, stored key heads, stored value heads
+    const int HK = prm.split ? prm.Hq : prm.H_out, HV = prm.split ? prm.Hkv : prm.H_out;   // key rows and value rows per token
+    const int items = prm.Hq + HK + HV;                    // per token: query heads, stored key heads, stored value heads
     const unsigned total = (unsigned)prm.n_tok * (unsigned)items;      // the launcher keeps this below 2^31: 32-bit index math
     const int n_rep = prm.Hq / prm.Hkv;
-    const bool expanded = prm.H_out == prm.Hq;
+    const bool expanded = prm.split || prm.H_out == prm.Hq;       // one key row per query head, each with its own 2-D table
     const PosT* pos = static_cast<const PosT*>(prm.pos);
     const unsigned rows_per_pass = gridDim.x * blockDim.x / kLanesPerRow;
     // whole warps stay in the loop together (shuffles below): rows past the end are computed on row 0 and dropped
@@ -95,13 +100,13 @@ pre_append_kernel(const PreAppendParams prm)
         const unsigned w = live ? w0 : 0u;
         const int t = (int)(w / (unsigned)items);
         const int item = (int)(w - (unsigned)t * (unsigned)items);
-        const int kind = item < prm.Hq ? 0 : (item < prm.Hq + prm.H_out ? 1 : 2);   // 0 query, 1 key, 2 value
-        const int ho = kind == 0 ? item : (kind == 1 ? item - prm.Hq : item - prm.Hq - prm.H_out);
+        const int kind = item < prm.Hq ? 0 : (item < prm.Hq + HK ? 1 : 2);   // 0 query, 1 key, 2 value
+        const int ho = kind == 0 ? item : (kind == 1 ? item - prm.Hq : item - prm.Hq - HK);
         // source head inside the token's QKV row, and the query head whose 2-D table applies
         int src_head, table_head;
         if (kind == 0) { src_head = ho; table_head = ho; }
         else {
-            const int kvh = expanded ? ho / n_rep : ho;
+            const int kvh = (kind == 1 ? expanded : (expanded && !prm.split)) ? ho / n_rep : ho;
             src_head = (kind == 1 ? prm.Hq : prm.Hq + prm.Hkv) + kvh;
             table_head = expanded ? ho : ho * n_rep;
         }
@@ -126,7 +131,16 @@ pre_append_kernel(const PreAppendParams prm)
                     store = false; page = 0;
                 }
                 const long long addr = page * prm.P + p % prm.P;
-                dst = prm.pool_layer + ((size_t)(kind - 1) * prm.H_out + ho) * prm.plane_bytes + (size_t)addr * D * sizeof(T);
+                if (!prm.split) {
+                    dst = prm.pool_layer + ((size_t)(kind - 1) * prm.H_out + ho) * prm.plane_bytes + (size_t)addr * D * sizeof(T);
+                } else if (kind == 2) {
+                    dst = prm.v_base + (size_t)ho * prm.plane_bytes + (size_t)addr * D * sizeof(T);
+                } else if (sub * E < D / 2) {              // first half of the key row: once per KV head, from the group's first query head
+                    if (ho % n_rep != 0) store = false;
+                    dst = prm.kt_base + (size_t)(ho / n_rep) * prm.half_plane_bytes + (size_t)addr * (D / 2) * sizeof(T);
+                } else {                                   // second half: per query head; `dst` is biased so that the lane offset below fits
+                    dst = prm.khw_base + (size_t)ho * prm.half_plane_bytes + (size_t)addr * (D / 2) * sizeof(T) - (size_t)(D / 2) * sizeof(T);
+                }
             }
         }
         const RowT in = *reinterpret_cast<const RowT*>(prm.qkv + t * prm.qkv_row_bytes + ((size_t)src_head * D + sub * E) * sizeof(T));
@@ -171,7 +185,7 @@ pre_append_kernel(const PreAppendParams prm)
 template <typename T, int D>
 int launch_typed(const PreAppendParams& prm, int pos_type, cudaStream_t stream)
 {
-    const long long rows = (long long)prm.n_tok * (prm.Hq + 2 * prm.H_out);
+    const long long rows = (long long)prm.n_tok * (prm.split ? 2 * prm.Hq + prm.Hkv : prm.Hq + 2 * prm.H_out);
     const int rows_per_block = 256 / kLanesPerRow;
     long long blocks = (rows + rows_per_block - 1) / rows_per_block;
     if (blocks > 148 * 8) blocks = 148 * 8;               // grid-stride beyond eight CTAs per SM
@@ -188,9 +202,12 @@ int launch_pre_append(const PoolView& pv, int layer, const void* qkv, long long 
                       long long q_stride_t, float eps, int32_t* status, cudaStream_t stream)
 {
     if (n_tok == 0) return FPKV_OK;
-    if ((long long)n_tok * (Hq + 2 * pv.H) >= (1ll << 31) - 4) return FPKV_ESHAPE;
+    if ((long long)n_tok * (2 * Hq + 2 * pv.H) >= (1ll << 31) - 4) return FPKV_ESHAPE;
     PreAppendParams prm;
     prm.pool_layer = pv.plane(layer, 0, 0); prm.plane_bytes = pv.plane_bytes(); prm.H_out = pv.H;
+    prm.split = pv.split_hq ? 1 : 0;
+    prm.kt_base = prm.khw_base = prm.v_base = nullptr; prm.half_plane_bytes = pv.half_plane_bytes();
+    if (pv.split_hq) { prm.kt_base = pv.kt_plane(layer, 0); prm.khw_base = pv.khw_plane(layer, 0); prm.v_base = pv.v_plane(layer, 0); }
     prm.page_table = pv.page_table; prm.n_pages = pv.n_pages; prm.max_batch = pv.max_batch; prm.P = pv.P;
     prm.qkv = static_cast<const char*>(qkv); prm.qkv_row_bytes = qkv_stride_t * pv.esize;
     prm.Hq = Hq; prm.Hkv = Hkv;

@@ -806,6 +806,7 @@ constexpr int kPrefillSmem = 1024 + (2 + 2 * kStages) * kTileBytes + 48 * 8 + 16
 
 bool prefill_tc_supported(const PoolView& pv, int Hq)
 {
+    if (pv.split_hq) return false;
     if (pv.dtype != FPKV_BF16 && pv.dtype != FPKV_F16) return false;
     if (pv.P != kPage || pv.D != kHeadDim) return false;
     if (Hq % pv.H) return false;

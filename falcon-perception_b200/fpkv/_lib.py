@@ -36,7 +36,7 @@ class FpkvPool(ctypes.Structure):
                 ("physical_to_logical", ctypes.c_void_p),
                 ("num_layers", ctypes.c_int32), ("n_heads", ctypes.c_int32), ("n_pages", ctypes.c_int32),
                 ("page_size", ctypes.c_int32), ("head_dim", ctypes.c_int32), ("max_batch_size", ctypes.c_int32),
-                ("dtype", ctypes.c_int32), ("reserved_", ctypes.c_int32)]
+                ("dtype", ctypes.c_int32), ("split_q_heads", ctypes.c_int32)]
 
 
 class FpkvAllocState(ctypes.Structure):

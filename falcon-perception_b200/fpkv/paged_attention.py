@@ -66,8 +66,25 @@ class PagedKVCache(KVCacheBase):
     """Page pool + page table + free lists; see the module docstring."""
 
     def __init__(self, n_pages: int, page_size: int, max_batch_size: int, n_heads: int, head_dim: int,
-                 num_layers: int, dtype: torch.dtype, device: str | torch.device = "cuda"):
+                 num_layers: int, dtype: torch.dtype, device: str | torch.device = "cuda",
+                 split_q_heads: int | None = None):
+        """``split_q_heads`` (the model's query head count, with ``n_heads`` the KV
+        heads) selects the split layout: the first half of every key head (1-D
+        rotary embedding, the same for all query heads of a group) and V are
+        stored once per KV head, the second half of K (per-query-head 2-D rotary
+        embedding, ``falcon_perception/rope.py:59-104``) once per query head.  That
+        is exactly the content of the reference's expanded cache in
+        (3*n_heads + split_q_heads)/(4*split_q_heads) of its bytes (5/8 at two
+        query heads per KV head).  ``insert_kv`` then takes the reference's
+        expanded K and V (``split_q_heads`` heads), ``pre_attention_append`` writes
+        the layout directly, attention is called with ``split_q_heads`` query heads.
+        ``kv_cache`` is then a (num_layers, elements) tensor; ``k_first``, ``k_second``
+        and ``v_plane`` give views of a layer's three regions."""
         assert dtype in _DTYPES, "dtype must be float32, bfloat16 or float16"
+        self.split_q_heads = int(split_q_heads) if split_q_heads else 0
+        if self.split_q_heads:
+            assert self.split_q_heads % n_heads == 0 and self.split_q_heads > n_heads, \
+                "split_q_heads must be a multiple of n_heads (the KV heads) and larger"
         self.n_pages = n_pages
         self.page_size = page_size
         self.max_batch_size = max_batch_size
@@ -88,12 +105,16 @@ class PagedKVCache(KVCacheBase):
         # [slot, physical page] -> logical page
         self._physical_to_logical = torch.full((max_batch_size, n_pages), -1, dtype=torch.int64, device=device)
 
-        self.kv_shape = (num_layers, 2, 1, n_heads, n_pages * page_size, head_dim)
+        if self.split_q_heads:
+            rows = n_pages * page_size
+            self.kv_shape = (num_layers, rows * (3 * n_heads + self.split_q_heads) * (head_dim // 2))
+        else:
+            self.kv_shape = (num_layers, 2, 1, n_heads, n_pages * page_size, head_dim)
         self.kv_cache = torch.zeros(self.kv_shape, dtype=dtype, device=device)
 
         self._pool = _lib.FpkvPool(self.kv_cache.data_ptr(), self._page_table.data_ptr(),
                                    self._physical_to_logical.data_ptr(), num_layers, n_heads, n_pages,
-                                   page_size, head_dim, max_batch_size, _DTYPES[dtype], 0)
+                                   page_size, head_dim, max_batch_size, _DTYPES[dtype], self.split_q_heads)
         self._status = torch.zeros(1, dtype=torch.int32, device=device)
         self._workspace = None
         self.decode_kernel = _lib.DECODE_AUTO       # DECODE_PORTABLE / DECODE_TMA force one kernel
@@ -118,6 +139,27 @@ class PagedKVCache(KVCacheBase):
             self._ops_dev = torch.empty((self._ops_cap, 4), dtype=torch.int32, device=device)
             self._ops_turn = 0
             self._upload_lists()
+
+    # ------------------------------------------------------- split-layout views
+    def _split_regions(self, layer_id: int):
+        assert self.split_q_heads, "the pool does not use the split layout"
+        rows, half = self.n_pages * self.page_size, self.head_dim // 2
+        flat = self.kv_cache[layer_id]
+        a, b = self.n_heads * rows * half, (self.n_heads + self.split_q_heads) * rows * half
+        return (flat[:a].view(self.n_heads, rows, half), flat[a:b].view(self.split_q_heads, rows, half),
+                flat[b:].view(self.n_heads, rows, self.head_dim))
+
+    def k_first(self, layer_id: int) -> Tensor:
+        """(n_heads, n_pages*page_size, head_dim/2): first half of K, one per KV head."""
+        return self._split_regions(layer_id)[0]
+
+    def k_second(self, layer_id: int) -> Tensor:
+        """(split_q_heads, n_pages*page_size, head_dim/2): second half of K, one per query head."""
+        return self._split_regions(layer_id)[1]
+
+    def v_plane(self, layer_id: int) -> Tensor:
+        """(n_heads, n_pages*page_size, head_dim): V, one per KV head."""
+        return self._split_regions(layer_id)[2]
 
     # ------------------------------------------------------------------ tables
     @property
@@ -307,7 +349,7 @@ class PagedKVCache(KVCacheBase):
     def assign(self, layer_id: int, batch_idx: Tensor, input_pos: Tensor, k_val: Tensor, v_val: Tensor):
         """Decode append of (B,H,1,D) rows; returns this layer's K and V pool views."""
         B, H, S, K_D = k_val.shape
-        _, _, _, H_cache, MAX_S, D_cache = self.kv_cache.shape
+        H_cache, MAX_S, D_cache = self.split_q_heads or self.n_heads, self.n_pages * self.page_size, self.head_dim
         assert H_cache == H, "number of heads must match"
         assert MAX_S >= S, "cache must have enough space"
         assert D_cache == K_D, "hidden dim must match"
@@ -327,6 +369,8 @@ class PagedKVCache(KVCacheBase):
             ctypes.byref(self._pool), layer_id, batch_idx.data_ptr(), input_pos.data_ptr(), _pos_type(input_pos),
             k_val.data_ptr(), k_val.stride(0), k_val.stride(1), v_val.data_ptr(), v_val.stride(0), v_val.stride(1),
             B, self._status_ptr(), _stream(self._dev)), "fpkv_append_decode")
+        if self.split_q_heads:
+            return None, None                       # no (1, H, rows, D) views exist of the split regions; attention reads the pool
         return self.kv_cache[layer_id, 0], self.kv_cache[layer_id, 1]
 
     def assign_prefill_no_paging(self, layer_id: int, k_val: Tensor, v_val: Tensor, input_pos: Tensor,
@@ -338,7 +382,7 @@ class PagedKVCache(KVCacheBase):
         assert input_pos.ndim == 2, "input_pos must be a 2D tensor"
         assert k_val.ndim == 4, "k_val must be a 4D tensor"
         assert v_val.ndim == 4, "v_val must be a 4D tensor"
-        assert k_val.shape[0] == 1 and k_val.shape[1] == self.n_heads and k_val.shape[3] == self.head_dim
+        assert k_val.shape[0] == 1 and k_val.shape[1] == (self.split_q_heads or self.n_heads) and k_val.shape[3] == self.head_dim
         assert v_val.shape == k_val.shape and k_val.shape[2] == batch_idx.shape[1] == input_pos.shape[1]
         assert k_val.dtype == self.dtype and v_val.dtype == self.dtype, "dtype must match the pool"
         self._require_cuda(k_val, v_val, batch_idx, input_pos)
@@ -372,7 +416,10 @@ class PagedKVCache(KVCacheBase):
         B, S, W = qkv.shape
         D = self.head_dim
         assert W == (n_q_heads + 2 * n_kv_heads) * D, "qkv width must be (Hq + 2*Hkv) * head_dim"
-        assert self.n_heads in (n_q_heads, n_kv_heads), "the pool must hold the query or the KV head count"
+        if self.split_q_heads:
+            assert (self.split_q_heads, self.n_heads) == (n_q_heads, n_kv_heads), "head counts must match the split pool"
+        else:
+            assert self.n_heads in (n_q_heads, n_kv_heads), "the pool must hold the query or the KV head count"
         assert qkv.dtype == self.dtype, "dtype must match the pool"
         assert freqs_cis.shape == (B, S, D // 4) and freqs_cis.dtype == torch.complex64
         if freqs_cis_2d is not None:
@@ -418,8 +465,9 @@ class PagedKVCache(KVCacheBase):
         """K and V of logical positions [0, n_tokens) of a slot as two
         (n_heads, n_tokens, head_dim) tensors read through the page table."""
         self._require_cuda()
-        k = torch.empty((self.n_heads, n_tokens, self.head_dim), dtype=self.dtype, device=self._dev)
-        v = torch.empty_like(k)
+        # split layout: K per query head (put together as the reference's expanded cache holds it), V per KV head
+        k = torch.empty((self.split_q_heads or self.n_heads, n_tokens, self.head_dim), dtype=self.dtype, device=self._dev)
+        v = torch.empty((self.n_heads, n_tokens, self.head_dim), dtype=self.dtype, device=self._dev)
         _lib.check(_lib.lib.fpkv_gather(ctypes.byref(self._pool), layer_id, slot, n_tokens, k.data_ptr(),
                                         v.data_ptr(), self._status_ptr(), _stream(self._dev)), "fpkv_gather")
         return k, v
@@ -460,6 +508,7 @@ class PagedKVCache(KVCacheBase):
         B, Hq, S, D = q.shape
         assert S == 1, "decode attention takes one query token per row"
         assert D == self.head_dim and Hq % self.n_heads == 0, "head layout must match the pool"
+        assert not self.split_q_heads or Hq == self.split_q_heads, "a split pool serves exactly split_q_heads query heads"
         assert q.dtype == self.dtype, "q dtype must match the pool"
         assert batch_idx.shape == (B,), "batch_idx must have one dimension only"
         input_pos = input_pos.reshape(-1)
@@ -501,6 +550,7 @@ class PagedKVCache(KVCacheBase):
         output projection, without the reference's permute + copy."""
         _, Hq, L, D = q.shape
         assert q.shape[0] == 1 and D == self.head_dim and Hq % self.n_heads == 0 and q.dtype == self.dtype
+        assert not self.split_q_heads or Hq == self.split_q_heads, "a split pool serves exactly split_q_heads query heads"
         assert batch_idx.shape[-1] == L and input_pos.shape[-1] == L and mask.L == L
         self._require_cuda(q, batch_idx, input_pos)
         bi = batch_idx.reshape(-1)

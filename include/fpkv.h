@@ -75,6 +75,25 @@ typedef enum { FPKV_I32 = 0, FPKV_I64 = 1 } fpkv_itype;
  *                        garbage never reaches a result.  Reserved page 0
  *                        (rows [0, page_size) of every plane) is the landing
  *                        place of padding rows and is never read.
+ *                        SPLIT LAYOUT (split_q_heads = the model's query head
+ *                        count, a multiple of n_heads greater than it): the
+ *                        reference expands K and V to the query heads before
+ *                        caching (model.py:114-115), and its copies of a KV head
+ *                        differ only in the second half of K, which carries the
+ *                        per-query-head 2-D rotary embedding (rope.py:59-104).
+ *                        The split pool stores exactly that content once: per
+ *                        layer, contiguous,
+ *                          K first halves  [n_heads]      [rows][head_dim/2]
+ *                          K second halves [split_q_heads][rows][head_dim/2]
+ *                          V               [n_heads]      [rows][head_dim]
+ *                        with rows = n_pages*page_size, i.e. (3*n_heads +
+ *                        split_q_heads)*head_dim/2 elements per token instead of
+ *                        the reference's 2*split_q_heads*head_dim.  Append entry
+ *                        points then take K and V with split_q_heads heads (the
+ *                        reference's expanded tensors; the first head of each
+ *                        group supplies the shared parts), fpkv_pre_append writes
+ *                        the layout directly, the attention entry points are
+ *                        called with n_q_heads = split_q_heads.
  *   page_table           device int64 (max_batch_size, n_pages)   (:58-59)
  *   physical_to_logical  device int64 (max_batch_size, n_pages)   (:70)
  */
@@ -89,7 +108,7 @@ typedef struct fpkv_pool {
     int32_t head_dim;
     int32_t max_batch_size;
     int32_t dtype;              /* fpkv_dtype */
-    int32_t reserved_;
+    int32_t split_q_heads;      /* 0: the layout above; > 0: the split layout below */
 } fpkv_pool;
 
 /*

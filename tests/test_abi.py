@@ -59,7 +59,7 @@ def test_version_and_strerror():
 def _pool(**kw):
     buf = torch.zeros(64, dtype=torch.int64)       # any 16-byte aligned host memory: never dereferenced
     d = dict(data=buf.data_ptr(), page_table=buf.data_ptr(), physical_to_logical=buf.data_ptr(), num_layers=1,
-             n_heads=2, n_pages=4, page_size=16, head_dim=64, max_batch_size=3, dtype=_lib.FPKV_BF16, reserved_=0)
+             n_heads=2, n_pages=4, page_size=16, head_dim=64, max_batch_size=3, dtype=_lib.FPKV_BF16, split_q_heads=0)
     d.update(kw)
     return _lib.FpkvPool(**d), buf
 
