@@ -821,7 +821,60 @@ def bench_stack(rk, args, steps=64):
     }
 
 
-PARTS = {"prefill": bench_prefill, "mixed_step": bench_mixed, "long_context": bench_long_context, "stack": bench_stack}
+def bench_split_layout(rk, args, n_pages=8192):
+    """Config 2's decode step over a split pool (first half of K and V once per KV head, second half of K once per
+    query head): the layout that is exact under per-query-head 2-D rotary, at 5/8 of the bytes of the expanded
+    cache the reference keeps for that case.  Reports the step, the attention call alone, and its rate on the bytes
+    the split layout holds (640 B per key and KV group at these head counts)."""
+    from fpkv.paged_attention import PagedKVCache
+    device, rank = rk.device, rk.rank
+    stream = torch.cuda.current_stream(device)
+    B, K = BATCH, 20
+    case = rank_case(rank, B, n_pages, LEN_LO, LEN_HI, 2002)
+    cache = PagedKVCache(n_pages, P, B + 9, HKV, D, 1, torch.bfloat16, device, split_q_heads=HQ)
+    cache.free_pages = list(case.free_pages)
+    slots = []
+    for L in case.lens:
+        s = cache.allocate(); slots.append(s); cache.reserve(s, None, L + 1 + WINDOW)
+    cache.kv_cache.normal_(0, D ** -0.5)
+    g = torch.Generator(device=device).manual_seed(55 + rank)
+    NV = 4
+    q, k, v = ((torch.randn((NV, B, HQ, 1, D), device=device, generator=g) * D ** -0.5).bfloat16() for _ in range(3))
+    bidx = torch.tensor(slots, dtype=torch.int64, device=device)
+    pos = (torch.tensor(case.lens, dtype=torch.int32).view(1, B) + torch.arange(WINDOW, dtype=torch.int32).view(-1, 1)).to(device)
+    out = torch.empty((B, HQ, 1, D), dtype=torch.bfloat16, device=device)
+    lse = torch.empty((B, HQ, 1), dtype=torch.float32, device=device)
+
+    def step(i):
+        cache.decode_step(0, q[i % NV], k[i % NV], v[i % NV], bidx, pos[i % WINDOW], out=out, lse=lse)
+
+    def attn(i):
+        cache.decode_attention(0, q[i % NV], bidx, pos[i % WINDOW], out=out, lse=lse)
+    for i in range(5):
+        step(i)
+    R = 10
+    step_blocks, _ = timed_blocks(rk, stream, R, K, step, 5)
+    attn_blocks, _ = timed_blocks(rk, stream, R, K, attn, 5)
+    cache.check_status()
+    per_key = (HKV * (D // 2) + HQ * (D // 2) + HKV * D) * 2          # bytes of one key position in the split layout
+    keys = [sum(L + 1 + (5 + r * K + i) % WINDOW for L in case.lens for i in range(K)) for r in range(R)]
+    rates = [kk * per_key / (t * 1e-3) / 1e9 for kk, t in zip(keys, attn_blocks)]
+    mid = sorted(range(R), key=lambda r: rates[r])[R // 2]
+    hbm_peak, _, which = measured_peaks()
+    (t_attn, t_step), (work,) = rk.reduce([attn_blocks[mid], step_blocks[mid]], [float(keys[mid] * per_key)])
+    gbs = work / (t_attn * 1e-3) / 1e9
+    return {"workload": "config 2's decode step on a split pool (16 q heads / 8 kv heads, head_dim 128, page 128, "
+                        f"batch {B}, context uniform [{LEN_LO},{LEN_HI}], pool {n_pages} pages)",
+            "metric": "split_layout_decode_attention_bandwidth", "value": round(gbs, 1), "unit": "GB/s",
+            "bytes_per_key_and_kv_group": per_key // HKV, "expanded_cache_bytes_per_key_and_kv_group": 2 * (HQ // HKV) * D * 2,
+            "attn_ms": round(t_attn / K, 4), "step_ms": round(t_step / K, 4), "steps": K, "blocks": R,
+            "frac_of_hbm_peak": round(gbs / (hbm_peak * rk.world), 3), "peak": which,
+            "expanded_equivalent_gbs": round(gbs * (2 * HQ * D * 2) / per_key, 1),
+            "gpu_launches_per_step": 3}
+
+
+PARTS = {"prefill": bench_prefill, "mixed_step": bench_mixed, "long_context": bench_long_context, "stack": bench_stack,
+         "split_layout": bench_split_layout}
 
 
 def run_fpkv(args):

@@ -48,6 +48,7 @@
 //  falcon_perception/paged_attention.py:234-333, falcon_perception/model.py:156-162).
 
 #include <cuda.h>          // CUtensorMap (types only; the encoder is fetched at run time)
+#include <string.h>
 #include "common.cuh"
 
 namespace fpkv {
@@ -193,11 +194,24 @@ __device__ __forceinline__ int unit_of(const int* ub, int NU, int t) {     // ub
 }
 
 // ------------------------------------------------------------------ kernel
-template <typename T, int D, int P, int NREP, typename PosT>
+// Tensor maps of one layer.  Uniform layout: `kv` covers the K and V planes (box = one page), `kv_rows` the
+// same tensor with a box of one consumer warp's rows of one 64-element column group.  Split layout (16-bit,
+// head_dim 128): the first K halves, the second K halves and V are three tensors, each with a page box and
+// a row-group box; a half-plane row is 64 elements = one 128-byte swizzle row, so a first half and a second
+// half copied side by side form the same shared-memory tile as a whole K page of the uniform layout.
+struct TileMaps {
+    CUtensorMap kv, kv_rows;
+    CUtensorMap kt, kt_rows, khw, khw_rows, v, v_rows;
+};
+
+template <typename T, int D, int P, int NREP, typename PosT, bool SPLIT>
 __global__ void __launch_bounds__(kThreads, 1)
-decode_tma_kernel(const __grid_constant__ CUtensorMap tmap, const __grid_constant__ CUtensorMap tmap_rows,
-                  const Params prm)
+decode_tma_kernel(const __grid_constant__ TileMaps maps, const Params prm)
 {
+    // ring slots one tile takes: K and V, or (split) K of the group's first query head, the second K half of each
+    // further query head, and V
+    constexpr int kSlotsPerTile = SPLIT ? NREP + 1 : 2;
+    static_assert(!SPLIT || (D == 128 && NREP >= 2), "the split layout needs head_dim 128 and a real GQA group");
     using L = Layout<D, P, NREP>;
     constexpr int NS = L::kSlots;
     constexpr int kTile = L::kTileBytes;
@@ -395,7 +409,8 @@ decode_tma_kernel(const __grid_constant__ CUtensorMap tmap, const __grid_constan
         // ============================ issue warp ============================
         if (lane != 0) return;
         if (prm.after_append) asm volatile("griddepcontrol.wait;" ::: "memory");   // the appended rows are in the pool
-        uint32_t it = 0, blk = 0;                      // ring position (one per K or V tile), descriptor block
+        uint32_t it = 0, blk = 0;                      // ring position (one per slot filled), descriptor block
+        int tiles_issued = 0;
         bool ok = true;
         while (ok) {
             const uint32_t ds = blk % kDescBlocks, dph = (blk / kDescBlocks) & 1u;
@@ -406,28 +421,67 @@ decode_tma_kernel(const __grid_constant__ CUtensorMap tmap, const __grid_constan
                 const int desc = drow[ds * 32 + j];
                 const int rk = desc < 0 ? -1 : (desc & ~(P - 1));
                 const int groups = desc < 0 ? 0 : (desc & (P - 1)) + 1;
+                if constexpr (!SPLIT) {
 #pragma unroll
-                for (int kv = 0; kv < 2; ++kv, ++it) {
-                    const uint32_t s = it % NS, ph = (it / NS) & 1u;
-                    if (!mbar_wait(empty0 + 8 * s, ph ^ 1u, abort_flag)) { ok = false; break; }
-                    slot_valid[s] = groups;
-                    const int row = rk + kv * Hkv * prm.rows_per_plane;
-                    const uint32_t dst = smem_u32(ring + s * kTile);
-                    if (groups == kConsumerWarps) {                     // whole page: one copy
-                        mbar_arrive_expect_tx(full0 + 8 * s, kTile);
-                        tma_load_3d(dst, &tmap, 0, row, 0, full0 + 8 * s);
-                    } else if (groups > 0) {                            // filled part of a row's last page
-                        mbar_arrive_expect_tx(full0 + 8 * s, groups * RW * D * 2);
-                        for (int g = 0; g < groups; ++g)
+                    for (int kv = 0; kv < 2; ++kv, ++it) {
+                        const uint32_t s = it % NS, ph = (it / NS) & 1u;
+                        if (!mbar_wait(empty0 + 8 * s, ph ^ 1u, abort_flag)) { ok = false; break; }
+                        slot_valid[s] = groups;
+                        const int row = rk + kv * Hkv * prm.rows_per_plane;
+                        const uint32_t dst = smem_u32(ring + s * kTile);
+                        if (groups == kConsumerWarps) {                     // whole page: one copy
+                            mbar_arrive_expect_tx(full0 + 8 * s, kTile);
+                            tma_load_3d(dst, &maps.kv, 0, row, 0, full0 + 8 * s);
+                        } else if (groups > 0) {                            // filled part of a row's last page
+                            mbar_arrive_expect_tx(full0 + 8 * s, groups * RW * D * 2);
+                            for (int g = 0; g < groups; ++g)
 #pragma unroll
-                            for (int half = 0; half < D / 64; ++half)
-                                tma_load_3d(dst + half * (P * 128) + g * (RW * 128), &tmap_rows, 0, row + g * RW, half,
-                                            full0 + 8 * s);
-                    } else {
-                        mbar_arrive(full0 + 8 * s);
+                                for (int half = 0; half < D / 64; ++half)
+                                    tma_load_3d(dst + half * (P * 128) + g * (RW * 128), &maps.kv_rows, 0, row + g * RW, half,
+                                                full0 + 8 * s);
+                        } else {
+                            mbar_arrive(full0 + 8 * s);
+                        }
+                    }
+                } else {
+                    // rk = stored head * rows + page * P: the row in the first-half tensor and in the V tensor; the
+                    // second half of query head r of the group lives (head * (NREP - 1) + r) planes further on
+                    const int hkv = rk < 0 ? 0 : rk / prm.rows_per_plane;
+#pragma unroll
+                    for (int part = 0; part < kSlotsPerTile; ++part, ++it) {
+                        const uint32_t s = it % NS, ph = (it / NS) & 1u;
+                        if (!mbar_wait(empty0 + 8 * s, ph ^ 1u, abort_flag)) { ok = false; break; }
+                        slot_valid[s] = groups;
+                        const uint32_t dst = smem_u32(ring + s * kTile);
+                        const uint32_t bar = full0 + 8 * s;
+                        if (groups == 0) { mbar_arrive(bar); continue; }
+                        const bool whole = groups == kConsumerWarps;
+                        if (part < NREP) {                                  // K: part 0 brings the shared first half too
+                            const int row_hw = rk + (hkv * (NREP - 1) + part) * prm.rows_per_plane;
+                            const int halves = part == 0 ? 2 : 1;
+                            mbar_arrive_expect_tx(bar, halves * groups * RW * 64 * 2);
+                            if (whole) {
+                                if (part == 0) tma_load_3d(dst, &maps.kt, 0, rk, 0, bar);
+                                tma_load_3d(dst + P * 128, &maps.khw, 0, row_hw, 0, bar);
+                            } else {
+                                for (int g = 0; g < groups; ++g) {
+                                    if (part == 0) tma_load_3d(dst + g * (RW * 128), &maps.kt_rows, 0, rk + g * RW, 0, bar);
+                                    tma_load_3d(dst + P * 128 + g * (RW * 128), &maps.khw_rows, 0, row_hw + g * RW, 0, bar);
+                                }
+                            }
+                        } else {                                            // V
+                            mbar_arrive_expect_tx(bar, groups * RW * D * 2);
+                            if (whole) tma_load_3d(dst, &maps.v, 0, rk, 0, bar);
+                            else
+                                for (int g = 0; g < groups; ++g)
+#pragma unroll
+                                    for (int half = 0; half < 2; ++half)
+                                        tma_load_3d(dst + half * (P * 128) + g * (RW * 128), &maps.v_rows, 0, rk + g * RW, half, bar);
+                        }
                     }
                 }
-                *issued = (int)(it >> 1);              // tiles issued so far: paces the scout's claims
+                ++tiles_issued;
+                *issued = tiles_issued;                // tiles issued so far: paces the scout's claims
             }
             mbar_arrive(dempty0 + 8 * ds);
             ++blk;
@@ -538,14 +592,46 @@ decode_tma_kernel(const __grid_constant__ CUtensorMap tmap, const __grid_constan
                                                   (((chunk & 7) ^ (row & 7)) << 4);
                             uint32_t b0, b1, b2, b3;
                             ldsm_x4(addr, b0, b1, b2, b3);
-                            Mma<T>::run(sc[j], qa[2 * kp][0], 0u, qa[2 * kp][1], 0u, b0, b1);
-                            Mma<T>::run(sc[j], qa[2 * kp + 1][0], 0u, qa[2 * kp + 1][1], 0u, b2, b3);
+                            // split layout: the second half of head_dim in this slot belongs to the group's first query
+                            // head only (row 0 of the A fragment); the other heads' second halves follow in their own slots
+                            const bool mine = !SPLIT || kp < D / 64 || g == 0;
+                            Mma<T>::run(sc[j], mine ? qa[2 * kp][0] : 0u, 0u, mine ? qa[2 * kp][1] : 0u, 0u, b0, b1);
+                            Mma<T>::run(sc[j], mine ? qa[2 * kp + 1][0] : 0u, 0u, mine ? qa[2 * kp + 1][1] : 0u, 0u, b2, b3);
                         }
                     }
                 }
                 __syncwarp();
                 if (lane == 0) mbar_arrive(empty0 + 8 * s);
                 ++it;
+                if constexpr (SPLIT) {
+#pragma unroll 1
+                    for (int r = 1; r < NREP; ++r) {                    // second K half of query head r of the group
+                        s = it % NS; ph = (it / NS) & 1u;
+                        if (!mbar_wait(full0 + 8 * s, ph, abort_flag)) { alive = false; break; }
+                        if (valid) {
+                            const uint32_t kt = smem_u32(ring + s * kTile);
+#pragma unroll
+                            for (int j = 0; j < NB; ++j) {
+                                const int row = warp * RW + j * 8 + (lane & 7);
+#pragma unroll
+                                for (int kp = D / 64; kp < D / 32; ++kp) {
+                                    const int chunk = kp * 4 + (lane >> 3);
+                                    const uint32_t addr = kt + (chunk >> 3) * (P * 128) + row * 128 +
+                                                          (((chunk & 7) ^ (row & 7)) << 4);
+                                    uint32_t b0, b1, b2, b3;
+                                    ldsm_x4(addr, b0, b1, b2, b3);
+                                    const bool mine = g == r;
+                                    Mma<T>::run(sc[j], mine ? qa[2 * kp][0] : 0u, 0u, mine ? qa[2 * kp][1] : 0u, 0u, b0, b1);
+                                    Mma<T>::run(sc[j], mine ? qa[2 * kp + 1][0] : 0u, 0u, mine ? qa[2 * kp + 1][1] : 0u, 0u, b2, b3);
+                                }
+                            }
+                        }
+                        __syncwarp();
+                        if (lane == 0) mbar_arrive(empty0 + 8 * s);
+                        ++it;
+                    }
+                    if (!alive) break;
+                }
 
                 // ---------------- online softmax (row g only) ---------------
                 uint32_t pa[NB];                                        // packed probabilities, A-operand order
@@ -777,11 +863,11 @@ size_t partial_bytes(int G, int nrep, int D) {
     return ((size_t)kPhases * G * 2 * nrep * (D + 2) * sizeof(float) + 255) / 256 * 256;
 }
 
-template <typename T, int D, int P, int NREP, typename PosT>
-int launch_one(const CUtensorMap& map, const CUtensorMap& map_rows, Params prm, int G, cudaStream_t stream)
+template <typename T, int D, int P, int NREP, typename PosT, bool SPLIT>
+int launch_one(const TileMaps& maps, Params prm, int G, cudaStream_t stream)
 {
     using L = Layout<D, P, NREP>;
-    auto kern = decode_tma_kernel<T, D, P, NREP, PosT>;
+    auto kern = decode_tma_kernel<T, D, P, NREP, PosT, SPLIT>;
     // per device and idempotent; set on every call so that the library keeps no state
     if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, L::kSmemBytes) != cudaSuccess)
         return FPKV_ELAUNCH;
@@ -792,7 +878,7 @@ int launch_one(const CUtensorMap& map, const CUtensorMap& map_rows, Params prm, 
         cudaLaunchConfig_t cfg = {};
         cfg.gridDim = dim3(G); cfg.blockDim = dim3(kThreads); cfg.dynamicSmemBytes = L::kSmemBytes; cfg.stream = stream;
         cfg.attrs = attr; cfg.numAttrs = 1;
-        if (cudaLaunchKernelEx(&cfg, kern, map, map_rows, prm) != cudaSuccess) return FPKV_ELAUNCH;
+        if (cudaLaunchKernelEx(&cfg, kern, maps, prm) != cudaSuccess) return FPKV_ELAUNCH;
     }
     // the finish kernel may become resident while the main grid runs; it waits for it on the device
     cudaLaunchConfig_t cfg = {};
@@ -803,35 +889,46 @@ int launch_one(const CUtensorMap& map, const CUtensorMap& map_rows, Params prm, 
 }
 
 template <typename T, int D, int P, typename PosT>
-int launch_nrep(int nrep, const CUtensorMap& map, const CUtensorMap& map_rows, const Params& prm, int G, cudaStream_t s)
+int launch_nrep(int nrep, const TileMaps& maps, const Params& prm, int G, cudaStream_t s)
 {
     switch (nrep) {
-        case 1: return launch_one<T, D, P, 1, PosT>(map, map_rows, prm, G, s);
-        case 2: return launch_one<T, D, P, 2, PosT>(map, map_rows, prm, G, s);
-        case 4: return launch_one<T, D, P, 4, PosT>(map, map_rows, prm, G, s);
-        case 8: return launch_one<T, D, P, 8, PosT>(map, map_rows, prm, G, s);
+        case 1: return launch_one<T, D, P, 1, PosT, false>(maps, prm, G, s);
+        case 2: return launch_one<T, D, P, 2, PosT, false>(maps, prm, G, s);
+        case 4: return launch_one<T, D, P, 4, PosT, false>(maps, prm, G, s);
+        case 8: return launch_one<T, D, P, 8, PosT, false>(maps, prm, G, s);
     }
     return FPKV_ESHAPE;
 }
 
 template <typename T, typename PosT>
-int launch_shape(int D, int nrep, const CUtensorMap& map, const CUtensorMap& map_rows, const Params& prm, int G, cudaStream_t s)
+int launch_split(int nrep, const TileMaps& maps, const Params& prm, int G, cudaStream_t s)
 {
-    return D == 128 ? launch_nrep<T, 128, 128, PosT>(nrep, map, map_rows, prm, G, s)
-                    : launch_nrep<T, 64, 128, PosT>(nrep, map, map_rows, prm, G, s);
+    switch (nrep) {
+        case 2: return launch_one<T, 128, 128, 2, PosT, true>(maps, prm, G, s);
+        case 4: return launch_one<T, 128, 128, 4, PosT, true>(maps, prm, G, s);
+    }
+    return FPKV_ESHAPE;
+}
+
+template <typename T, typename PosT>
+int launch_shape(int D, int nrep, bool split, const TileMaps& maps, const Params& prm, int G, cudaStream_t s)
+{
+    if (split) return launch_split<T, PosT>(nrep, maps, prm, G, s);
+    return D == 128 ? launch_nrep<T, 128, 128, PosT>(nrep, maps, prm, G, s)
+                    : launch_nrep<T, 64, 128, PosT>(nrep, maps, prm, G, s);
 }
 
 }  // namespace
 
-
 bool decode_tma_supported(const PoolView& pv, int Hq)
 {
-    if (pv.split_hq) return false;
     if (pv.dtype != FPKV_BF16 && pv.dtype != FPKV_F16) return false;
     if (pv.P != 128 || (pv.D != 64 && pv.D != 128)) return false;
     if (Hq % pv.H) return false;
     const int nrep = Hq / pv.H;
     if (nrep != 1 && nrep != 2 && nrep != 4 && nrep != 8) return false;
+    // split layout: a half-plane row must be one 128-byte swizzle row (head_dim 128); groups of 2 or 4 query heads
+    if (pv.split_hq && (pv.D != 128 || Hq != pv.split_hq || (nrep != 2 && nrep != 4))) return false;
     // TMA coordinates are 32-bit token rows within one layer's K and V planes
     if ((long long)2 * pv.H * pv.n_pages * pv.P >= (1ll << 31)) return false;
     return encode_fn() != nullptr;
@@ -851,25 +948,35 @@ int launch_decode_tma(const PoolView& pv, int layer, void* out, float* lse, cons
 {
     if (B == 0) return FPKV_OK;
     const int nrep = Hq / pv.H;
-    // One layer's K and V planes as a 3-D tensor: (64 elements = 128 bytes, token rows, head_dim/64).
-    CUtensorMap map;
-    const cuuint64_t dims[3] = {64, (cuuint64_t)2 * pv.H * pv.n_pages * pv.P, (cuuint64_t)(pv.D / 64)};
-    const cuuint64_t strides[2] = {(cuuint64_t)pv.D * 2, 128};
-    const cuuint32_t box[3] = {64, (cuuint32_t)pv.P, (cuuint32_t)(pv.D / 64)};
-    const cuuint32_t estr[3] = {1, 1, 1};
     const CUtensorMapDataType dt = pv.dtype == FPKV_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
-    if (encode_fn()(&map, dt, 3, pv.plane(layer, 0, 0), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
-                    CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
-                    CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
-        return FPKV_ELAUNCH;
-
-    // the same tensor with a box of one consumer warp's rows (page_size / 8) of one 64-element column group
-    CUtensorMap map_rows;
-    const cuuint32_t box_rows[3] = {64, (cuuint32_t)(pv.P / kConsumerWarps), 1};
-    if (encode_fn()(&map_rows, dt, 3, pv.plane(layer, 0, 0), dims, strides, box_rows, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
-                    CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
-                    CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
-        return FPKV_ELAUNCH;
+    // A tensor of `rows` token rows of `halves` 64-element column groups (row pitch halves * 128 bytes), seen through a
+    // box of `box_rows` rows and `box_halves` column groups, 128-byte swizzle.
+    auto encode = [&](CUtensorMap* m, void* base, unsigned long long rows, int halves, int box_rows, int box_halves) {
+        const cuuint64_t dims[3] = {64, (cuuint64_t)rows, (cuuint64_t)halves};
+        const cuuint64_t strides[2] = {(cuuint64_t)halves * 128, 128};
+        const cuuint32_t box[3] = {64, (cuuint32_t)box_rows, (cuuint32_t)box_halves};
+        const cuuint32_t estr[3] = {1, 1, 1};
+        return encode_fn()(m, dt, 3, base, dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                           CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+    };
+    const unsigned long long R = (unsigned long long)pv.n_pages * pv.P;
+    const int RWh = pv.P / kConsumerWarps;             // rows of one consumer warp
+    TileMaps maps;
+    memset(&maps, 0, sizeof(maps));
+    bool ok;
+    if (!pv.split_hq) {
+        // one layer's K and V planes as one tensor: a page box, and a box of one warp's rows of one column group
+        ok = encode(&maps.kv, pv.plane(layer, 0, 0), 2ull * pv.H * R, pv.D / 64, pv.P, pv.D / 64) &&
+             encode(&maps.kv_rows, pv.plane(layer, 0, 0), 2ull * pv.H * R, pv.D / 64, RWh, 1);
+    } else {
+        ok = encode(&maps.kt, pv.kt_plane(layer, 0), (unsigned long long)pv.H * R, 1, pv.P, 1) &&
+             encode(&maps.kt_rows, pv.kt_plane(layer, 0), (unsigned long long)pv.H * R, 1, RWh, 1) &&
+             encode(&maps.khw, pv.khw_plane(layer, 0), (unsigned long long)pv.split_hq * R, 1, pv.P, 1) &&
+             encode(&maps.khw_rows, pv.khw_plane(layer, 0), (unsigned long long)pv.split_hq * R, 1, RWh, 1) &&
+             encode(&maps.v, pv.v_plane(layer, 0), (unsigned long long)pv.H * R, 2, pv.P, 2) &&
+             encode(&maps.v_rows, pv.v_plane(layer, 0), (unsigned long long)pv.H * R, 2, RWh, 1);
+    }
+    if (!ok) return FPKV_ELAUNCH;
 
     const int G = sm_count() < kMaxGrid ? sm_count() : kMaxGrid;
     const size_t esz = 2;
@@ -894,11 +1001,11 @@ int launch_decode_tma(const PoolView& pv, int layer, void* out, float* lse, cons
         prm.epi = epi;
         int rc;
         if (pv.dtype == FPKV_BF16)
-            rc = pos_type == FPKV_I32 ? launch_shape<__nv_bfloat16, int32_t>(pv.D, nrep, map, map_rows, prm, G, stream)
-                                      : launch_shape<__nv_bfloat16, int64_t>(pv.D, nrep, map, map_rows, prm, G, stream);
+            rc = pos_type == FPKV_I32 ? launch_shape<__nv_bfloat16, int32_t>(pv.D, nrep, pv.split_hq != 0, maps, prm, G, stream)
+                                      : launch_shape<__nv_bfloat16, int64_t>(pv.D, nrep, pv.split_hq != 0, maps, prm, G, stream);
         else
-            rc = pos_type == FPKV_I32 ? launch_shape<__half, int32_t>(pv.D, nrep, map, map_rows, prm, G, stream)
-                                      : launch_shape<__half, int64_t>(pv.D, nrep, map, map_rows, prm, G, stream);
+            rc = pos_type == FPKV_I32 ? launch_shape<__half, int32_t>(pv.D, nrep, pv.split_hq != 0, maps, prm, G, stream)
+                                      : launch_shape<__half, int64_t>(pv.D, nrep, pv.split_hq != 0, maps, prm, G, stream);
         if (rc != FPKV_OK) return rc;
     }
     return FPKV_OK;

@@ -54,6 +54,7 @@
 // flight are drained (bounded), TMEM is freed and the kernel returns.
 
 #include <cuda.h>
+#include <string.h>
 #include <type_traits>
 #include "common.cuh"
 
@@ -286,6 +287,8 @@ struct PrefillParams {
     int rows_per_plane;         // n_pages * page_size
     float scale_log2;
     int heads_per_item;         // 2: both query heads of a GQA pair share the staged K/V tiles; 1 otherwise
+    int split;                  // split pool layout: kv_map covers the first K halves, khw_map the second halves (per query
+                                // head), v_map the values; an item is then a single query head (its K tile is its own)
     int n_qtiles, n_pairs, n_items;
     Epilogue epi;
 };
@@ -351,6 +354,7 @@ __device__ __forceinline__ float max64(const uint32_t (&sv)[2][32], int valid_co
 template <typename T>
 __global__ void __launch_bounds__(kPrefillThreads, 1)
 prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constant__ CUtensorMap kv_map,
+                  const __grid_constant__ CUtensorMap khw_map, const __grid_constant__ CUtensorMap v_map,
                   const PrefillParams prm)
 {
     extern __shared__ uint8_t smem_raw[];
@@ -504,7 +508,13 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_consta
                             const uint32_t g = gk + jk, st = g % kStages;
                             if (bar_try(k_empty0 + 8 * st, ((g / kStages) & 1u) ^ 1u)) {
                                 bar_expect_tx(k_full0 + 8 * st, kTileBytes);
-                                tma_3d(s32(k_s + st * kTileBytes), &kv_map, 0, d->page_row[jk], 0, k_full0 + 8 * st);
+                                if (!prm.split) {
+                                    tma_3d(s32(k_s + st * kTileBytes), &kv_map, 0, d->page_row[jk], 0, k_full0 + 8 * st);
+                                } else {                   // shared first half and this query head's second half, side by side
+                                    tma_3d(s32(k_s + st * kTileBytes), &kv_map, 0, d->page_row[jk], 0, k_full0 + 8 * st);
+                                    tma_3d(s32(k_s + st * kTileBytes + kHalfBytes), &khw_map, 0,
+                                           d->page_row[jk] + (d->hq0 - d->hq0 / n_rep) * prm.rows_per_plane, 0, k_full0 + 8 * st);
+                                }
                                 k_requested = g + 1; ++jk; progress = true;
                             }
                         }
@@ -512,7 +522,8 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_consta
                             const uint32_t g = gk + jv, st = g % kStages;
                             if (bar_try(v_empty0 + 8 * st, ((g / kStages) & 1u) ^ 1u)) {
                                 bar_expect_tx(v_full0 + 8 * st, kTileBytes);
-                                tma_3d(s32(v_s + st * kTileBytes), &kv_map, 0, d->page_row[jv] + prm.Hkv * prm.rows_per_plane, 0, v_full0 + 8 * st);
+                                if (!prm.split) tma_3d(s32(v_s + st * kTileBytes), &kv_map, 0, d->page_row[jv] + prm.Hkv * prm.rows_per_plane, 0, v_full0 + 8 * st);
+                                else tma_3d(s32(v_s + st * kTileBytes), &v_map, 0, d->page_row[jv], 0, v_full0 + 8 * st);
                                 v_requested = g + 1; ++jv; progress = true;
                             }
                         }
@@ -806,7 +817,7 @@ constexpr int kPrefillSmem = 1024 + (2 + 2 * kStages) * kTileBytes + 48 * 8 + 16
 
 bool prefill_tc_supported(const PoolView& pv, int Hq)
 {
-    if (pv.split_hq) return false;
+    if (pv.split_hq && Hq != pv.split_hq) return false;
     if (pv.dtype != FPKV_BF16 && pv.dtype != FPKV_F16) return false;
     if (pv.P != kPage || pv.D != kHeadDim) return false;
     if (Hq % pv.H) return false;
@@ -821,15 +832,24 @@ int launch_prefill_tc(const PoolView& pv, int layer, void* out, float* lse, cons
 {
     if (L == 0) return FPKV_OK;
     const CUtensorMapDataType dt = pv.dtype == FPKV_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
-    CUtensorMap kv_map, q_map;
-    {   // one layer's K and V planes: (64 elements, token rows, head_dim / 64)
-        const cuuint64_t dims[3] = {64, (cuuint64_t)2 * pv.H * pv.n_pages * pv.P, (cuuint64_t)(pv.D / 64)};
-        const cuuint64_t strides[2] = {(cuuint64_t)pv.D * 2, 128};
-        const cuuint32_t box[3] = {64, (cuuint32_t)kPage, (cuuint32_t)(pv.D / 64)};
+    CUtensorMap kv_map, khw_map, v_map, q_map;
+    memset(&khw_map, 0, sizeof(khw_map)); memset(&v_map, 0, sizeof(v_map));
+    // a tensor of `rows` token rows of `halves` 64-element column groups, seen through a box of one page
+    auto encode_pages = [&](CUtensorMap* m, void* base, unsigned long long rows, int halves) {
+        const cuuint64_t dims[3] = {64, (cuuint64_t)rows, (cuuint64_t)halves};
+        const cuuint64_t strides[2] = {(cuuint64_t)halves * 128, 128};
+        const cuuint32_t box[3] = {64, (cuuint32_t)kPage, (cuuint32_t)halves};
         const cuuint32_t es[3] = {1, 1, 1};
-        if (encoder()(&kv_map, dt, 3, pv.plane(layer, 0, 0), dims, strides, box, es, CU_TENSOR_MAP_INTERLEAVE_NONE,
-                      CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
-                      CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
+        return encoder()(m, dt, 3, base, dims, strides, box, es, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                         CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+    };
+    const unsigned long long R = (unsigned long long)pv.n_pages * pv.P;
+    if (!pv.split_hq) {     // one layer's K and V planes as one tensor
+        if (!encode_pages(&kv_map, pv.plane(layer, 0, 0), 2ull * pv.H * R, pv.D / 64)) return FPKV_ELAUNCH;
+    } else {                // first K halves (per KV head), second K halves (per query head), values (per KV head)
+        if (!encode_pages(&kv_map, pv.kt_plane(layer, 0), (unsigned long long)pv.H * R, 1) ||
+            !encode_pages(&khw_map, pv.khw_plane(layer, 0), (unsigned long long)pv.split_hq * R, 1) ||
+            !encode_pages(&v_map, pv.v_plane(layer, 0), (unsigned long long)pv.H * R, 2))
             return FPKV_ELAUNCH;
     }
     {   // queries: (64 elements, L tokens, head_dim / 64, Hq heads); rows past L read as zeros
@@ -848,7 +868,8 @@ int launch_prefill_tc(const PoolView& pv, int layer, void* out, float* lse, cons
     prm.L = L; prm.Hq = Hq; prm.Hkv = pv.H; prm.n_pages = pv.n_pages; prm.max_batch = pv.max_batch;
     prm.rows_per_plane = pv.n_pages * pv.P;
     prm.scale_log2 = sm_scale * kLog2e;
-    prm.heads_per_item = ((Hq / pv.H) % 2 == 0) ? 2 : 1;
+    prm.split = pv.split_hq ? 1 : 0;
+    prm.heads_per_item = (!prm.split && (Hq / pv.H) % 2 == 0) ? 2 : 1;
     prm.n_qtiles = (L + kTileM - 1) / kTileM;
     prm.n_pairs = Hq / prm.heads_per_item;
     const long long n_items = (long long)prm.n_qtiles * prm.n_pairs;
@@ -859,11 +880,11 @@ int launch_prefill_tc(const PoolView& pv, int layer, void* out, float* lse, cons
     if (pv.dtype == FPKV_BF16) {
         auto kern = prefill_tc_kernel<__nv_bfloat16>;
         if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, kPrefillSmem) != cudaSuccess) return FPKV_ELAUNCH;
-        kern<<<grid, kPrefillThreads, kPrefillSmem, stream>>>(q_map, kv_map, prm);
+        kern<<<grid, kPrefillThreads, kPrefillSmem, stream>>>(q_map, kv_map, khw_map, v_map, prm);
     } else {
         auto kern = prefill_tc_kernel<__half>;
         if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, kPrefillSmem) != cudaSuccess) return FPKV_ELAUNCH;
-        kern<<<grid, kPrefillThreads, kPrefillSmem, stream>>>(q_map, kv_map, prm);
+        kern<<<grid, kPrefillThreads, kPrefillSmem, stream>>>(q_map, kv_map, khw_map, v_map, prm);
     }
     return cudaGetLastError() == cudaSuccess ? FPKV_OK : FPKV_ELAUNCH;
 }

@@ -112,6 +112,8 @@ def test_split_pool_holds_the_expanded_cache_and_attends_like_it(dtype, D, Hq, H
     # decode attention over the split pool = the oracle's attention over the expanded cache
     ref_out, ref_lse = orc.decode_attention(o, 0, q.float(), bidx, pos)
     kernels = [_lib.DECODE_PORTABLE] + ([_lib.DECODE_AUTO] if dtype != torch.float32 else [])
+    if dtype == torch.bfloat16 and D == 128:
+        kernels.append(_lib.DECODE_TMA)             # asked for by name: an unsupported shape would be refused, not rerouted
     for kern in kernels:
         c.decode_kernel = kern
         out, lse = paged_attention(q.cuda(), c, 0, bidx.cuda(), pos.cuda())
@@ -119,7 +121,7 @@ def test_split_pool_holds_the_expanded_cache_and_attends_like_it(dtype, D, Hq, H
     c.check_status()
 
 
-@pytest.mark.parametrize("kernel", [_lib.PREFILL_PORTABLE, _lib.PREFILL_AUTO])
+@pytest.mark.parametrize("kernel", [_lib.PREFILL_PORTABLE, _lib.PREFILL_AUTO, _lib.PREFILL_TC])
 def test_split_pool_prefill(kernel):
     """Packed prefill with an image span over a split pool against the oracle's attention over the expanded K, V."""
     T = wl.image_text_tokens
@@ -145,6 +147,37 @@ def test_split_pool_prefill(kernel):
     live = case.seq_index.view(-1) > 0
     assert_attention_close(out[0][:, live], lse[0][:, live], torch.as_tensor(ref_out)[0][:, live],
                            torch.as_tensor(ref_lse)[0][:, live], f"split prefill, kernel {kernel}")
+    c.check_status()
+
+
+@pytest.mark.parametrize("Hq,Hkv", [(16, 8), (8, 2)])
+def test_split_pool_long_contexts_on_the_tiled_decode_kernel(Hq, Hkv):
+    """Contexts of many pages (several work units per sequence, partial last groups) on the TMA decode kernel over a
+    split pool, against the oracle's attention over the reference's expanded cache."""
+    P, D, dtype = 128, 128, torch.bfloat16
+    lens = [4097, 2500, 1023, 3333, 640, 2049, 129, 3967]
+    n_pages = sum((n + 1 + P - 1) // P for n in lens) + 3
+    hist, (k_new, v_new), q = _expanded_inputs(29, lens, Hq, Hkv, D, dtype)
+    c = PagedKVCache(n_pages, P, len(lens) + 1, Hkv, D, 1, dtype, "cuda", split_q_heads=Hq)
+    o = orc.OraclePagedKVCache(n_pages, P, len(lens) + 1, Hq, D, 1, dtype)
+    perm = (np.random.default_rng(5).permutation(n_pages - 1) + 1).tolist()
+    c.free_pages = list(perm); o.free_pages = list(perm)
+    slots = []
+    for n, (kh, vh) in zip(lens, hist):
+        s = c.allocate(); assert o.allocate() == s; slots.append(s)
+        c.reserve(s, None, n + 1); o.reserve(s, n + 1)
+        kk, vv = kh.permute(1, 0, 2).unsqueeze(0), vh.permute(1, 0, 2).unsqueeze(0)
+        ip, bi = torch.arange(n).view(1, n), torch.full((1, n), s)
+        c.insert_kv(0, kk.cuda(), vv.cuda(), input_pos=ip.cuda(), batch_idx=bi.cuda())
+        o.append_packed(0, bi, ip, kk, vv)
+    bidx = torch.tensor(slots); pos = torch.tensor(lens, dtype=torch.int32)
+    kd, vd = k_new.unsqueeze(2), v_new.unsqueeze(2)
+    c.insert_kv(0, kd.cuda(), vd.cuda(), input_pos=pos.cuda().view(-1, 1), batch_idx=bidx.cuda())
+    o.append_decode(0, bidx, pos, kd, vd)
+    ref_out, ref_lse = orc.decode_attention(o, 0, q.float(), bidx, pos)
+    c.decode_kernel = _lib.DECODE_TMA
+    out, lse = paged_attention(q.cuda(), c, 0, bidx.cuda(), pos.cuda())
+    assert_attention_close(out, lse, ref_out, ref_lse, "split decode, long contexts")
     c.check_status()
 
 
