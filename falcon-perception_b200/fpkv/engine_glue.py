@@ -59,7 +59,8 @@ def fpkv_attention_forward(self, x, attention_masks, kv_cache, freqs_cis, freqs_
     come out of the attention kernel, and ``wo`` consumes that directly.
     fused=False: the reference's own ``_pre_attention`` / ``_post_attention``
     around ``insert_kv`` and the paged attention entry (K/V heads sliced back
-    to one copy per group when the pool stores the KV heads)."""
+    to one copy per group when the pool stores the KV heads; a split pool takes
+    the expanded K and V as they are)."""
     del flex_attn_kernel_options
     B, S, _ = x.shape
     n_q, n_kv, D = self.n_kv_heads * self.n_rep, self.n_kv_heads, self.head_dim
@@ -74,7 +75,7 @@ def fpkv_attention_forward(self, x, attention_masks, kv_cache, freqs_cis, freqs_
                                                 sinks=self.sinks, token_major=True)
         return self.wo(out.reshape(B, S, n_q * D))
     xq, xk, xv = self._pre_attention(x, freqs_cis, freqs_cis_2d)
-    if kv_cache.n_heads == n_kv and self.n_rep > 1:            # the pool stores each KV head once: drop the expanded copies
+    if kv_cache.n_heads == n_kv and self.n_rep > 1 and not kv_cache.split_q_heads:   # each KV head stored once: drop the copies
         xk, xv = xk[:, ::self.n_rep], xv[:, ::self.n_rep]
     if decode:
         out, lse = kv_cache.decode_step(self.layer_id, xq, xk, xv, batch_idx, input_pos)

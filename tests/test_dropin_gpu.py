@@ -123,9 +123,9 @@ def run_reference(ref, model, args, dtype, n_steps):
     return out
 
 
-def run_fpkv(ref, model, args, dtype, n_steps, stored_heads, forced_tokens):
+def run_fpkv(ref, model, args, dtype, n_steps, stored_heads, forced_tokens, split_q_heads=None):
     ids, pos, doc, rhw, offsets, lens = (x.cuda() if torch.is_tensor(x) else x for x in packed_prompts())
-    cache = PagedKVCache(16, 128, 4, stored_heads, args.head_dim, args.n_layers, dtype, "cuda")
+    cache = PagedKVCache(16, 128, 4, stored_heads, args.head_dim, args.n_layers, dtype, "cuda", split_q_heads=split_q_heads)
     slots = [cache.allocate() for _ in lens]
     for s, n in zip(slots, lens):
         cache.reserve(s, None, n + n_steps + 1)
@@ -157,6 +157,9 @@ def run_fpkv(ref, model, args, dtype, n_steps, stored_heads, forced_tokens):
     (torch.bfloat16, False, "kv", True, 6e-2),       # compact pool, every step fused: the fast kernels
     (torch.bfloat16, False, "kv", False, 6e-2),      # compact pool, the reference's own pre/post attention around the calls
     (torch.bfloat16, True, "q", True, 6e-2),         # per-query-head 2-D frequencies: the reference's expanded layout
+    (torch.bfloat16, True, "split", True, 6e-2),     # the same frequencies on the split pool (5/8 of the expanded bytes), fused
+    (torch.bfloat16, True, "split", False, 6e-2),    # ... and with the reference's own pre/post attention around the calls
+    (torch.float32, True, "split", False, 2e-3),
     (torch.float32, True, "q", False, 2e-3),         # fp32 end to end (portable kernels): tight
     (torch.float32, False, "kv", True, 2e-3),
 ])
@@ -167,7 +170,8 @@ def test_reference_model_with_fpkv_cache(ref, dtype, golden_per_head, stored, fu
     forced = [w.argmax(-1) for w in want]
     original = install_attention(ref.model.Attention, fused=fused)
     try:
-        got = run_fpkv(ref, model, args, dtype, n_steps, args.n_kv_heads if stored == "kv" else args.n_heads, forced)
+        got = run_fpkv(ref, model, args, dtype, n_steps, args.n_heads if stored == "q" else args.n_kv_heads, forced,
+                       split_q_heads=args.n_heads if stored == "split" else None)
     finally:
         ref.model.Attention.forward = original
     same, decided = 0, 0
