@@ -821,7 +821,7 @@ def bench_stack(rk, args, steps=64):
     }
 
 
-def bench_split_layout(rk, args, n_pages=8192):
+def bench_split_layout(rk, args, n_pages=4096):
     """Config 2's decode step over a split pool (first half of K and V once per KV head, second half of K once per
     query head): the layout that is exact under per-query-head 2-D rotary, at 5/8 of the bytes of the expanded
     cache the reference keeps for that case.  Reports the step, the attention call alone, and its rate on the bytes
