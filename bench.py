@@ -868,7 +868,11 @@ def bench_split_layout(rk, args, n_pages=4096):
             "metric": "split_layout_decode_attention_bandwidth", "value": round(gbs, 1), "unit": "GB/s",
             "bytes_per_key_and_kv_group": per_key // HKV, "expanded_cache_bytes_per_key_and_kv_group": 2 * (HQ // HKV) * D * 2,
             "attn_ms": round(t_attn / K, 4), "step_ms": round(t_step / K, 4), "steps": K, "blocks": R,
-            "frac_of_hbm_peak": round(gbs / (hbm_peak * rk.world), 3), "peak": which,
+            "roofline": {"bound": "hbm", "kernel": "decode_tma_kernel (split instantiation) + decode_tma_finish_kernel, timed alone",
+                         "achieved": round(gbs, 1), "peak": hbm_peak * rk.world, "unit": "GB/s",
+                         "frac": round(gbs / (hbm_peak * rk.world), 3), "peak_source": which,
+                         "traffic": 1.4807e9, "traffic_source": "ncu capture of one launch of this workload; not observed by this run",
+                         "bytes_per_launch": work / K / rk.world, "ms_per_launch": round(t_attn / K, 4)},
             "expanded_equivalent_gbs": round(gbs * (2 * HQ * D * 2) / per_key, 1),
             "gpu_launches_per_step": 3}
 
