@@ -78,8 +78,8 @@ def _expanded_inputs(seed, lens, Hq, Hkv, D, dtype, scale=1.0):
     return hist, new, q
 
 
-@pytest.mark.parametrize("dtype,D,Hq,Hkv", [(torch.bfloat16, 128, 16, 8), (torch.bfloat16, 128, 8, 2), (torch.float16, 64, 4, 2),
-                                            (torch.float32, 64, 4, 2)])
+@pytest.mark.parametrize("dtype,D,Hq,Hkv", [(torch.bfloat16, 128, 16, 8), (torch.bfloat16, 128, 8, 2), (torch.float16, 128, 4, 2),
+                                            (torch.float16, 64, 4, 2), (torch.float32, 64, 4, 2)])
 def test_split_pool_holds_the_expanded_cache_and_attends_like_it(dtype, D, Hq, Hkv):
     P, n_pages = 128, 40
     lens = [1, 127, 128, 300, 515, 700]
@@ -112,7 +112,7 @@ def test_split_pool_holds_the_expanded_cache_and_attends_like_it(dtype, D, Hq, H
     # decode attention over the split pool = the oracle's attention over the expanded cache
     ref_out, ref_lse = orc.decode_attention(o, 0, q.float(), bidx, pos)
     kernels = [_lib.DECODE_PORTABLE] + ([_lib.DECODE_AUTO] if dtype != torch.float32 else [])
-    if dtype == torch.bfloat16 and D == 128:
+    if dtype != torch.float32 and D == 128:
         kernels.append(_lib.DECODE_TMA)             # asked for by name: an unsupported shape would be refused, not rerouted
     for kern in kernels:
         c.decode_kernel = kern
@@ -121,11 +121,12 @@ def test_split_pool_holds_the_expanded_cache_and_attends_like_it(dtype, D, Hq, H
     c.check_status()
 
 
+@pytest.mark.parametrize("Hq,Hkv", [(8, 4), (8, 2), (6, 2)])
 @pytest.mark.parametrize("kernel", [_lib.PREFILL_PORTABLE, _lib.PREFILL_AUTO, _lib.PREFILL_TC])
-def test_split_pool_prefill(kernel):
+def test_split_pool_prefill(kernel, Hq, Hkv):
     """Packed prefill with an image span over a split pool against the oracle's attention over the expanded K, V."""
     T = wl.image_text_tokens
-    Hq, Hkv, D = 8, 4, 128
+    D = 128
     n_rep = Hq // Hkv
     case = wl.make_prefill_case(81, [T(3, 150, 40), T(0, 0, 200)], Hq=Hq, Hkv=Hkv, D=D, dtype=torch.bfloat16)
     g = torch.Generator().manual_seed(5)
