@@ -1,6 +1,7 @@
 // Paged prefill / chunked-prefill attention on the 5th-generation tensor cores
 // (tcgen05.mma, accumulators in tensor memory) for 16-bit pools, page_size 128,
-// head_dim 128.
+// head_dim 128 or 64 (the comments speak of 128; with 64 the Q, K and V tiles are one 64-element column block of 16 KiB
+// instead of two, Q.K^T has four K = 16 steps instead of eight, and O is 64 columns wide).
 //
 // Mask.  The reference's prefill mask (falcon_perception/paged_attention.py:343-362,
 // falcon_perception/attention.py:75-96) lets query t see key u of the same
@@ -61,8 +62,8 @@
 namespace fpkv {
 namespace {
 
-constexpr int kTileM = 128, kTileN = 128, kHeadDim = 128, kPage = 128;
-constexpr int kTileBytes = 128 * 128 * 2;              // any 128 x 128 16-bit tile
+constexpr int kTileM = 128, kTileN = 128, kPage = 128;
+constexpr int kTileBytes = 128 * 128 * 2;              // a 128 x 128 16-bit tile: the size of every tile buffer (head_dim 64 fills half)
 constexpr int kHalfBytes = kTileBytes / 2;             // 64 columns (128 bytes) x 128 rows
 constexpr int kStages = 2;
 constexpr int kSoftmaxWarps = 4;                       // per head: warps 0-3 are head 0's softmax group, warps 4-7 head 1's
@@ -265,10 +266,10 @@ __device__ __forceinline__ void issue_pv_half(uint32_t d, uint32_t a, uint32_t b
         umma_ts(d, a + k * 8, b_lo + (kHalf * 4 + k) * ((16 * 128) >> 4), hi, idesc, k > 0 ? 1u : acc_first);
 }
 // S half = Q K^T over 64 keys (N = 64): the K tile's rows [64 * kHalf, +64), i.e. 8 KiB into each 64-element column block.
-template <int kHalf>
+template <int kHalf, int D>
 __device__ __forceinline__ void issue_qk_half(uint32_t d, uint32_t a_lo, uint32_t b_lo, uint32_t hi, uint32_t idesc, uint32_t bar) {
 #pragma unroll
-    for (int k = 0; k < kHeadDim / 16; ++k) {
+    for (int k = 0; k < D / 16; ++k) {
         const uint32_t off = ((k >> 2) * kHalfBytes + (k & 3) * 32) >> 4;
         umma(d, a_lo + off, hi, b_lo + off + ((kHalf * 64 * 128) >> 4), hi, idesc, k > 0);
     }
@@ -351,7 +352,7 @@ __device__ __forceinline__ float max64(const uint32_t (&sv)[2][32], int valid_co
     return mx;
 }
 
-template <typename T>
+template <typename T, int D>
 __global__ void __launch_bounds__(kPrefillThreads, 1)
 prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constant__ CUtensorMap kv_map,
                   const __grid_constant__ CUtensorMap khw_map, const __grid_constant__ CUtensorMap v_map,
@@ -380,6 +381,7 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_consta
     const uint32_t drain0 = s_half0 + 112;                                             // [2] give-up path: a head's MMAs have completed
 
     const int tid = threadIdx.x, warp = tid / 32, lane = tid % 32;
+    constexpr int kTileBytesD = kTileM * D * 2;            // bytes a Q, K or V tile really holds
     const int heads = prm.heads_per_item;                  // 1 or 2 query heads of one stored head
     const int n_rep = prm.Hq / prm.Hkv;
 
@@ -493,7 +495,7 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_consta
                 if (n > 0) {
                     for (int h = 0; h < heads && alive; ++h) {           // the head's query buffer is free once its last Q.K^T is through
                         if (!bar_wait(q_empty0 + 8 * h, (wit & 1u) ^ 1u, abort_flag)) { alive = false; break; }
-                        bar_expect_tx(q_full0 + 8 * h, kTileBytes);
+                        bar_expect_tx(q_full0 + 8 * h, kTileBytesD);
                         tma_4d(s32(q_s + h * kTileBytes), &q_map, 0, d->t0, 0, d->hq0 + h, q_full0 + 8 * h);
                         q_requested[h] = wit + 1;
                     }
@@ -507,7 +509,7 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_consta
                         if (jk < n) {
                             const uint32_t g = gk + jk, st = g % kStages;
                             if (bar_try(k_empty0 + 8 * st, ((g / kStages) & 1u) ^ 1u)) {
-                                bar_expect_tx(k_full0 + 8 * st, kTileBytes);
+                                bar_expect_tx(k_full0 + 8 * st, kTileBytesD);
                                 if (!prm.split) {
                                     tma_3d(s32(k_s + st * kTileBytes), &kv_map, 0, d->page_row[jk], 0, k_full0 + 8 * st);
                                 } else {                   // shared first half and this query head's second half, side by side
@@ -521,7 +523,7 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_consta
                         if (jv < n) {
                             const uint32_t g = gk + jv, st = g % kStages;
                             if (bar_try(v_empty0 + 8 * st, ((g / kStages) & 1u) ^ 1u)) {
-                                bar_expect_tx(v_full0 + 8 * st, kTileBytes);
+                                bar_expect_tx(v_full0 + 8 * st, kTileBytesD);
                                 if (!prm.split) tma_3d(s32(v_s + st * kTileBytes), &kv_map, 0, d->page_row[jv] + prm.Hkv * prm.rows_per_plane, 0, v_full0 + 8 * st);
                                 else tma_3d(s32(v_s + st * kTileBytes), &v_map, 0, d->page_row[jv], 0, v_full0 + 8 * st);
                                 v_requested = g + 1; ++jv; progress = true;
@@ -546,7 +548,7 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_consta
         if (lane == 0) {
             const bool is_bf16 = std::is_same<T, __nv_bfloat16>::value;
             const uint32_t idesc_qk = umma_idesc(is_bf16, false, 64);
-            const uint32_t idesc_pv = umma_idesc(is_bf16, true);
+            const uint32_t idesc_pv = umma_idesc(is_bf16, true, D);
             // descriptor words: low = start address >> 4 (| LBO for MN-major), high = SBO 1024 | version | 128-byte swizzle
             const uint32_t desc_hi = (uint32_t)(umma_desc(0, 0, 1024) >> 32);
             const uint32_t q_lo = ((s32(q_s) & 0x3FFFF) >> 4) + g * (kTileBytes >> 4), k_lo = (s32(k_s) & 0x3FFFF) >> 4;
@@ -567,8 +569,8 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_consta
                             bar_wait(k_full0 + 8 * st0, (gk / kStages) & 1u, abort_flag);
                     if (!alive) break;
                     tc_fence_after();
-                    issue_qk_half<0>(t_s, q_lo, k_lo + st0 * (kTileBytes >> 4), desc_hi, idesc_qk, s_lo);
-                    issue_qk_half<1>(t_s + 64, q_lo, k_lo + st0 * (kTileBytes >> 4), desc_hi, idesc_qk, s_hi);
+                    issue_qk_half<0, D>(t_s, q_lo, k_lo + st0 * (kTileBytes >> 4), desc_hi, idesc_qk, s_lo);
+                    issue_qk_half<1, D>(t_s + 64, q_lo, k_lo + st0 * (kTileBytes >> 4), desc_hi, idesc_qk, s_hi);
                     umma_commit(k_empty0 + 8 * st0);
                     if (n == 1) umma_commit(q_empty0 + 8 * g);
                     for (int j = 0; j < n; ++j) {
@@ -585,7 +587,7 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_consta
                         tc_fence_after();
                         issue_pv_half<0>(t_o, t_s, v_lo + st * (kTileBytes >> 4), desc_hi, idesc_pv, j > 0);
                         umma_commit(pv_done);
-                        if (j + 1 < n) issue_qk_half<0>(t_s, q_lo, k_lo + sn * (kTileBytes >> 4), desc_hi, idesc_qk, s_lo);
+                        if (j + 1 < n) issue_qk_half<0, D>(t_s, q_lo, k_lo + sn * (kTileBytes >> 4), desc_hi, idesc_qk, s_lo);
                         // keys 64-127
                         if (!bar_wait(p_hi, th & 1u, abort_flag)) { alive = false; break; }
                         tc_fence_after();
@@ -594,7 +596,7 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_consta
                         umma_commit(v_empty0 + 8 * st);
                         ++th;
                         if (j + 1 < n) {
-                            issue_qk_half<1>(t_s + 64, q_lo, k_lo + sn * (kTileBytes >> 4), desc_hi, idesc_qk, s_hi);
+                            issue_qk_half<1, D>(t_s + 64, q_lo, k_lo + sn * (kTileBytes >> 4), desc_hi, idesc_qk, s_hi);
                             umma_commit(k_empty0 + 8 * sn);
                             if (j + 2 == n) umma_commit(q_empty0 + 8 * g);     // that was the item's last Q.K^T
                         }
@@ -652,8 +654,8 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_consta
                     const int tile_rows = page_ok ? min(kTileN, max_extent - j * kTileN) : 0;
                     const uint32_t cur = gk + j, st = cur % kStages;
                     if (!bar_wait(v_full0 + 8 * st, (cur / kStages) & 1u, abort_flag)) { alive = false; break; }
-                    for (int i = row; i < (kTileN - tile_rows) * 16; i += kSoftmaxWarps * 32) {
-                        const int r = tile_rows + (i >> 4), c = i & 15;         // token row, 16-byte piece of its 256 bytes
+                    for (int i = row; i < (kTileN - tile_rows) * (D / 8); i += kSoftmaxWarps * 32) {
+                        const int r = tile_rows + i / (D / 8), c = i % (D / 8);  // token row, 16-byte piece of its D * 2 bytes
                         *reinterpret_cast<uint4*>(v_s + st * kTileBytes + (c >> 3) * kHalfBytes + r * 128 + ((c & 7) << 4)) =
                             make_uint4(0u, 0u, 0u, 0u);
                     }
@@ -685,7 +687,7 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_consta
                             if (!bar_wait(pv_done, (unit - 1) & 1u, abort_flag)) { alive = false; break; }
                             tc_fence_after();
 #pragma unroll 1
-                            for (int c4 = 0; c4 < 4; ++c4) {
+                            for (int c4 = 0; c4 < D / 32; ++c4) {
                                 tmem_ld32(to + c4 * 32, pk);
 #pragma unroll
                                 for (int c = 0; c < 32; ++c) pk[c] = __float_as_uint(__uint_as_float(pk[c]) * alpha);
@@ -720,14 +722,14 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_consta
             const float lse_nat = l > 0.f ? (m_ref + log2f(l)) * kLn2 : -INFINITY;
             const bool gate_on = prm.epi.sinks != nullptr;
             const float gate = sink_gate(prm.epi, hq, lse_nat);
-            T* dst = out + (prm.epi.token_major ? ((size_t)tk * prm.Hq + hq) : ((size_t)hq * prm.L + tk)) * kHeadDim;
+            T* dst = out + (prm.epi.token_major ? ((size_t)tk * prm.Hq + hq) : ((size_t)hq * prm.L + tk)) * D;
 #pragma unroll 1
-            for (int c2 = 0; c2 < 2; ++c2) {
+            for (int c2 = 0; c2 < D / 64; ++c2) {
                 if (n > 0) {
                     tmem_ld32_nowait(to + c2 * 64, sv[0]);
                     tmem_ld32_nowait(to + c2 * 64 + 32, sv[1]);
                     tmem_wait_ld();
-                    if (c2 == 1) {                         // O is in registers: the next item's first P.V may overwrite it
+                    if (c2 == D / 64 - 1) {                // O is in registers: the next item's first P.V may overwrite it
                         tc_fence_before();
                         __syncwarp();
                         if (lane == 0) bar_arrive(o_free0 + 8 * h);
@@ -817,9 +819,9 @@ constexpr int kPrefillSmem = 1024 + (2 + 2 * kStages) * kTileBytes + 48 * 8 + 16
 
 bool prefill_tc_supported(const PoolView& pv, int Hq)
 {
-    if (pv.split_hq && Hq != pv.split_hq) return false;
+    if (pv.split_hq && (Hq != pv.split_hq || pv.D != 128)) return false;   // half rows of a split pool must fill a 128-byte swizzle row
     if (pv.dtype != FPKV_BF16 && pv.dtype != FPKV_F16) return false;
-    if (pv.P != kPage || pv.D != kHeadDim) return false;
+    if (pv.P != kPage || (pv.D != 128 && pv.D != 64)) return false;
     if (Hq % pv.H) return false;
     // TMA coordinates are 32-bit token rows within one layer's K and V planes (more rows than 180 GB can hold)
     if ((long long)2 * pv.H * pv.n_pages * pv.P >= (1ll << 31)) return false;
@@ -877,15 +879,15 @@ int launch_prefill_tc(const PoolView& pv, int layer, void* out, float* lse, cons
     prm.n_items = (int)n_items;
     prm.epi = epi;
     const int grid = prm.n_items < prefill_sm_count() ? prm.n_items : prefill_sm_count();    // persistent: one CTA per SM
-    if (pv.dtype == FPKV_BF16) {
-        auto kern = prefill_tc_kernel<__nv_bfloat16>;
-        if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, kPrefillSmem) != cudaSuccess) return FPKV_ELAUNCH;
+    auto launch = [&](auto kern) {
+        if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, kPrefillSmem) != cudaSuccess) return false;
         kern<<<grid, kPrefillThreads, kPrefillSmem, stream>>>(q_map, kv_map, khw_map, v_map, prm);
-    } else {
-        auto kern = prefill_tc_kernel<__half>;
-        if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, kPrefillSmem) != cudaSuccess) return FPKV_ELAUNCH;
-        kern<<<grid, kPrefillThreads, kPrefillSmem, stream>>>(q_map, kv_map, khw_map, v_map, prm);
-    }
+        return true;
+    };
+    bool ok;
+    if (pv.dtype == FPKV_BF16) ok = pv.D == 128 ? launch(prefill_tc_kernel<__nv_bfloat16, 128>) : launch(prefill_tc_kernel<__nv_bfloat16, 64>);
+    else ok = pv.D == 128 ? launch(prefill_tc_kernel<__half, 128>) : launch(prefill_tc_kernel<__half, 64>);
+    if (!ok) return FPKV_ELAUNCH;
     return cudaGetLastError() == cudaSuccess ? FPKV_OK : FPKV_ELAUNCH;
 }
 

@@ -337,8 +337,9 @@ FPKV_API int fpkv_decode_attn(const fpkv_pool* pool, int32_t layer,
  * lse  device (1, n_q_heads, L) fp32 natural log; rows without a visible key
  *      give out = 0, lse = -inf.
  * flags: FPKV_PREFILL_AUTO runs the tcgen05 tensor-core kernel for 16-bit
- * pools with page_size 128 and head_dim 128 and a portable CUDA-core kernel
- * (any pool dtype, head_dim 64/128, any page size; not tuned) otherwise;
+ * pools with page_size 128 and head_dim 128 or 64 (a split pool: head_dim
+ * 128) and a portable CUDA-core kernel (any pool dtype, head_dim 64/128,
+ * any page size; not tuned) otherwise;
  * FPKV_PREFILL_PORTABLE / FPKV_PREFILL_TC force one (the latter returns
  * FPKV_ESHAPE outside its range).  Needs no workspace.
  */

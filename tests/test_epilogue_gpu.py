@@ -47,10 +47,11 @@ def test_decode_sink_gate(kernel):
     c.check_status()
 
 
+@pytest.mark.parametrize("D", [128, 64])
 @pytest.mark.parametrize("kernel", [_lib.PREFILL_TC, _lib.PREFILL_PORTABLE])
-def test_prefill_sink_gate_and_token_major_layout(kernel):
-    case = wl.make_prefill_case(707, [T(2, 200, 40), T(0, 0, 90)], Hq=16, Hkv=8, D=128, dtype=torch.bfloat16)
-    c = PagedKVCache(16, 128, 4, 8, 128, 1, torch.bfloat16, "cuda")
+def test_prefill_sink_gate_and_token_major_layout(kernel, D):
+    case = wl.make_prefill_case(707, [T(2, 200, 40), T(0, 0, 90)], Hq=16, Hkv=8, D=D, dtype=torch.bfloat16)
+    c = PagedKVCache(16, 128, 4, 8, D, 1, torch.bfloat16, "cuda")
     c.prefill_kernel = kernel
     slots = []
     for toks in case.seq_tokens:
@@ -62,7 +63,7 @@ def test_prefill_sink_gate_and_token_major_layout(kernel):
     sinks = (torch.randn(16) * 2).bfloat16().cuda()
     out, lse = paged_attention(q, c, 0, bidx, ipos, mask)
     gout, glse = c.prefill_attention(0, q, bidx, ipos, mask, sinks=sinks, token_major=True)
-    assert tuple(gout.shape) == (1, case.L, 16, 128) and torch.equal(lse, glse)
+    assert tuple(gout.shape) == (1, case.L, 16, D) and torch.equal(lse, glse)
     want = orc.post_attention_gate(out.cpu(), lse.cpu(), sinks.cpu())                 # (1, L, Hq*D)
     close_to_gated(gout.view(1, case.L, -1), want, "prefill gate, token-major")
     # layout alone, no gate: a pure permutation of the head-major result

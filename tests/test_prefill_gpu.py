@@ -50,9 +50,10 @@ def compare_live_rows(case, out, lse, ref_out, ref_lse, what):
 
 
 @pytest.mark.parametrize("name,kernel", [("prefill_img_d128", _lib.PREFILL_TC), ("prefill_img_d128", _lib.PREFILL_PORTABLE),
+                                         ("prefill_mixed_d64", _lib.PREFILL_TC), ("prefill_mixed_d64", _lib.PREFILL_PORTABLE),
                                          ("prefill_mixed_d64", _lib.PREFILL_AUTO)])
 def test_prefill_against_reference_golden(name, kernel):
-    """Both kernels against the reference's own output; head_dim 64 is served by the portable one."""
+    """Both kernels against the reference's own output, head_dim 128 and 64."""
     make, n_pages, mb = PREFILL_CASES[name]
     case = make()
     g = golden(name)
@@ -146,21 +147,25 @@ def test_random_prompt_layouts(seed):
         for _ in range(int(rng.integers(1, 4))):
             toks += T(int(rng.integers(0, 40)), int(rng.integers(0, 2)) * int(rng.integers(2, 400)), int(rng.integers(0, 150)))
         seqs.append(toks or T(0, 0, 1))
-    case = wl.make_prefill_case(900 + seed, seqs, Hq=8, Hkv=4, D=128, dtype=torch.bfloat16)
+    # odd seeds at head_dim 64 (fp16 for one of them), three query heads per stored head for another
+    D, Hq, Hkv = (64, 8, 4) if seed % 2 else ((128, 6, 2) if seed == 4 else (128, 8, 4))
+    dtype = torch.float16 if seed == 3 else torch.bfloat16
+    case = wl.make_prefill_case(900 + seed, seqs, Hq=Hq, Hkv=Hkv, D=D, dtype=dtype)
     n_pages = sum((len(s) + 127) // 128 for s in seqs) + 2
     for kernel in (_lib.PREFILL_TC, _lib.PREFILL_PORTABLE):
-        c, slots, bidx, ipos, mask, out, lse = run_product(case, n_pages, len(seqs) + 2, kernel=kernel)
-        ref_out, ref_lse = oracle_prefill(case, slots)
+        c, slots, bidx, ipos, mask, out, lse = run_product(case, n_pages, len(seqs) + 2, dtype=dtype, kernel=kernel)
+        ref_out, ref_lse = oracle_prefill(case, slots, dtype=dtype)
         compare_live_rows(case, out, lse, ref_out, ref_lse, f"random layout {seed}, kernel {kernel}")
         c.check_status()
 
 
+@pytest.mark.parametrize("D", [128, 64])
 @pytest.mark.parametrize("kernel", [_lib.PREFILL_TC, _lib.PREFILL_PORTABLE])
-def test_rows_never_appended_may_hold_anything(kernel):
+def test_rows_never_appended_may_hold_anything(kernel, D):
     """A pool that was not zero-filled: the tails of the sequences' last pages (fetched with the page) and
     reserved page 0 hold NaN bit patterns; no result is touched by them."""
     seqs = [T(0, 100, 30), T(0, 0, 129), T(3, 250, 1), T(0, 0, 5)]
-    case = wl.make_prefill_case(4141, seqs, Hq=8, Hkv=4, D=128, dtype=torch.bfloat16)
+    case = wl.make_prefill_case(4141, seqs, Hq=8, Hkv=4, D=D, dtype=torch.bfloat16)
     c, slots, bidx, ipos, mask, out, lse = run_product(case, 12, 6, kernel=kernel, poison=True)
     ref_out, ref_lse = oracle_prefill(case, slots)
     live = case.seq_index.view(-1) > 0
