@@ -1,6 +1,7 @@
 """Benchmark of the paged KV-cache hot path.
 
     python bench.py [--gpus N] [--steps K] [--warmup W] [--impl fpkv|reference] [--only PART]
+    python bench.py --impl engine --engine-cache reference|expanded|split|compact     (opt-in, for context)
 
 Headline workload (one "step" = one decode step of one layer over the whole
 batch): bf16, batch 64 per GPU, 16 query heads over 8 stored heads, head_dim
@@ -48,7 +49,9 @@ import sys
 import threading
 import time
 
-if "reference" in sys.argv:                        # the reference's compiled handles must run eagerly on the CPU;
+_impl = next((sys.argv[i + 1] for i, a in enumerate(sys.argv[:-1]) if a == "--impl"),
+             next((a.split("=", 1)[1] for a in sys.argv if a.startswith("--impl=")), "fpkv"))
+if _impl == "reference":                            # the reference's compiled handles must run eagerly on the CPU;
     os.environ.setdefault("TORCHDYNAMO_DISABLE", "1")   # the switch is read when torch is imported
 
 ROOT = os.path.dirname(os.path.abspath(__file__))
@@ -1138,6 +1141,95 @@ def run_reference_gpu(args):
                 "twice those bytes"}), flush=True)
 
 
+def run_engine(args):
+    """--impl engine (opt-in, N = 1, for context): the reference's own PagedInferenceEngine.generate on its
+    flagship-sized model (28 layers, 16 / 8 heads, head_dim 128, random weights, bf16) with its own cache and compiled
+    FlexAttention, or -- `--engine-cache split` / `compact` -- with fpkv.PagedKVCache substituted (the substitutions
+    of tests/test_engine_dropin_gpu.py).  64 requests of 8000 tokens; prefill is timed as a generate() that stops
+    after the first token, decode as the difference to one that goes on for 64 more.  One JSON line."""
+    import types
+    root = reference_root()
+    if root is None:
+        print(json.dumps({"impl": "engine", "unavailable": "the reference project is not installed under baseline/_ref"}))
+        return
+    assert torch.cuda.is_available()
+    sys.path.insert(0, root)
+    stub = types.ModuleType("pycocotools"); stub.mask = types.ModuleType("pycocotools.mask")
+    sys.modules.setdefault("pycocotools", stub); sys.modules.setdefault("pycocotools.mask", stub.mask)
+    import falcon_perception.model as ref_model
+    import falcon_perception.paged_inference as eng_mod
+    from falcon_perception import ModelArgs
+    which = args.engine_cache
+    n_seq, prompt, new = 64, 8000, 64
+
+    class Tok:                                               # what the engine and ModelArgs.update read; requests arrive tokenised
+        padding_side = "right"
+        pad_token_id, eos_token_id, bos_id = 0, 1, None
+        start_of_image_token_id, image_cls_token_id, end_of_image_token_id, image_token_id = 2, 3, 4, 5
+        image_row_sep_token_id = 7
+        image_reg_1_token_id, image_reg_2_token_id, image_reg_3_token_id, image_reg_4_token_id = 8, 9, 10, 11
+        seg_token_id, coord_token_id, size_token_id = 12, 13, 14
+    margs = ModelArgs(perception_heads=False, do_segmentation=False, max_seq_len=8192)
+    margs.update(Tok())
+    torch.manual_seed(1)
+    model = ref_model.FalconPerception(margs)
+    with torch.no_grad():
+        for name, prm in model.named_parameters():
+            if prm.dim() >= 2: prm.normal_(0, 0.02)
+            elif "norm" in name: prm.fill_(1.0)
+            else: prm.zero_()
+        for name, buf in model.named_buffers():
+            if buf.is_floating_point() and not torch.isfinite(buf).all(): buf.zero_()
+    model = model.to(device="cuda", dtype=torch.bfloat16).eval()
+    if which != "reference":
+        from fpkv.engine_glue import decoding_block_mask, install_attention
+        from fpkv.paged_attention import PagedKVCache
+
+        def fpkv_cache(**kw):
+            if which == "split": kw = dict(kw, n_heads=margs.n_kv_heads, split_q_heads=margs.n_heads)
+            if which == "compact": kw = dict(kw, n_heads=margs.n_kv_heads)
+            return PagedKVCache(**kw)
+        eng_mod.PagedKVCache = fpkv_cache
+        eng_mod.PagedInferenceEngine.get_decoding_block_mask = \
+            lambda self, batch_idx, input_pos: decoding_block_mask(self.block_mask, batch_idx, input_pos)
+        install_attention(ref_model.Attention, fused=True)
+    pages = n_seq * ((prompt + new + P - 1) // P + 1) + 8
+    t0 = time.perf_counter()
+    eng = eng_mod.PagedInferenceEngine(model, Tok(), None, max_batch_size=n_seq + 1, max_seq_length=8192, n_pages=pages,
+                                       seed=0, enable_hr_cache=False, capture_cudagraph=True, prefill_length_limit=32768)
+    ready_s = time.perf_counter() - t0
+
+    def requests():
+        gen = torch.Generator().manual_seed(3)
+        out = []
+        for i in range(n_seq):
+            r = eng_mod.Sequence(text="", image=None, request_idx=i, task="detection")
+            r.input_ids = torch.randint(20, 60000, (prompt,), generator=gen)
+            r.rope_pos_t = torch.arange(prompt, dtype=torch.long)
+            r.rope_pos_hw = torch.zeros(prompt, 2)
+            out.append(r)
+        return out
+
+    def timed(n_new):
+        sp = eng_mod.SamplingParams(max_new_tokens=n_new, stop_token_ids=[1])
+        torch.cuda.synchronize(); t = time.perf_counter()
+        done = eng.generate(requests(), sampling_params=sp)
+        torch.cuda.synchronize()
+        return time.perf_counter() - t, done
+    timed(2)                                                 # compilation and autotuning of whatever is compiled
+    t_pre = min(timed(1)[0] for _ in range(2))
+    t_all, done = timed(1 + new)
+    finite = all(bool(torch.isfinite(r.output_probs).all()) for r in done)
+    print(json.dumps({
+        "impl": "engine", "cache": which, "n_gpus": 1, "dtype": "bf16", "data": "synthetic",
+        "config": {"workload": f"the reference's PagedInferenceEngine.generate, 28-layer model (16 q / 8 kv heads, head_dim 128, "
+                               f"random weights), {n_seq} requests of {prompt} tokens, {new} decode steps, CUDA graphs"},
+        "engine_ready_s": round(ready_s, 1),
+        "prefill_ms": round(t_pre * 1e3, 1), "prefill_tokens_per_s": round(n_seq * prompt / t_pre),
+        "decode_ms_per_step": round((t_all - t_pre) / new * 1e3, 2), "decode_tokens_per_s": round(n_seq * new / (t_all - t_pre)),
+        "outputs_finite": finite, "first_tokens": [int(r.output_ids[0]) for r in done[:4]]}), flush=True)
+
+
 def run_reference(args):
     """--impl reference: the reference's own CPU implementation of the path on the host cores, same metric and
     workload string as the GPU arm.  Rank 0 alone runs it; its throughput does not depend on how many GPU
@@ -1178,7 +1270,9 @@ def main():
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=200)
     ap.add_argument("--warmup", type=int, default=20)
-    ap.add_argument("--impl", default="fpkv", choices=["fpkv", "reference", "reference-gpu"])
+    ap.add_argument("--impl", default="fpkv", choices=["fpkv", "reference", "reference-gpu", "engine"])
+    ap.add_argument("--engine-cache", default="split", choices=["reference", "expanded", "split", "compact"],
+                    help="--impl engine: the cache the reference's engine runs on (its own, or fpkv's in one of its layouts)")
     ap.add_argument("--pool-pages", type=int, default=N_PAGES,
                     help="pages in the pool (default 65536 = 32 GiB; profiling captures use a small pool)")
     ap.add_argument("--batch", type=int, default=BATCH, help="sequences per GPU (default 64: the headline workload)")
@@ -1194,6 +1288,8 @@ def main():
         run_reference(args)
     elif args.impl == "reference-gpu":
         run_reference_gpu(args)
+    elif args.impl == "engine":
+        run_engine(args)
     else:
         run_fpkv(args)
 
