@@ -410,7 +410,8 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_consta
     tc_fence_after();
     const uint32_t tmem = (uint32_t)*tmem_slot;
     // tensor memory: S/P of head 0 [0,128), S/P of head 1 [128,256), O of head 0 [256,384), O of head 1 [384,512);
-    // P (packed pairs) goes over the upper half of S: keys 0-63 in columns [64,96), keys 64-127 in [96,128)
+    // within a head's 128 columns the scores of keys 0-63 take [0,64), those of keys 64-127 [64,128); the packed P of a
+    // half (32 columns) goes over the first half of its own score columns
     bool alive = true;
     // copies requested so far by the producer thread (for the give-up path)
     uint32_t k_requested = 0, v_requested = 0, q_requested[2] = {0, 0};
