@@ -1193,6 +1193,9 @@ def run_engine(args):
         eng_mod.PagedInferenceEngine.get_decoding_block_mask = \
             lambda self, batch_idx, input_pos: decoding_block_mask(self.block_mask, batch_idx, input_pos)
         install_attention(ref_model.Attention, fused=True)
+    if args.engine_batched_setup:
+        from fpkv.engine_glue import install_decode_setup
+        install_decode_setup(eng_mod.PagedInferenceEngine)
     pages = n_seq * ((prompt + new + P - 1) // P + 1) + 8
     t0 = time.perf_counter()
     eng = eng_mod.PagedInferenceEngine(model, Tok(), None, max_batch_size=n_seq + 1, max_seq_length=8192, n_pages=pages,
@@ -1221,7 +1224,7 @@ def run_engine(args):
     t_all, done = timed(1 + new)
     finite = all(bool(torch.isfinite(r.output_probs).all()) for r in done)
     print(json.dumps({
-        "impl": "engine", "cache": which, "n_gpus": 1, "dtype": "bf16", "data": "synthetic",
+        "impl": "engine", "cache": which, "batched_decode_setup": bool(args.engine_batched_setup), "n_gpus": 1, "dtype": "bf16", "data": "synthetic",
         "config": {"workload": f"the reference's PagedInferenceEngine.generate, 28-layer model (16 q / 8 kv heads, head_dim 128, "
                                f"random weights), {n_seq} requests of {prompt} tokens, {new} decode steps, CUDA graphs"},
         "engine_ready_s": round(ready_s, 1),
@@ -1271,6 +1274,8 @@ def main():
     ap.add_argument("--steps", type=int, default=200)
     ap.add_argument("--warmup", type=int, default=20)
     ap.add_argument("--impl", default="fpkv", choices=["fpkv", "reference", "reference-gpu", "engine"])
+    ap.add_argument("--engine-batched-setup", action="store_true",
+                    help="--impl engine: also batch the engine's per-request decode set-up copies (fpkv.engine_glue.install_decode_setup)")
     ap.add_argument("--engine-cache", default="split", choices=["reference", "expanded", "split", "compact"],
                     help="--impl engine: the cache the reference's engine runs on (its own, or fpkv's in one of its layouts)")
     ap.add_argument("--pool-pages", type=int, default=N_PAGES,

@@ -13,6 +13,9 @@ shrinks to:
 * ``install_attention`` -- the attention call site of the reference model
   (``model.py:139-164``) routed through ``fpkv.PagedKVCache``;
 * ``decoding_block_mask`` -- what ``get_decoding_block_mask`` becomes;
+* ``install_decode_setup`` -- the reference engine's own decode step with its
+  per-request device copies batched (``:966-1003``), and ``install_engine``,
+  which applies all the substitutions to an engine module at once;
 * ``SlotState`` -- per-slot position / rope position / last token kept on the
   device (the reference's ``_input_pos`` and ``_rope_pos_t``, ``:346-352``, plus
   the last token), advanced by one batched device update after sampling, so
@@ -100,6 +103,79 @@ def install_attention(attention_cls, fused: bool = True):
                         flex_attn_kernel_options)
     attention_cls.forward = forward
     return original
+
+
+# ------------------------------------------------- decode step set-up, batched
+def batched_decode_forward(self, sequences):
+    """``PagedInferenceEngine._decode_forward`` (``paged_inference.py:954-1031``)
+    with the graph's inputs filled by a handful of batched operations instead of
+    four small device copies per request (rope position, last token and the two
+    box values, ``:986-1003``) and three element-wise writes into pinned memory
+    per request (``:970-975``).  Same buffers, same graph, same results; the
+    eager path (no captured graph) is the reference's own."""
+    if not self.cudagraph_captured:
+        return self._fpkv_original_decode_forward(sequences)
+    B = len(sequences)
+    graph_bs = next(x for x in self._graph_bs if x >= B)
+    graph = self._graphs[graph_bs]
+    gv = self._graph_vars
+    slots = [seq.batch_idx for seq in sequences]
+    # host: slots and positions of the batch, written into the pinned staging buffers in one go each
+    self._decode_gv_bidx_pinned.zero_()
+    slots_t = torch.tensor(slots, dtype=torch.int64)
+    self._decode_bidx_pinned[:B] = slots_t
+    self._decode_gv_bidx_pinned[:B] = slots_t
+    self._decode_pos_pinned[:B] = torch.tensor([seq.total_length - 1 for seq in sequences], dtype=torch.int32)
+    # device: positions by slot, then rope positions, last tokens and box values of the whole batch at once
+    self._decode_bidx_gpu[:B].copy_(self._decode_bidx_pinned[:B], non_blocking=True)
+    self._decode_pos_gpu[:B].copy_(self._decode_pos_pinned[:B], non_blocking=True)
+    self._input_pos.scatter_(0, self._decode_bidx_gpu[:B], self._decode_pos_gpu[:B])
+    self._rope_pos_t.scatter_(0, self._decode_bidx_gpu[:B],
+                              torch.stack([seq.pos_t for seq in sequences]).to(self._rope_pos_t.dtype))
+    gv["input_ids"][:B].copy_(torch.stack([seq.last_token_id for seq in sequences]))
+    gv["input_ids"][B:].zero_()
+    gv["batch_idx"].copy_(self._decode_gv_bidx_pinned, non_blocking=True)
+    gv["coord_xy"].zero_()
+    gv["size_hw"].zero_()
+    boxed = [i for i, seq in enumerate(sequences) if seq.current_bbox_xy is not None]
+    if boxed:
+        rows = slice(0, B) if len(boxed) == B else torch.tensor(boxed, device=gv["coord_xy"].device)
+        gv["coord_xy"][rows] = torch.stack([sequences[i].current_bbox_xy for i in boxed]).to(gv["coord_xy"].dtype)
+        gv["size_hw"][rows] = torch.stack([sequences[i].current_bbox_hw for i in boxed]).to(gv["size_hw"].dtype)
+    graph.replay()
+    return gv["logits_out"][:B], gv["h_out"][:B]
+
+
+def install_decode_setup(engine_cls):
+    """Replace ``engine_cls._decode_forward`` (the reference's
+    ``PagedInferenceEngine``) by ``batched_decode_forward``.  Returns the
+    original method."""
+    original = engine_cls._decode_forward
+    engine_cls._fpkv_original_decode_forward = original
+    engine_cls._decode_forward = batched_decode_forward
+    return original
+
+
+def install_engine(engine_module, attention_cls, fused: bool = True, cache_factory=None):
+    """Everything an engine built like the reference's needs to run on this
+    package, in one call: ``engine_module.PagedKVCache`` (the name the engine
+    constructs its cache through, ``paged_inference.py:27,321``) becomes
+    ``cache_factory`` (default: ``fpkv.PagedKVCache`` with the arguments the
+    engine passes), ``get_decoding_block_mask`` becomes ``decoding_block_mask``,
+    ``Attention.forward`` goes through ``install_attention`` and the decode
+    step's set-up through ``install_decode_setup``.  Returns a function that
+    puts everything back."""
+    engine_cls = engine_module.PagedInferenceEngine
+    saved = (engine_module.PagedKVCache, engine_cls.get_decoding_block_mask, engine_cls._decode_forward, attention_cls.forward)
+    engine_module.PagedKVCache = cache_factory or PagedKVCache
+    engine_cls.get_decoding_block_mask = \
+        lambda self, batch_idx, input_pos: decoding_block_mask(self.block_mask, batch_idx, input_pos)
+    install_attention(attention_cls, fused=fused)
+    install_decode_setup(engine_cls)
+
+    def restore():
+        engine_module.PagedKVCache, engine_cls.get_decoding_block_mask, engine_cls._decode_forward, attention_cls.forward = saved
+    return restore
 
 
 # ------------------------------------------------------- per-slot step state

@@ -23,7 +23,7 @@ import types
 import pytest
 import torch
 
-from fpkv.engine_glue import decoding_block_mask, install_attention
+from fpkv.engine_glue import decoding_block_mask, install_attention, install_engine
 from fpkv.paged_attention import PagedKVCache
 from test_dropin_gpu import _reference_root
 
@@ -93,19 +93,23 @@ def make_requests(ref):
     return requests
 
 
-def generate(ref, model, args, cache, graphs):
+def generate(ref, model, args, cache, graphs, batched_setup=False):
     eng_mod = ref.engine
     saved = (eng_mod.PagedKVCache, eng_mod.PagedInferenceEngine.get_decoding_block_mask, ref.model.Attention.forward)
+    restore = None
     try:
         if cache != "reference":
             def fpkv_cache(**kw):
                 if cache == "split":                                 # KV heads stored once, second K halves per query head
                     kw = dict(kw, n_heads=args.n_kv_heads, split_q_heads=args.n_heads)
                 return PagedKVCache(**kw)
-            eng_mod.PagedKVCache = fpkv_cache
-            eng_mod.PagedInferenceEngine.get_decoding_block_mask = \
-                lambda self, batch_idx, input_pos: decoding_block_mask(self.block_mask, batch_idx, input_pos)
-            install_attention(ref.model.Attention, fused=True)
+            if batched_setup:                                        # all substitutions at once, decode set-up batched too
+                restore = install_engine(eng_mod, ref.model.Attention, fused=True, cache_factory=fpkv_cache)
+            else:
+                eng_mod.PagedKVCache = fpkv_cache
+                eng_mod.PagedInferenceEngine.get_decoding_block_mask = \
+                    lambda self, batch_idx, input_pos: decoding_block_mask(self.block_mask, batch_idx, input_pos)
+                install_attention(ref.model.Attention, fused=True)
         engine = eng_mod.PagedInferenceEngine(model, FakeTokenizer(), None, max_batch_size=4, max_seq_length=1024,
                                               n_pages=24, seed=0, enable_hr_cache=False, capture_cudagraph=graphs,
                                               max_decode_steps_between_prefills=3)
@@ -116,7 +120,10 @@ def generate(ref, model, args, cache, graphs):
             assert engine.paged_kv_cache.num_free_pages == 23 and len(engine.paged_kv_cache.free_batch_idx) == 3
         return [s.output_ids.tolist() for s in done]
     finally:
-        eng_mod.PagedKVCache, eng_mod.PagedInferenceEngine.get_decoding_block_mask, ref.model.Attention.forward = saved
+        if restore is not None:
+            restore()
+        else:
+            eng_mod.PagedKVCache, eng_mod.PagedInferenceEngine.get_decoding_block_mask, ref.model.Attention.forward = saved
 
 
 @pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
@@ -129,3 +136,6 @@ def test_reference_engine_generates_the_same_tokens_on_the_fpkv_cache(ref, dtype
         for graphs in (False, True):
             got = generate(ref, model, args, cache, graphs)
             assert got == want, f"{cache} pool, {'CUDA graphs' if graphs else 'eager decode'}: tokens differ from the reference's"
+    # the engine's own decode step with its per-request copies batched (install_engine), graphs on
+    got = generate(ref, model, args, "split", graphs=True, batched_setup=True)
+    assert got == want, "batched decode set-up: tokens differ from the reference's"
