@@ -46,6 +46,11 @@
 //     thread does, so each head gets its own issuer.
 //   * Warp 11 prepares the next item while the current one runs: slot, visible
 //     extent of every row, page ids of all key tiles (two descriptor buffers).
+//   * An item of a SINGLE head (odd GQA ratio, a pool with one stored head per query head, a split pool) runs the
+//     same machinery with the pair's two sides taken by the even and the odd key tiles of the one head: softmax
+//     group g and MMA issuer g work through tiles g, g + 2, ..., each side with its own score columns, reference
+//     maximum, row sum and O accumulator, and the two partial results are merged in the epilogue (each group
+//     writes half of the output columns).
 // The running maximum is only raised when a half exceeds it by more than 2^8
 // (probabilities stay below 256, exact in fp32 and harmless in bf16), so O in
 // TMEM is rarely rescaled.  Each thread owns a whole output row and writes it
@@ -352,7 +357,7 @@ __device__ __forceinline__ float max64(const uint32_t (&sv)[2][32], int valid_co
     return mx;
 }
 
-template <typename T, int D>
+template <typename T, int D, bool kSolo>
 __global__ void __launch_bounds__(kPrefillThreads, 1)
 prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constant__ CUtensorMap kv_map,
                   const __grid_constant__ CUtensorMap khw_map, const __grid_constant__ CUtensorMap v_map,
@@ -368,6 +373,7 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_consta
     volatile int* abort_flag = ints;                       // [0] abort, [1] TMEM base
     int* tmem_slot = ints + 1;
     ItemDesc* desc = reinterpret_cast<ItemDesc*>(ints + 16);   // [2]
+    float* xch = reinterpret_cast<float*>(desc + 2);       // [2][2 groups][128 rows][m, l]: merge of single-head items
 
     // mbarriers; every one keeps its phase across items
     const uint32_t desc_full0 = s32(bars + 0), desc_empty0 = s32(bars + 2);            // [2] descriptor buffers
@@ -379,24 +385,28 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_consta
     const uint32_t pv_done0 = s_half0 + 64;                                            // [2] a half's P.V has completed (one phase per half)
     const uint32_t all_done0 = s_half0 + 80, o_free0 = s_half0 + 96;                   // [2] last P.V complete / O read by the epilogue
     const uint32_t drain0 = s_half0 + 112;                                             // [2] give-up path: a head's MMAs have completed
+    const uint32_t merge0 = s_half0 + 128;                                             // single-head items: both groups have published (m, l)
 
     const int tid = threadIdx.x, warp = tid / 32, lane = tid % 32;
     constexpr int kTileBytesD = kTileM * D * 2;            // bytes a Q, K or V tile really holds
-    const int heads = prm.heads_per_item;                  // 1 or 2 query heads of one stored head
+    constexpr bool solo = kSolo;                           // single-head items: the two softmax groups split every key tile
+    constexpr int heads = kSolo ? 1 : 2;                   // query heads of one stored head in an item
     const int n_rep = prm.Hq / prm.Hkv;
 
     // ---- set-up, once per CTA ------------------------------------------------
     if (tid == 0) {
         for (int b = 0; b < 2; ++b) {
-            bar_init(desc_full0 + 8 * b, 1); bar_init(desc_empty0 + 8 * b, 1 + 5 * heads);
-            bar_init(q_full0 + 8 * b, 1); bar_init(q_empty0 + 8 * b, 1);
+            bar_init(desc_full0 + 8 * b, 1); bar_init(desc_empty0 + 8 * b, 3 + 2 * kSoftmaxWarps);
+            bar_init(q_full0 + 8 * b, 1); bar_init(q_empty0 + 8 * b, solo ? 2 : 1);      // single head: both issuers read the one query tile
             for (int hf = 0; hf < 2; ++hf) { bar_init(s_half0 + 16 * b + 8 * hf, 1); bar_init(p_half0 + 16 * b + 8 * hf, kSoftmaxWarps); }
-            bar_init(pv_done0 + 8 * b, 1); bar_init(all_done0 + 8 * b, 1); bar_init(o_free0 + 8 * b, kSoftmaxWarps);
+            bar_init(pv_done0 + 8 * b, 1); bar_init(all_done0 + 8 * b, 1);
+            bar_init(o_free0 + 8 * b, solo ? 2 * kSoftmaxWarps : kSoftmaxWarps);
             bar_init(drain0 + 8 * b, 1);
         }
+        bar_init(merge0, 2 * kSoftmaxWarps);
         for (int s = 0; s < kStages; ++s) {
             bar_init(k_full0 + 8 * s, 1); bar_init(v_full0 + 8 * s, 1);
-            bar_init(k_empty0 + 8 * s, heads); bar_init(v_empty0 + 8 * s, heads);     // one commit per head's MMA warp
+            bar_init(k_empty0 + 8 * s, heads); bar_init(v_empty0 + 8 * s, heads);     // one commit per MMA warp that reads the tile
         }
         *abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -539,12 +549,13 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_consta
                 if (alive) bar_arrive(desc_empty0 + 8 * b);
             }
         }
-    } else if (warp >= kMmaWarp && warp < kMmaWarp + heads) {
+    } else if (warp >= kMmaWarp && warp < kMmaWarp + 2) {
         // ============================== MMA issuers =========================
-        // One issuing warp per head of the pair.  The tensor pipe takes the MMAs of one thread strictly one
-        // after the other, and whatever else that thread does (barrier waits, commits) is time the pipe
-        // idles for it; with an issuer per head the other head's MMAs fill those gaps, and each head's
-        // chain  S -> softmax -> P.V -> next S  advances on its own.  Both heads read the one staged K / V tile.
+        // Two issuing warps.  The tensor pipe takes the MMAs of one thread strictly one after the other, and
+        // whatever else that thread does (barrier waits, commits) is time the pipe idles for it; with two issuers
+        // the other one's MMAs fill those gaps, and each side's chain  S -> softmax -> P.V -> next S  advances on its
+        // own.  With a head pair, issuer g has head g and both read the one staged K / V tile; with a single head,
+        // issuer g has the key tiles g, g + 2, ... of that head.
         const int g = warp - kMmaWarp;
         if (lane == 0) {
             const bool is_bf16 = std::is_same<T, __nv_bfloat16>::value;
@@ -552,43 +563,47 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_consta
             const uint32_t idesc_pv = umma_idesc(is_bf16, true, D);
             // descriptor words: low = start address >> 4 (| LBO for MN-major), high = SBO 1024 | version | 128-byte swizzle
             const uint32_t desc_hi = (uint32_t)(umma_desc(0, 0, 1024) >> 32);
-            const uint32_t q_lo = ((s32(q_s) & 0x3FFFF) >> 4) + g * (kTileBytes >> 4), k_lo = (s32(k_s) & 0x3FFFF) >> 4;
+            const int qb = solo ? 0 : g;                   // query buffer (and its barriers) this issuer reads
+            constexpr int step = solo ? 2 : 1;             // distance between this issuer's key tiles
+            const int j0 = solo ? g : 0;                   // its first key tile of an item
+            const uint32_t q_lo = ((s32(q_s) & 0x3FFFF) >> 4) + qb * (kTileBytes >> 4), k_lo = (s32(k_s) & 0x3FFFF) >> 4;
             const uint32_t v_lo = ((s32(v_s) & 0x3FFFF) >> 4) | (uint32_t)umma_desc(0, kHalfBytes, 1024);
             const uint32_t t_s = tmem + g * kTileN, t_o = tmem + 256 + g * kTileN;
             const uint32_t s_lo = s_half0 + 16 * g, s_hi = s_lo + 8, p_lo = p_half0 + 16 * g, p_hi = p_lo + 8;
             const uint32_t pv_done = pv_done0 + 8 * g;
-            uint32_t gk = 0, th = 0, wit = 0;              // key tiles, head-tiles and items with work so far
+            uint32_t gk = 0, th = 0, wit = 0, wg = 0;      // key tiles of all items, this issuer's tiles, items with work, items with work for this issuer
             for (uint32_t it = 0; alive; ++it) {
                 const uint32_t b = it & 1u;
                 if (!bar_wait(desc_full0 + 8 * b, (it >> 1) & 1u, abort_flag)) { alive = false; break; }
                 const ItemDesc* d = desc + b;
                 if (!d->valid) break;
                 const int n = d->n_tiles;
-                if (n > 0) {
-                    const uint32_t st0 = gk % kStages;
-                    alive = bar_wait(q_full0 + 8 * g, wit & 1u, abort_flag) &&
-                            bar_wait(k_full0 + 8 * st0, (gk / kStages) & 1u, abort_flag);
+                if (n > j0) {
+                    const uint32_t c0 = gk + j0, st0 = c0 % kStages;
+                    alive = bar_wait(q_full0 + 8 * qb, wit & 1u, abort_flag) &&
+                            bar_wait(k_full0 + 8 * st0, (c0 / kStages) & 1u, abort_flag);
                     if (!alive) break;
                     tc_fence_after();
                     issue_qk_half<0, D>(t_s, q_lo, k_lo + st0 * (kTileBytes >> 4), desc_hi, idesc_qk, s_lo);
                     issue_qk_half<1, D>(t_s + 64, q_lo, k_lo + st0 * (kTileBytes >> 4), desc_hi, idesc_qk, s_hi);
                     umma_commit(k_empty0 + 8 * st0);
-                    if (n == 1) umma_commit(q_empty0 + 8 * g);
-                    for (int j = 0; j < n; ++j) {
-                        const uint32_t cur = gk + j, nxt = cur + 1;
+                    if (j0 + step >= n) umma_commit(q_empty0 + 8 * qb);    // that was this issuer's only Q.K^T of the item
+                    for (int j = j0; j < n; j += step) {
+                        const uint32_t cur = gk + j, nxt = cur + step;
                         const uint32_t st = cur % kStages, sn = nxt % kStages;
+                        const bool more = j + step < n;
                         // the operand tiles first: they arrived long ago, and waiting for them here costs nothing
                         // while the softmax group is still busy
                         if (!bar_wait(v_full0 + 8 * st, (cur / kStages) & 1u, abort_flag)) { alive = false; break; }
-                        if (j + 1 < n && !bar_wait(k_full0 + 8 * sn, (nxt / kStages) & 1u, abort_flag)) { alive = false; break; }
+                        if (more && !bar_wait(k_full0 + 8 * sn, (nxt / kStages) & 1u, abort_flag)) { alive = false; break; }
                         // O of the previous item must have been read by its epilogue before the first P.V overwrites it
-                        if (j == 0 && !bar_wait(o_free0 + 8 * g, (wit & 1u) ^ 1u, abort_flag)) { alive = false; break; }
+                        if (j == j0 && !bar_wait(o_free0 + 8 * g, (wg & 1u) ^ 1u, abort_flag)) { alive = false; break; }
                         // keys 0-63: P.V, then at once the next tile's scores of the same half (its columns are free again)
                         if (!bar_wait(p_lo, th & 1u, abort_flag)) { alive = false; break; }
                         tc_fence_after();
-                        issue_pv_half<0>(t_o, t_s, v_lo + st * (kTileBytes >> 4), desc_hi, idesc_pv, j > 0);
+                        issue_pv_half<0>(t_o, t_s, v_lo + st * (kTileBytes >> 4), desc_hi, idesc_pv, j > j0);
                         umma_commit(pv_done);
-                        if (j + 1 < n) issue_qk_half<0, D>(t_s, q_lo, k_lo + sn * (kTileBytes >> 4), desc_hi, idesc_qk, s_lo);
+                        if (more) issue_qk_half<0, D>(t_s, q_lo, k_lo + sn * (kTileBytes >> 4), desc_hi, idesc_qk, s_lo);
                         // keys 64-127
                         if (!bar_wait(p_hi, th & 1u, abort_flag)) { alive = false; break; }
                         tc_fence_after();
@@ -596,16 +611,19 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_consta
                         umma_commit(pv_done);
                         umma_commit(v_empty0 + 8 * st);
                         ++th;
-                        if (j + 1 < n) {
+                        if (more) {
                             issue_qk_half<1, D>(t_s + 64, q_lo, k_lo + sn * (kTileBytes >> 4), desc_hi, idesc_qk, s_hi);
                             umma_commit(k_empty0 + 8 * sn);
-                            if (j + 2 == n) umma_commit(q_empty0 + 8 * g);     // that was the item's last Q.K^T
+                            if (j + 2 * step >= n) umma_commit(q_empty0 + 8 * qb);     // that was this issuer's last Q.K^T of the item
                         }
                     }
                     if (!alive) break;
                     umma_commit(all_done0 + 8 * g);
-                    gk += n; ++wit;
+                    ++wg;
+                } else if (n > 0) {
+                    bar_arrive(q_empty0 + 8 * qb);         // single head, one key tile: nothing for this issuer, only its share of the hand-back
                 }
+                if (n > 0) { gk += n; ++wit; }
                 bar_arrive(desc_empty0 + 8 * b);
             }
             if (!alive) {
@@ -615,19 +633,25 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_consta
                 for (uint32_t k = 0; k < kSpin && !bar_try(drain0 + 8 * g, 0); ++k) {}
             }
         }
-    } else if (warp < kSoftmaxWarps * heads) {
+    } else if (warp < 2 * kSoftmaxWarps && (warp < kSoftmaxWarps || heads == 2 || solo)) {
         // ============================== softmax groups ======================
-        // Group h (warps 4h .. 4h+3) owns head h of the pair: one thread per query row, warp w reaches tensor-
-        // memory lanes [32 (w % 4), +32).  The groups do not synchronise with each other: while one exponentiates,
-        // the other one's score loads, maximum, P store and barrier traffic -- and both heads' MMAs -- run underneath.
-        const int h = warp / kSoftmaxWarps, quarter = warp % kSoftmaxWarps;
+        // Group g (warps 4g .. 4g+3): one thread per query row, warp w reaches tensor-memory lanes [32 (w % 4), +32).
+        // With a head pair, group g owns head g.  With a single head, group g owns the key tiles g, g + 2, ... of
+        // that head, with its own score columns, reference maximum, row sum and accumulator (those of group 1 live
+        // in the columns the second head would use).  The groups do not synchronise with each other inside an
+        // item: while one exponentiates, the other one's score loads, maximum, P store and barrier traffic -- and
+        // the MMAs -- run underneath.
+        const int grp = warp / kSoftmaxWarps, quarter = warp % kSoftmaxWarps;
+        const int h = solo ? 0 : grp;                                  // head of the item this group works on
+        constexpr int step = solo ? 2 : 1;                             // distance between this group's key tiles
+        const int j0 = solo ? grp : 0;                                 // its first key tile of an item
         const int row = quarter * 32 + lane;
         const uint32_t lane_base = (uint32_t)(quarter * 32) << 16;
-        const uint32_t ts = tmem + h * kTileN + lane_base;            // S of this head: keys 0-63 in columns [0,64), keys 64-127 in [64,128)
-        const uint32_t to = tmem + 256 + h * kTileN + lane_base;      // O of this head
-        const uint32_t pv_done = pv_done0 + 8 * h;
+        const uint32_t ts = tmem + grp * kTileN + lane_base;          // this group's scores: keys 0-63 in columns [0,64), keys 64-127 in [64,128)
+        const uint32_t to = tmem + 256 + grp * kTileN + lane_base;    // this group's accumulator
+        const uint32_t pv_done = pv_done0 + 8 * grp;
         T* out = reinterpret_cast<T*>(prm.out);
-        uint32_t gk = 0, th = 0, wit = 0;                  // key tiles, head-tiles and items with work so far
+        uint32_t gk = 0, th = 0, wit = 0, wg = 0;          // key tiles of all items, this group's tiles, items with work, items with work for this group
         for (uint32_t it = 0; alive; ++it) {
             const uint32_t b = it & 1u;
             if (!bar_wait(desc_full0 + 8 * b, (it >> 1) & 1u, abort_flag)) { alive = false; break; }
@@ -644,13 +668,13 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_consta
             for (int o = 16; o > 0; o >>= 1) wfull = min(wfull, __shfl_xor_sync(0xffffffffu, wfull, o));
             wfull = min(wfull, first_bad);
             const int zero_from = min(first_bad, (max_extent % kTileN) ? n - 1 : n);   // first tile with value rows to clear
-            for (int j = 0; j < n && alive; ++j) {
+            for (int j = j0; j < n && alive; j += step) {
                 const bool page_ok = j < first_bad || d->page_ok[j];
                 // Value rows past the last key any row of this tile sees (the tail of the last key tile, or all of
                 // an unmapped page's stand-in) were fetched but possibly never appended: the pool may hold anything
-                // there, and 0 x NaN would poison O.  Clear them in shared memory before this head's first P.V of
-                // the tile (both groups do, each ahead of its own hand-over; the tensor cores read shared memory
-                // through the async proxy, hence the proxy fence).
+                // there, and 0 x NaN would poison O.  Clear them in shared memory before this group's first P.V of
+                // the tile (every group that reads the tile does, each ahead of its own hand-over; the tensor cores
+                // read shared memory through the async proxy, hence the proxy fence).
                 if (j >= zero_from) {
                     const int tile_rows = page_ok ? min(kTileN, max_extent - j * kTileN) : 0;
                     const uint32_t cur = gk + j, st = cur % kStages;
@@ -669,9 +693,9 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_consta
                 // issued: the scores of the next half are there when this group comes back for them.
 #pragma unroll
                 for (int hf = 0; hf < 2; ++hf) {
-                    const uint32_t unit = 2 * th + hf;                          // halves this head has gone through so far
+                    const uint32_t unit = 2 * th + hf;                          // halves this group has gone through so far
                     const int valid_cols = valid_row - 64 * hf;
-                    if (!bar_wait(s_half0 + 16 * h + 8 * hf, th & 1u, abort_flag)) { alive = false; break; }
+                    if (!bar_wait(s_half0 + 16 * grp + 8 * hf, th & 1u, abort_flag)) { alive = false; break; }
                     tc_fence_after();
                     tmem_ld32_nowait(ts + 64 * hf, sv[0]);
                     tmem_ld32_nowait(ts + 64 * hf + 32, sv[1]);
@@ -684,7 +708,7 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_consta
                     if (__any_sync(0xffffffffu, raise)) {  // tensor-memory access is a whole-warp operation
                         const float m_new = raise ? mx : m_ref;
                         const float alpha = (m_ref == -INFINITY) ? 0.f : exp2f(m_ref - m_new);
-                        if (j > 0 || hf > 0) {             // rescale this row of O in tensor memory
+                        if (j > j0 || hf > 0) {            // rescale this row of O in tensor memory (nothing is in it before the group's first P.V)
                             if (!bar_wait(pv_done, (unit - 1) & 1u, abort_flag)) { alive = false; break; }
                             tc_fence_after();
 #pragma unroll 1
@@ -707,53 +731,113 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_consta
                     asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
                     tc_fence_before();
                     __syncwarp();
-                    if (lane == 0) bar_arrive(p_half0 + 16 * h + 8 * hf);
+                    if (lane == 0) bar_arrive(p_half0 + 16 * grp + 8 * hf);
                 }
                 ++th;
             }
             if (!alive) break;
             gk += n;
             // ---- epilogue: O / l -> out, lse; every thread owns one row of 256 contiguous bytes ----
-            if (n > 0) {
-                if (!bar_wait(all_done0 + 8 * h, wit & 1u, abort_flag)) { alive = false; break; }
+            const bool own_tiles = n > j0;                 // this group's accumulator holds something
+            const bool oth_tiles = solo && n > (j0 ^ 1);   // single head: so does the other group's
+            if (own_tiles) {
+                if (!bar_wait(all_done0 + 8 * grp, wg & 1u, abort_flag)) { alive = false; break; }
                 tc_fence_after();
-                ++wit;
+                ++wg;
             }
+            float w_own = 1.f, w_oth = 0.f;                // single head: weights of the two groups' partial results
+            if (solo && n > 0) {
+                // The two groups went through disjoint sets of key tiles, each with its own reference maximum: tell
+                // each other (m, l) -- each after its own last P.V has completed, so that both accumulators are final
+                // once both have told -- then every thread scales both accumulators of its row to the common maximum.
+                float2* told = reinterpret_cast<float2*>(xch) + (wit & 1u) * (2 * kTileM);   // two buffers, used in turn
+                told[grp * kTileM + row] = make_float2(m_ref, l);
+                __syncwarp();
+                if (lane == 0) bar_arrive(merge0);
+                if (!bar_wait(merge0, wit & 1u, abort_flag)) { alive = false; break; }
+                tc_fence_after();
+                const float2 oth = told[(grp ^ 1) * kTileM + row];
+                const float m = fmaxf(m_ref, oth.x);
+                w_own = (m_ref == -INFINITY) ? 0.f : exp2f(m_ref - m);
+                w_oth = (oth.x == -INFINITY) ? 0.f : exp2f(oth.x - m);
+                l = l * w_own + oth.y * w_oth;
+                m_ref = m;
+            }
+            if (n > 0) ++wit;
             const float inv = l > 0.f ? 1.f / l : 0.f;
             const float lse_nat = l > 0.f ? (m_ref + log2f(l)) * kLn2 : -INFINITY;
             const bool gate_on = prm.epi.sinks != nullptr;
             const float gate = sink_gate(prm.epi, hq, lse_nat);
             T* dst = out + (prm.epi.token_major ? ((size_t)tk * prm.Hq + hq) : ((size_t)hq * prm.L + tk)) * D;
+            if (!solo) {
 #pragma unroll 1
-            for (int c2 = 0; c2 < D / 64; ++c2) {
-                if (n > 0) {
-                    tmem_ld32_nowait(to + c2 * 64, sv[0]);
-                    tmem_ld32_nowait(to + c2 * 64 + 32, sv[1]);
-                    tmem_wait_ld();
-                    if (c2 == D / 64 - 1) {                // O is in registers: the next item's first P.V may overwrite it
-                        tc_fence_before();
-                        __syncwarp();
-                        if (lane == 0) bar_arrive(o_free0 + 8 * h);
+                for (int c2 = 0; c2 < D / 64; ++c2) {
+                    if (n > 0) {
+                        tmem_ld32_nowait(to + c2 * 64, sv[0]);
+                        tmem_ld32_nowait(to + c2 * 64 + 32, sv[1]);
+                        tmem_wait_ld();
+                        if (c2 == D / 64 - 1) {            // O is in registers: the next item's first P.V may overwrite it
+                            tc_fence_before();
+                            __syncwarp();
+                            if (lane == 0) bar_arrive(o_free0 + 8 * grp);
+                        }
+                    }
+                    if (tk < prm.L) {
+#pragma unroll
+                        for (int q8 = 0; q8 < 4; ++q8) {
+                            uint32_t w[8];
+#pragma unroll
+                            for (int e = 0; e < 8; ++e) {
+                                const int c = q8 * 16 + 2 * e;
+                                const float a = (n > 0 && l > 0.f) ? __uint_as_float(sv[c >> 5][c & 31]) * inv : 0.f;
+                                const float bb = (n > 0 && l > 0.f) ? __uint_as_float(sv[c >> 5][(c & 31) + 1]) * inv : 0.f;
+                                w[e] = gated_pair<T>(a, bb, gate, gate_on);
+                            }
+                            T* at = dst + c2 * 64 + q8 * 16;   // two adjacent 16-byte stores fill a 32-byte sector
+                            *reinterpret_cast<uint4*>(at) = make_uint4(w[0], w[1], w[2], w[3]);
+                            *reinterpret_cast<uint4*>(at + 8) = make_uint4(w[4], w[5], w[6], w[7]);
+                        }
                     }
                 }
-                if (tk < prm.L) {
+            } else {
+                // single head: this group writes columns [grp * D/2, +D/2) of the row, from both accumulators
+                constexpr int kCols = D / 2;
+                const uint32_t to_oth = tmem + 256 + (grp ^ 1) * kTileN + lane_base;
+#pragma unroll 1
+                for (int c2 = 0; c2 < kCols / 32; ++c2) {
+                    const int col0 = grp * kCols + c2 * 32;
+                    // (an accumulator that got no key tile of this item holds whatever was there: it is not read)
+                    if (own_tiles) tmem_ld32_nowait(to + col0, sv[0]);
+                    if (oth_tiles) tmem_ld32_nowait(to_oth + col0, sv[1]);
+                    if (own_tiles || oth_tiles) tmem_wait_ld();
+                    if (c2 == kCols / 32 - 1 && (own_tiles || oth_tiles)) {   // read: the next item's P.V may overwrite them
+                        tc_fence_before();
+                        __syncwarp();
+                        if (lane == 0 && own_tiles) bar_arrive(o_free0 + 8 * grp);
+                        if (lane == 0 && oth_tiles) bar_arrive(o_free0 + 8 * (grp ^ 1));
+                    }
+                    if (tk < prm.L) {
 #pragma unroll
-                    for (int q8 = 0; q8 < 4; ++q8) {
-                        uint32_t w[8];
+                        for (int q8 = 0; q8 < 2; ++q8) {
+                            uint32_t w[8];
 #pragma unroll
-                        for (int e = 0; e < 8; ++e) {
-                            const int c = q8 * 16 + 2 * e;
-                            const float a = (n > 0 && l > 0.f) ? __uint_as_float(sv[c >> 5][c & 31]) * inv : 0.f;
-                            const float bb = (n > 0 && l > 0.f) ? __uint_as_float(sv[c >> 5][(c & 31) + 1]) * inv : 0.f;
-                            w[e] = gated_pair<T>(a, bb, gate, gate_on);
+                            for (int e = 0; e < 8; ++e) {
+                                const int c = q8 * 16 + 2 * e;
+                                const bool some = n > 0 && l > 0.f;
+                                const float a0 = own_tiles ? __uint_as_float(sv[0][c]) * w_own : 0.f, a1 = oth_tiles ? __uint_as_float(sv[1][c]) * w_oth : 0.f;
+                                const float b0 = own_tiles ? __uint_as_float(sv[0][c + 1]) * w_own : 0.f, b1 = oth_tiles ? __uint_as_float(sv[1][c + 1]) * w_oth : 0.f;
+                                const float a = some ? (a0 + a1) * inv : 0.f;
+                                const float bb = some ? (b0 + b1) * inv : 0.f;
+                                w[e] = gated_pair<T>(a, bb, gate, gate_on);
+                            }
+                            T* at = dst + col0 + q8 * 16;
+                            *reinterpret_cast<uint4*>(at) = make_uint4(w[0], w[1], w[2], w[3]);
+                            *reinterpret_cast<uint4*>(at + 8) = make_uint4(w[4], w[5], w[6], w[7]);
                         }
-                        T* at = dst + c2 * 64 + q8 * 16;   // two adjacent 16-byte stores fill a 32-byte sector
-                        *reinterpret_cast<uint4*>(at) = make_uint4(w[0], w[1], w[2], w[3]);
-                        *reinterpret_cast<uint4*>(at + 8) = make_uint4(w[4], w[5], w[6], w[7]);
                     }
                 }
             }
-            if (tk < prm.L) prm.lse[(size_t)hq * prm.L + tk] = lse_nat;
+            if (tk < prm.L && (!solo || grp == 0)) prm.lse[(size_t)hq * prm.L + tk] = lse_nat;
             __syncwarp();
             if (lane == 0) bar_arrive(desc_empty0 + 8 * b);
         }
@@ -813,7 +897,8 @@ int prefill_sm_count() {
     return n;
 }
 
-constexpr int kPrefillSmem = 1024 + (2 + 2 * kStages) * kTileBytes + 48 * 8 + 16 * 4 + 2 * (int)sizeof(ItemDesc) + 64;   // Q x2, K and V x kStages
+constexpr int kPrefillSmem = 1024 + (2 + 2 * kStages) * kTileBytes + 48 * 8 + 16 * 4 + 2 * (int)sizeof(ItemDesc) +
+                             2 * 2 * kTileM * 8 + 64;   // Q x2, K and V x kStages, barriers, flags, descriptors, merge buffers
 
 }  // namespace
 
@@ -886,8 +971,13 @@ int launch_prefill_tc(const PoolView& pv, int layer, void* out, float* lse, cons
         return true;
     };
     bool ok;
-    if (pv.dtype == FPKV_BF16) ok = pv.D == 128 ? launch(prefill_tc_kernel<__nv_bfloat16, 128>) : launch(prefill_tc_kernel<__nv_bfloat16, 64>);
-    else ok = pv.D == 128 ? launch(prefill_tc_kernel<__half, 128>) : launch(prefill_tc_kernel<__half, 64>);
+    if (prm.heads_per_item == 2) {
+        if (pv.dtype == FPKV_BF16) ok = pv.D == 128 ? launch(prefill_tc_kernel<__nv_bfloat16, 128, false>) : launch(prefill_tc_kernel<__nv_bfloat16, 64, false>);
+        else ok = pv.D == 128 ? launch(prefill_tc_kernel<__half, 128, false>) : launch(prefill_tc_kernel<__half, 64, false>);
+    } else {
+        if (pv.dtype == FPKV_BF16) ok = pv.D == 128 ? launch(prefill_tc_kernel<__nv_bfloat16, 128, true>) : launch(prefill_tc_kernel<__nv_bfloat16, 64, true>);
+        else ok = pv.D == 128 ? launch(prefill_tc_kernel<__half, 128, true>) : launch(prefill_tc_kernel<__half, 64, true>);
+    }
     if (!ok) return FPKV_ELAUNCH;
     return cudaGetLastError() == cudaSuccess ? FPKV_OK : FPKV_ELAUNCH;
 }
