@@ -859,12 +859,32 @@ def bench_split_layout(rk, args, n_pages=4096):
     step_blocks, _ = timed_blocks(rk, stream, R, K, step, 5)
     attn_blocks, _ = timed_blocks(rk, stream, R, K, attn, 5)
     cache.check_status()
+    del cache
+    torch.cuda.empty_cache()
+    # config 3's packed prefill row on a split pool: single-head items in the tensor-core kernel
+    import workloads as wl
+    from fpkv.paged_attention import paged_attention
+    pcase, pipos, pq, pk, pv = prefill_inputs(device)
+    pcache = PagedKVCache(256, P, 16, HKV, D, 1, torch.bfloat16, device, split_q_heads=HQ)
+    pslots = []
+    for toks in pcase.seq_tokens:
+        s = pcache.allocate(); pslots.append(s); pcache.reserve(s, None, len(toks))
+    pbidx = pcase.batch_idx_for(pslots).to(device)
+    pmask = pcache.create_prefill_blockmask(pbidx, pcase.input_ids.to(device), wl.IMG_CLS_ID, wl.END_OF_IMG_ID)
+    pairs = int(pmask.extent(pipos).to(torch.int64).sum().item())
+    n_rep = HQ // HKV
+    pcache.insert_kv(0, pk.repeat_interleave(n_rep, 1).contiguous(), pv.repeat_interleave(n_rep, 1).contiguous(),
+                     input_pos=pipos, batch_idx=pbidx)
+    ms_prefill = time_loop(rk, stream, 50, lambda: paged_attention(pq, pcache, 0, pbidx, pipos, pmask))
+    pcache.check_status()
+    del pcache
+    torch.cuda.empty_cache()
     per_key = (HKV * (D // 2) + HQ * (D // 2) + HKV * D) * 2          # bytes of one key position in the split layout
     keys = [sum(L + 1 + (5 + r * K + i) % WINDOW for L in case.lens for i in range(K)) for r in range(R)]
     rates = [kk * per_key / (t * 1e-3) / 1e9 for kk, t in zip(keys, attn_blocks)]
     mid = sorted(range(R), key=lambda r: rates[r])[R // 2]
     hbm_peak, _, which = measured_peaks()
-    (t_attn, t_step), (work,) = rk.reduce([attn_blocks[mid], step_blocks[mid]], [float(keys[mid] * per_key)])
+    (t_attn, t_step, ms_prefill), (work,) = rk.reduce([attn_blocks[mid], step_blocks[mid], ms_prefill], [float(keys[mid] * per_key)])
     gbs = work / (t_attn * 1e-3) / 1e9
     return {"workload": "config 2's decode step on a split pool (16 q heads / 8 kv heads, head_dim 128, page 128, "
                         f"batch {B}, context uniform [{LEN_LO},{LEN_HI}], pool {n_pages} pages)",
@@ -877,6 +897,8 @@ def bench_split_layout(rk, args, n_pages=4096):
                          "traffic": 1.4807e9, "traffic_source": "ncu capture of one launch of this workload; not observed by this run",
                          "bytes_per_launch": work / K / rk.world, "ms_per_launch": round(t_attn / K, 4)},
             "expanded_equivalent_gbs": round(gbs * (2 * HQ * D * 2) / per_key, 1),
+            "prefill_config3_row": {"ms": round(ms_prefill, 4), "tflops_per_gpu": round(4.0 * HQ * D * pairs / (ms_prefill * 1e-3) / 1e12, 1),
+                                    "what": "paged prefill attention of config 3's packed row over the split pool (single-head items)"},
             "gpu_launches_per_step": 3}
 
 
