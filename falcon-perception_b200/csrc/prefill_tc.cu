@@ -70,7 +70,8 @@ namespace {
 constexpr int kTileM = 128, kTileN = 128, kPage = 128;
 constexpr int kTileBytes = 128 * 128 * 2;              // a 128 x 128 16-bit tile: the size of every tile buffer (head_dim 64 fills half)
 constexpr int kHalfBytes = kTileBytes / 2;             // 64 columns (128 bytes) x 128 rows
-constexpr int kStages = 2;
+constexpr int kStages = 2;                             // K ring, and V ring of head-pair items
+constexpr int kStagesVMax = 3;                         // V ring of single-head items: the unused second query buffer is its third stage
 constexpr int kSoftmaxWarps = 4;                       // per head: warps 0-3 are head 0's softmax group, warps 4-7 head 1's
 constexpr int kLoadWarp = 8, kMmaWarp = 9;              // warps 9 and 10 issue the MMAs of head 0 and head 1 of the pair
 constexpr int kScoutWarp = 11;                         // prepares the next item's descriptor
@@ -379,8 +380,8 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_consta
     const uint32_t desc_full0 = s32(bars + 0), desc_empty0 = s32(bars + 2);            // [2] descriptor buffers
     const uint32_t q_full0 = s32(bars + 4), q_empty0 = s32(bars + 6);                  // [2] per head
     const uint32_t k_full0 = s32(bars + 8), v_full0 = s32(bars + 8 + kStages);
-    const uint32_t k_empty0 = s32(bars + 8 + 2 * kStages), v_empty0 = s32(bars + 8 + 3 * kStages);
-    const uint32_t s_half0 = s32(bars + 8 + 4 * kStages);                              // [head][half] scores of 64 keys are in TMEM
+    const uint32_t k_empty0 = s32(bars + 8 + kStages + kStagesVMax), v_empty0 = s32(bars + 8 + 2 * kStages + kStagesVMax);
+    const uint32_t s_half0 = s32(bars + 8 + 2 * kStages + 2 * kStagesVMax);           // [head][half] scores of 64 keys are in TMEM
     const uint32_t p_half0 = s_half0 + 32;                                             // [head][half] P of 64 keys written
     const uint32_t pv_done0 = s_half0 + 64;                                            // [2] a half's P.V has completed (one phase per half)
     const uint32_t all_done0 = s_half0 + 80, o_free0 = s_half0 + 96;                   // [2] last P.V complete / O read by the epilogue
@@ -389,7 +390,12 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_consta
 
     const int tid = threadIdx.x, warp = tid / 32, lane = tid % 32;
     constexpr int kTileBytesD = kTileM * D * 2;            // bytes a Q, K or V tile really holds
-    constexpr bool solo = kSolo;                           // single-head items: the two softmax groups split every key tile
+    constexpr bool solo = kSolo;                           // single-head items: the two sides take the even and the odd key tiles
+    // Single-head items consume two key tiles at once (one per side), so a two-stage ring leaves no room to fetch
+    // ahead.  K is needed late (see the issuer), V is not: its ring gets the second query buffer, which such items
+    // do not use, as a third stage.
+    constexpr int kStagesV = kSolo ? kStagesVMax : kStages;
+    auto v_stage = [&](uint32_t st) -> uint8_t* { return (kSolo && st == 2) ? q_s + kTileBytes : v_s + st * kTileBytes; };
     constexpr int heads = kSolo ? 1 : 2;                   // query heads of one stored head in an item
     const int n_rep = prm.Hq / prm.Hkv;
 
@@ -404,10 +410,8 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_consta
             bar_init(drain0 + 8 * b, 1);
         }
         bar_init(merge0, 2 * kSoftmaxWarps);
-        for (int s = 0; s < kStages; ++s) {
-            bar_init(k_full0 + 8 * s, 1); bar_init(v_full0 + 8 * s, 1);
-            bar_init(k_empty0 + 8 * s, heads); bar_init(v_empty0 + 8 * s, heads);     // one commit per MMA warp that reads the tile
-        }
+        for (int s = 0; s < kStages; ++s) { bar_init(k_full0 + 8 * s, 1); bar_init(k_empty0 + 8 * s, heads); }   // one commit per MMA warp that reads the tile
+        for (int s = 0; s < kStagesV; ++s) { bar_init(v_full0 + 8 * s, 1); bar_init(v_empty0 + 8 * s, heads); }
         *abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
@@ -532,11 +536,11 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_consta
                             }
                         }
                         if (jv < n) {
-                            const uint32_t g = gk + jv, st = g % kStages;
-                            if (bar_try(v_empty0 + 8 * st, ((g / kStages) & 1u) ^ 1u)) {
+                            const uint32_t g = gk + jv, st = g % kStagesV;
+                            if (bar_try(v_empty0 + 8 * st, ((g / kStagesV) & 1u) ^ 1u)) {
                                 bar_expect_tx(v_full0 + 8 * st, kTileBytesD);
-                                if (!prm.split) tma_3d(s32(v_s + st * kTileBytes), &kv_map, 0, d->page_row[jv] + prm.Hkv * prm.rows_per_plane, 0, v_full0 + 8 * st);
-                                else tma_3d(s32(v_s + st * kTileBytes), &v_map, 0, d->page_row[jv], 0, v_full0 + 8 * st);
+                                if (!prm.split) tma_3d(s32(v_stage(st)), &kv_map, 0, d->page_row[jv] + prm.Hkv * prm.rows_per_plane, 0, v_full0 + 8 * st);
+                                else tma_3d(s32(v_stage(st)), &v_map, 0, d->page_row[jv], 0, v_full0 + 8 * st);
                                 v_requested = g + 1; ++jv; progress = true;
                             }
                         }
@@ -567,7 +571,9 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_consta
             constexpr int step = solo ? 2 : 1;             // distance between this issuer's key tiles
             const int j0 = solo ? g : 0;                   // its first key tile of an item
             const uint32_t q_lo = ((s32(q_s) & 0x3FFFF) >> 4) + qb * (kTileBytes >> 4), k_lo = (s32(k_s) & 0x3FFFF) >> 4;
-            const uint32_t v_lo = ((s32(v_s) & 0x3FFFF) >> 4) | (uint32_t)umma_desc(0, kHalfBytes, 1024);
+            // V stage descriptors (MN-major: LBO = distance between the 64-column groups); the third stage of single-head items lies apart
+            const uint32_t v_lo0 = ((s32(v_s) & 0x3FFFF) >> 4) | (uint32_t)umma_desc(0, kHalfBytes, 1024);
+            const uint32_t v_lo2 = ((s32(q_s + kTileBytes) & 0x3FFFF) >> 4) | (uint32_t)umma_desc(0, kHalfBytes, 1024);
             const uint32_t t_s = tmem + g * kTileN, t_o = tmem + 256 + g * kTileN;
             const uint32_t s_lo = s_half0 + 16 * g, s_hi = s_lo + 8, p_lo = p_half0 + 16 * g, p_hi = p_lo + 8;
             const uint32_t pv_done = pv_done0 + 8 * g;
@@ -590,26 +596,29 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_consta
                     if (j0 + step >= n) umma_commit(q_empty0 + 8 * qb);    // that was this issuer's only Q.K^T of the item
                     for (int j = j0; j < n; j += step) {
                         const uint32_t cur = gk + j, nxt = cur + step;
-                        const uint32_t st = cur % kStages, sn = nxt % kStages;
+                        const uint32_t sv = cur % kStagesV, sn = nxt % kStages;
                         const bool more = j + step < n;
                         // the operand tiles first: they arrived long ago, and waiting for them here costs nothing
-                        // while the softmax group is still busy
-                        if (!bar_wait(v_full0 + 8 * st, (cur / kStages) & 1u, abort_flag)) { alive = false; break; }
-                        if (more && !bar_wait(k_full0 + 8 * sn, (nxt / kStages) & 1u, abort_flag)) { alive = false; break; }
+                        // while the softmax group is still busy.  (Single head: the next K tile of this side goes into
+                        // the stage its present tile has just left, so it is waited for only where it is needed.)
+                        if (!bar_wait(v_full0 + 8 * sv, (cur / kStagesV) & 1u, abort_flag)) { alive = false; break; }
+                        if (!solo && more && !bar_wait(k_full0 + 8 * sn, (nxt / kStages) & 1u, abort_flag)) { alive = false; break; }
                         // O of the previous item must have been read by its epilogue before the first P.V overwrites it
                         if (j == j0 && !bar_wait(o_free0 + 8 * g, (wg & 1u) ^ 1u, abort_flag)) { alive = false; break; }
                         // keys 0-63: P.V, then at once the next tile's scores of the same half (its columns are free again)
                         if (!bar_wait(p_lo, th & 1u, abort_flag)) { alive = false; break; }
                         tc_fence_after();
-                        issue_pv_half<0>(t_o, t_s, v_lo + st * (kTileBytes >> 4), desc_hi, idesc_pv, j > j0);
+                        const uint32_t v_lo = (solo && sv == 2) ? v_lo2 : v_lo0 + sv * (kTileBytes >> 4);
+                        issue_pv_half<0>(t_o, t_s, v_lo, desc_hi, idesc_pv, j > j0);
                         umma_commit(pv_done);
+                        if (solo && more && !bar_wait(k_full0 + 8 * sn, (nxt / kStages) & 1u, abort_flag)) { alive = false; break; }
                         if (more) issue_qk_half<0, D>(t_s, q_lo, k_lo + sn * (kTileBytes >> 4), desc_hi, idesc_qk, s_lo);
                         // keys 64-127
                         if (!bar_wait(p_hi, th & 1u, abort_flag)) { alive = false; break; }
                         tc_fence_after();
-                        issue_pv_half<1>(t_o, t_s + 64, v_lo + st * (kTileBytes >> 4), desc_hi, idesc_pv, 1u);
+                        issue_pv_half<1>(t_o, t_s + 64, v_lo, desc_hi, idesc_pv, 1u);
                         umma_commit(pv_done);
-                        umma_commit(v_empty0 + 8 * st);
+                        umma_commit(v_empty0 + 8 * sv);
                         ++th;
                         if (more) {
                             issue_qk_half<1, D>(t_s + 64, q_lo, k_lo + sn * (kTileBytes >> 4), desc_hi, idesc_qk, s_hi);
@@ -677,11 +686,11 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_consta
                 // read shared memory through the async proxy, hence the proxy fence).
                 if (j >= zero_from) {
                     const int tile_rows = page_ok ? min(kTileN, max_extent - j * kTileN) : 0;
-                    const uint32_t cur = gk + j, st = cur % kStages;
-                    if (!bar_wait(v_full0 + 8 * st, (cur / kStages) & 1u, abort_flag)) { alive = false; break; }
+                    const uint32_t cur = gk + j, st = cur % kStagesV;
+                    if (!bar_wait(v_full0 + 8 * st, (cur / kStagesV) & 1u, abort_flag)) { alive = false; break; }
                     for (int i = row; i < (kTileN - tile_rows) * (D / 8); i += kSoftmaxWarps * 32) {
                         const int r = tile_rows + i / (D / 8), c = i % (D / 8);  // token row, 16-byte piece of its D * 2 bytes
-                        *reinterpret_cast<uint4*>(v_s + st * kTileBytes + (c >> 3) * kHalfBytes + r * 128 + ((c & 7) << 4)) =
+                        *reinterpret_cast<uint4*>(v_stage(st) + (c >> 3) * kHalfBytes + r * 128 + ((c & 7) << 4)) =
                             make_uint4(0u, 0u, 0u, 0u);
                     }
                     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
@@ -859,9 +868,11 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_consta
                 const uint32_t last = ((k_requested - 1 - s) / kStages) * kStages + s;    // last key tile requested into stage s
                 for (uint32_t k = 0; k < kSpin && !bar_try(k_full0 + 8 * s, (last / kStages) & 1u); ++k) {}
             }
+        }
+        for (uint32_t s = 0; s < (uint32_t)kStagesV; ++s) {
             if (v_requested > s) {
-                const uint32_t last = ((v_requested - 1 - s) / kStages) * kStages + s;
-                for (uint32_t k = 0; k < kSpin && !bar_try(v_full0 + 8 * s, (last / kStages) & 1u); ++k) {}
+                const uint32_t last = ((v_requested - 1 - s) / kStagesV) * kStagesV + s;
+                for (uint32_t k = 0; k < kSpin && !bar_try(v_full0 + 8 * s, (last / kStagesV) & 1u); ++k) {}
             }
         }
     }
