@@ -62,9 +62,9 @@ def ref():
     return types.SimpleNamespace(model=ref_model, engine=ref_engine)
 
 
-def build_model(ref, dtype):
+def build_model(ref, dtype, head_dim=128):
     from falcon_perception import ModelArgs
-    args = ModelArgs(max_seq_len=1024, dim=256, n_layers=2, n_heads=4, head_dim=128, n_kv_heads=2, vocab_size=512,
+    args = ModelArgs(max_seq_len=1024, dim=256, n_layers=2, n_heads=4, head_dim=head_dim, n_kv_heads=2, vocab_size=512,
                      ffn_dim=512, perception_heads=False, do_segmentation=False)
     args.update(FakeTokenizer())
     torch.manual_seed(1234)
@@ -159,3 +159,12 @@ def test_reference_engine_generates_the_same_tokens_on_the_fpkv_cache(ref, dtype
     got = generate(ref, model, args, "split", graphs=True, batched_setup=True)
     parted += same_tokens(want, got, "batched decode set-up", tie)
     assert parted <= 4, f"{parted} of 20 request runs parted from the reference at a tie: too many to be chance"
+
+
+def test_reference_engine_with_head_dim_64_on_the_expanded_pool(ref):
+    """The smaller released variants have head_dim 64: their exact layout is the reference's own (one stored head per
+    query head), served by the same tiled kernels (single-head items in prefill, n_rep = 1 in decode)."""
+    model, args = build_model(ref, torch.bfloat16, head_dim=64)
+    want = generate(ref, model, args, "reference", graphs=False)
+    got = generate(ref, model, args, "expanded", graphs=True, batched_setup=True)
+    assert same_tokens(want, got, "head_dim 64, expanded pool", 0.05) <= 1
