@@ -375,6 +375,7 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_consta
     int* tmem_slot = ints + 1;
     ItemDesc* desc = reinterpret_cast<ItemDesc*>(ints + 16);   // [2]
     float* xch = reinterpret_cast<float*>(desc + 2);       // [2][2 groups][128 rows][m, l]: merge of single-head items
+    uint8_t* ostage = reinterpret_cast<uint8_t*>(xch + 2 * 2 * kTileM * 2);   // [8 softmax warps][32 rows][64 bytes]: output transposition
 
     // mbarriers; every one keeps its phase across items
     const uint32_t desc_full0 = s32(bars + 0), desc_empty0 = s32(bars + 2);            // [2] descriptor buffers
@@ -777,7 +778,28 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_consta
             const float lse_nat = l > 0.f ? (m_ref + log2f(l)) * kLn2 : -INFINITY;
             const bool gate_on = prm.epi.sinks != nullptr;
             const float gate = sink_gate(prm.epi, hq, lse_nat);
-            T* dst = out + (prm.epi.token_major ? ((size_t)tk * prm.Hq + hq) : ((size_t)hq * prm.L + tk)) * D;
+            // A thread owns a row, so a plain store instruction of the warp would touch 32 rows with 16 bytes each.
+            // 32 columns (64 bytes per row) at a time go through a per-warp staging buffer instead and leave as
+            // 64-byte pieces of 8 rows per instruction (four lanes per row): a quarter of the memory transactions.
+            uint8_t* stage = ostage + warp * 2048;
+            auto put_rows = [&](const uint32_t (&w)[16], int col) {
+                __syncwarp();                              // the buffer's previous readers are done
+#pragma unroll
+                for (int c = 0; c < 4; ++c)                // 16-byte chunk c of row `lane`, chunks permuted against bank conflicts
+                    *reinterpret_cast<uint4*>(stage + lane * 64 + ((c ^ ((lane >> 1) & 3)) << 4)) =
+                        make_uint4(w[4 * c], w[4 * c + 1], w[4 * c + 2], w[4 * c + 3]);
+                __syncwarp();
+#pragma unroll
+                for (int i = 0; i < 4; ++i) {
+                    const int rr = i * 8 + (lane >> 2), cc = lane & 3;
+                    const uint4 v = *reinterpret_cast<const uint4*>(stage + rr * 64 + ((cc ^ ((rr >> 1) & 3)) << 4));
+                    const int tk2 = d->t0 + quarter * 32 + rr;
+                    if (tk2 < prm.L) {
+                        T* at = out + (prm.epi.token_major ? ((size_t)tk2 * prm.Hq + hq) : ((size_t)hq * prm.L + tk2)) * D + col + cc * 8;
+                        *reinterpret_cast<uint4*>(at) = v;
+                    }
+                }
+            };
             if (!solo) {
 #pragma unroll 1
                 for (int c2 = 0; c2 < D / 64; ++c2) {
@@ -791,21 +813,16 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_consta
                             if (lane == 0) bar_arrive(o_free0 + 8 * grp);
                         }
                     }
-                    if (tk < prm.L) {
 #pragma unroll
-                        for (int q8 = 0; q8 < 4; ++q8) {
-                            uint32_t w[8];
+                    for (int q16 = 0; q16 < 2; ++q16) {
+                        uint32_t w[16];
 #pragma unroll
-                            for (int e = 0; e < 8; ++e) {
-                                const int c = q8 * 16 + 2 * e;
-                                const float a = (n > 0 && l > 0.f) ? __uint_as_float(sv[c >> 5][c & 31]) * inv : 0.f;
-                                const float bb = (n > 0 && l > 0.f) ? __uint_as_float(sv[c >> 5][(c & 31) + 1]) * inv : 0.f;
-                                w[e] = gated_pair<T>(a, bb, gate, gate_on);
-                            }
-                            T* at = dst + c2 * 64 + q8 * 16;   // two adjacent 16-byte stores fill a 32-byte sector
-                            *reinterpret_cast<uint4*>(at) = make_uint4(w[0], w[1], w[2], w[3]);
-                            *reinterpret_cast<uint4*>(at + 8) = make_uint4(w[4], w[5], w[6], w[7]);
+                        for (int e = 0; e < 16; ++e) {
+                            const float a = (n > 0 && l > 0.f) ? __uint_as_float(sv[q16][2 * e]) * inv : 0.f;
+                            const float bb = (n > 0 && l > 0.f) ? __uint_as_float(sv[q16][2 * e + 1]) * inv : 0.f;
+                            w[e] = gated_pair<T>(a, bb, gate, gate_on);
                         }
+                        put_rows(w, c2 * 64 + q16 * 32);
                     }
                 }
             } else {
@@ -825,25 +842,18 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_consta
                         if (lane == 0 && own_tiles) bar_arrive(o_free0 + 8 * grp);
                         if (lane == 0 && oth_tiles) bar_arrive(o_free0 + 8 * (grp ^ 1));
                     }
-                    if (tk < prm.L) {
+                    uint32_t w[16];
 #pragma unroll
-                        for (int q8 = 0; q8 < 2; ++q8) {
-                            uint32_t w[8];
-#pragma unroll
-                            for (int e = 0; e < 8; ++e) {
-                                const int c = q8 * 16 + 2 * e;
-                                const bool some = n > 0 && l > 0.f;
-                                const float a0 = own_tiles ? __uint_as_float(sv[0][c]) * w_own : 0.f, a1 = oth_tiles ? __uint_as_float(sv[1][c]) * w_oth : 0.f;
-                                const float b0 = own_tiles ? __uint_as_float(sv[0][c + 1]) * w_own : 0.f, b1 = oth_tiles ? __uint_as_float(sv[1][c + 1]) * w_oth : 0.f;
-                                const float a = some ? (a0 + a1) * inv : 0.f;
-                                const float bb = some ? (b0 + b1) * inv : 0.f;
-                                w[e] = gated_pair<T>(a, bb, gate, gate_on);
-                            }
-                            T* at = dst + col0 + q8 * 16;
-                            *reinterpret_cast<uint4*>(at) = make_uint4(w[0], w[1], w[2], w[3]);
-                            *reinterpret_cast<uint4*>(at + 8) = make_uint4(w[4], w[5], w[6], w[7]);
-                        }
+                    for (int e = 0; e < 16; ++e) {
+                        const int c = 2 * e;
+                        const bool some = n > 0 && l > 0.f;
+                        const float a0 = own_tiles ? __uint_as_float(sv[0][c]) * w_own : 0.f, a1 = oth_tiles ? __uint_as_float(sv[1][c]) * w_oth : 0.f;
+                        const float b0 = own_tiles ? __uint_as_float(sv[0][c + 1]) * w_own : 0.f, b1 = oth_tiles ? __uint_as_float(sv[1][c + 1]) * w_oth : 0.f;
+                        const float a = some ? (a0 + a1) * inv : 0.f;
+                        const float bb = some ? (b0 + b1) * inv : 0.f;
+                        w[e] = gated_pair<T>(a, bb, gate, gate_on);
                     }
+                    put_rows(w, col0);
                 }
             }
             if (tk < prm.L && (!solo || grp == 0)) prm.lse[(size_t)hq * prm.L + tk] = lse_nat;
@@ -909,7 +919,7 @@ int prefill_sm_count() {
 }
 
 constexpr int kPrefillSmem = 1024 + (2 + 2 * kStages) * kTileBytes + 48 * 8 + 16 * 4 + 2 * (int)sizeof(ItemDesc) +
-                             2 * 2 * kTileM * 8 + 64;   // Q x2, K and V x kStages, barriers, flags, descriptors, merge buffers
+                             2 * 2 * kTileM * 8 + 8 * 2048 + 64;   // Q x2, K and V x kStages, barriers, flags, descriptors, merge and output staging buffers
 
 }  // namespace
 
