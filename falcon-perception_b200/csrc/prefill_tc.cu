@@ -362,7 +362,7 @@ template <typename T, int D, bool kSolo>
 __global__ void __launch_bounds__(kPrefillThreads, 1)
 prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_constant__ CUtensorMap kv_map,
                   const __grid_constant__ CUtensorMap khw_map, const __grid_constant__ CUtensorMap v_map,
-                  const PrefillParams prm)
+                  const __grid_constant__ CUtensorMap o_map, const PrefillParams prm)
 {
     extern __shared__ uint8_t smem_raw[];
     uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -660,7 +660,6 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_consta
         const uint32_t ts = tmem + grp * kTileN + lane_base;          // this group's scores: keys 0-63 in columns [0,64), keys 64-127 in [64,128)
         const uint32_t to = tmem + 256 + grp * kTileN + lane_base;    // this group's accumulator
         const uint32_t pv_done = pv_done0 + 8 * grp;
-        T* out = reinterpret_cast<T*>(prm.out);
         uint32_t gk = 0, th = 0, wit = 0, wg = 0;          // key tiles of all items, this group's tiles, items with work, items with work for this group
         for (uint32_t it = 0; alive; ++it) {
             const uint32_t b = it & 1u;
@@ -779,25 +778,27 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_consta
             const bool gate_on = prm.epi.sinks != nullptr;
             const float gate = sink_gate(prm.epi, hq, lse_nat);
             // A thread owns a row, so a plain store instruction of the warp would touch 32 rows with 16 bytes each.
-            // 32 columns (64 bytes per row) at a time go through a per-warp staging buffer instead and leave as
-            // 64-byte pieces of 8 rows per instruction (four lanes per row): a quarter of the memory transactions.
+            // 32 columns (64 bytes per row) at a time go into a per-warp staging buffer instead, in the 64-byte
+            // swizzle pattern (conflict-free for the row-per-lane writes), and leave as one bulk tensor store of
+            // 32 rows x 64 bytes: the warp does not wait for the memory system, only -- before it refills the buffer
+            // -- for the copy engine to have read it.  Rows past the end of the packed row fall outside the tensor
+            // map and are dropped by the copy.
             uint8_t* stage = ostage + warp * 2048;
             auto put_rows = [&](const uint32_t (&w)[16], int col) {
-                __syncwarp();                              // the buffer's previous readers are done
-#pragma unroll
-                for (int c = 0; c < 4; ++c)                // 16-byte chunk c of row `lane`, chunks permuted against bank conflicts
-                    *reinterpret_cast<uint4*>(stage + lane * 64 + ((c ^ ((lane >> 1) & 3)) << 4)) =
-                        make_uint4(w[4 * c], w[4 * c + 1], w[4 * c + 2], w[4 * c + 3]);
+                if (lane == 0) asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");   // the previous copy has read the buffer
                 __syncwarp();
 #pragma unroll
-                for (int i = 0; i < 4; ++i) {
-                    const int rr = i * 8 + (lane >> 2), cc = lane & 3;
-                    const uint4 v = *reinterpret_cast<const uint4*>(stage + rr * 64 + ((cc ^ ((rr >> 1) & 3)) << 4));
-                    const int tk2 = d->t0 + quarter * 32 + rr;
-                    if (tk2 < prm.L) {
-                        T* at = out + (prm.epi.token_major ? ((size_t)tk2 * prm.Hq + hq) : ((size_t)hq * prm.L + tk2)) * D + col + cc * 8;
-                        *reinterpret_cast<uint4*>(at) = v;
-                    }
+                for (int c = 0; c < 4; ++c)                // 16-byte chunk c of row `lane`
+                    *reinterpret_cast<uint4*>(stage + lane * 64 + ((c ^ ((lane >> 1) & 3)) << 4)) =
+                        make_uint4(w[4 * c], w[4 * c + 1], w[4 * c + 2], w[4 * c + 3]);
+                asm volatile("fence.proxy.async.shared::cta;" ::: "memory");     // every writer, ahead of the copy engine's read
+                __syncwarp();
+                const int row0 = d->t0 + quarter * 32;     // first packed token of this warp's rows
+                if (lane == 0 && row0 < prm.L) {
+                    const int c1 = prm.epi.token_major ? hq : row0, c2 = prm.epi.token_major ? row0 : hq;
+                    asm volatile("cp.async.bulk.tensor.3d.global.shared::cta.tile.bulk_group [%0, {%1, %2, %3}], [%4];"
+                                 ::"l"(reinterpret_cast<uint64_t>(&o_map)), "r"(col), "r"(c1), "r"(c2), "r"(s32(stage)) : "memory");
+                    asm volatile("cp.async.bulk.commit_group;" ::: "memory");
                 }
             };
             if (!solo) {
@@ -860,6 +861,7 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_consta
             __syncwarp();
             if (lane == 0) bar_arrive(desc_empty0 + 8 * b);
         }
+        if (lane == 0) asm volatile("cp.async.bulk.wait_group.read 0;" ::: "memory");   // the staging buffer is shared memory the next CTA gets
     }
     if (!alive && lane == 0) {
         if (!*abort_flag) raise_status(prm.status, FPKV_STATUS_TIMEOUT);
@@ -971,6 +973,17 @@ int launch_prefill_tc(const PoolView& pv, int layer, void* out, float* lse, cons
                       CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
             return FPKV_ELAUNCH;
     }
+    CUtensorMap o_map;
+    {   // output rows: (head_dim, Hq heads, L tokens) or (head_dim, L tokens, Hq heads), written 32 rows x 64 bytes at a time
+        const bool tm = epi.token_major;
+        const cuuint64_t dims[3] = {(cuuint64_t)pv.D, (cuuint64_t)(tm ? Hq : L), (cuuint64_t)(tm ? L : Hq)};
+        const cuuint64_t strides[2] = {(cuuint64_t)pv.D * 2, (cuuint64_t)(tm ? Hq : L) * pv.D * 2};
+        const cuuint32_t box[3] = {32, tm ? 1u : 32u, tm ? 32u : 1u};
+        const cuuint32_t es[3] = {1, 1, 1};
+        if (encoder()(&o_map, dt, 3, out, dims, strides, box, es, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_64B,
+                      CU_TENSOR_MAP_L2_PROMOTION_NONE, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
+            return FPKV_ELAUNCH;
+    }
     PrefillParams prm;
     prm.page_table = pv.page_table; prm.p2l = pv.p2l; prm.batch_idx = batch_idx; prm.extent = extent;
     prm.out = out; prm.lse = lse; prm.status = status;
@@ -988,7 +1001,7 @@ int launch_prefill_tc(const PoolView& pv, int layer, void* out, float* lse, cons
     const int grid = prm.n_items < prefill_sm_count() ? prm.n_items : prefill_sm_count();    // persistent: one CTA per SM
     auto launch = [&](auto kern) {
         if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, kPrefillSmem) != cudaSuccess) return false;
-        kern<<<grid, kPrefillThreads, kPrefillSmem, stream>>>(q_map, kv_map, khw_map, v_map, prm);
+        kern<<<grid, kPrefillThreads, kPrefillSmem, stream>>>(q_map, kv_map, khw_map, v_map, o_map, prm);
         return true;
     };
     bool ok;
