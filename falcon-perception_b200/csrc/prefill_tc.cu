@@ -376,6 +376,8 @@ prefill_tc_kernel(const __grid_constant__ CUtensorMap q_map, const __grid_consta
     ItemDesc* desc = reinterpret_cast<ItemDesc*>(ints + 16);   // [2]
     float* xch = reinterpret_cast<float*>(desc + 2);       // [2][2 groups][128 rows][m, l]: merge of single-head items
     uint8_t* ostage = reinterpret_cast<uint8_t*>(xch + 2 * 2 * kTileM * 2);   // [8 softmax warps][32 rows][64 bytes]: output transposition
+    static_assert((48 * 8 + 16 * 4 + 2 * sizeof(ItemDesc) + 2 * 2 * kTileM * 8) % 512 == 0,
+                  "the output staging buffers must start on a 512-byte boundary (64-byte swizzle pattern of the bulk stores)");
 
     // mbarriers; every one keeps its phase across items
     const uint32_t desc_full0 = s32(bars + 0), desc_empty0 = s32(bars + 2);            // [2] descriptor buffers
