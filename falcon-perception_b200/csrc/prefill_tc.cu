@@ -53,8 +53,9 @@
 //     writes half of the output columns).
 // The running maximum is only raised when a half exceeds it by more than 2^8
 // (probabilities stay below 256, exact in fp32 and harmless in bf16), so O in
-// TMEM is rarely rescaled.  Each thread owns a whole output row and writes it
-// straight from registers (256 contiguous bytes).
+// TMEM is rarely rescaled.  Each thread owns a whole output row; 32 columns of
+// a warp's 32 rows at a time are staged in shared memory (64-byte swizzle) and
+// leave as one bulk tensor store.
 // Every wait is a bounded mbarrier wait; on expiry the CTA raises
 // FPKV_STATUS_TIMEOUT, every role leaves its loops, the copies and MMAs in
 // flight are drained (bounded), TMEM is freed and the kernel returns.
