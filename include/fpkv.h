@@ -333,7 +333,8 @@ FPKV_API int fpkv_decode_attn(const fpkv_pool* pool, int32_t layer,
  * (paged_inference.py:634-672); other rows raise FPKV_STATUS_BAD_SLOT.
  *
  * q    device (1, n_q_heads, L, head_dim), element strides q_stride_h / _t
- * out  device (1, n_q_heads, L, head_dim) contiguous, dtype of q
+ * out  device (1, n_q_heads, L, head_dim) contiguous, 16-byte aligned, dtype
+ *      of q
  * lse  device (1, n_q_heads, L) fp32 natural log; rows without a visible key
  *      give out = 0, lse = -inf.
  * flags: FPKV_PREFILL_AUTO runs the tcgen05 tensor-core kernel for 16-bit

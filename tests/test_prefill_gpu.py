@@ -90,6 +90,27 @@ def test_prefill_against_oracle(name, seqs, scale):
     c.check_status()
 
 
+@pytest.mark.parametrize("kernel", [_lib.PREFILL_TC, _lib.PREFILL_PORTABLE])
+def test_prefill_row_of_any_length(kernel):
+    """A packed row that ends with its last token instead of padding, its length no multiple of the query tile,
+    of a warp's 32 rows or of 8: the last tile's rows past the end are neither read nor written, in either
+    output layout.  (Sequences still start on tile boundaries: a query tile holds rows of one sequence.)"""
+    seqs = [T(0, 0, 301), T(2, 70, 30), T(0, 0, 77)]
+    case = wl.make_prefill_case(2024, seqs, Hq=16, Hkv=8, D=128, P=128, align=128, dtype=torch.bfloat16)
+    L = case.offsets[-1] + len(seqs[-1])
+    assert L == 384 + 128 + 77 and L % 8
+    case.input_ids, case.input_pos, case.seq_index = (x[:, :L].contiguous() for x in (case.input_ids, case.input_pos, case.seq_index))
+    case.q, case.k, case.v = (x[:, :, :L].contiguous() for x in (case.q, case.k, case.v))
+    c, slots, bidx, ipos, mask, out, lse = run_product(case, 8, 5, kernel=kernel)
+    ref_out, ref_lse = oracle_prefill(case, slots)
+    compare_live_rows(case, out, lse, ref_out, ref_lse, "unpadded row")
+    # the token-major output layout holds the same numbers
+    tout, tlse = c.prefill_attention(0, case.q.to(torch.bfloat16).cuda(), bidx, ipos, mask, token_major=True)
+    assert tuple(tout.shape) == (1, L, 16, 128)
+    assert torch.equal(tout.transpose(1, 2), out) and torch.equal(tlse, lse)
+    c.check_status()
+
+
 def test_chunked_prefill_equals_whole_prompt():
     """Queries of a prompt processed 512 rows at a time against the pages (all K/V appended first, as the
     bidirectional image span needs) give the rows of the unchunked result; so does a reordered packing."""
