@@ -111,6 +111,21 @@ def test_prefill_row_of_any_length(kernel):
     c.check_status()
 
 
+@pytest.mark.parametrize("n_tokens", [1, 5, 33])
+def test_prefill_row_shorter_than_a_tile(n_tokens):
+    """A packed row of a few tokens (shorter than the 128-row query tile and the 32-row output piece) on the
+    tensor-core kernel, both output layouts."""
+    seqs = [T(0, 0, n_tokens)]
+    case = wl.make_prefill_case(77 + n_tokens, seqs, Hq=16, Hkv=8, D=128, P=128, align=1, dtype=torch.bfloat16)
+    assert case.L == n_tokens
+    c, slots, bidx, ipos, mask, out, lse = run_product(case, 4, 3, kernel=_lib.PREFILL_TC)
+    ref_out, ref_lse = oracle_prefill(case, slots)
+    compare_live_rows(case, out, lse, ref_out, ref_lse, "short row")
+    tout, tlse = c.prefill_attention(0, case.q.to(torch.bfloat16).cuda(), bidx, ipos, mask, token_major=True)
+    assert torch.equal(tout.transpose(1, 2), out) and torch.equal(tlse, lse)
+    c.check_status()
+
+
 def test_chunked_prefill_equals_whole_prompt():
     """Queries of a prompt processed 512 rows at a time against the pages (all K/V appended first, as the
     bidirectional image span needs) give the rows of the unchunked result; so does a reordered packing."""
